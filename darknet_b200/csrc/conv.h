@@ -1,0 +1,103 @@
+// Internal argument blocks of the convolution kernels and the plan object.
+#pragma once
+#include <cuda.h>
+
+#include <vector>
+
+#include "common.h"
+
+namespace dnb {
+
+// ---- conv_direct.cu
+struct DirectArgs {
+    const void *x;                       // input, any layout through element strides
+    int x_dtype;
+    long long xs_b, xs_c, xs_h, xs_w;    // element strides of x
+    const float *wpk;                    // weights [groups][K][npg_pad], K = c/groups*size*size
+    int npg_pad;                         // filters per group rounded up to 16
+    void *y_nhwc;                        // optional NHWC output
+    int y_dtype, y_cpitch;
+    float *y_nchw;                       // optional NCHW f32 output
+    ConvGeom g;
+    ConvEpilogue ep;
+};
+int launch_conv_direct(const DirectArgs &a, cudaStream_t s);
+
+// ---- conv_tc.cu : implicit GEMM on tcgen05 / TMEM, operands by TMA
+struct alignas(64) TcArgs {
+    CUtensorMap tmx[4];   // activation maps: one per (row parity, column parity) lattice of a strided conv
+    CUtensorMap tmw;      // weights [taps][n_pad][c_pad], channels innermost
+    int is_bf16;          // 0: kind::tf32 on f32 operands, 1: kind::f16 on bf16 operands
+    int row_bytes;        // bytes of channels per pipeline stage row: 128, 64 or 32 (= swizzle span)
+    int bk;               // channels per stage row (row_bytes / element size)
+    int c_blocks;         // ceil(c_pad / bk)
+    int taps;             // size*size
+    int bn;               // filters per tile: multiple of 16, <= 256
+    int n_tiles;          // ceil(n / bn)
+    int wt, ht, bt;       // output pixels per tile along w, h, batch; wt*ht*bt == 128
+    int tiles_w, tiles_h, tiles_b;
+    int total_tiles;      // n_tiles * tiles_w * tiles_h * tiles_b
+    int stages;           // depth of the shared-memory ring
+    int a_bytes, b_bytes; // shared-memory bytes of one stage's activation / weight tile (1024-multiples)
+    void *y_nhwc;
+    int y_dtype, y_cpitch;
+    float *y_nchw;
+    int *status;          // device word: 0, or the code of the wait that expired
+    ConvGeom g;
+    ConvEpilogue ep;
+};
+int launch_conv_tc(const TcArgs &a, cudaStream_t s);
+size_t conv_tc_smem_bytes(const TcArgs &a);
+int conv_tc_max_smem();
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link).
+int encode_tensor_map(CUtensorMap *map, int is_bf16, int rank, void *base, const uint64_t *dims,
+                      const uint64_t *strides_bytes /* rank-1 */, const uint32_t *box, int swizzle_bytes);
+
+// ---- conv_xnor.cu : bit-packed popcount GEMM
+struct XnorArgs {
+    const uint32_t *xbits;   // [b][h][w][cwords] sign bits of the input (1 = x > 0)
+    const uint32_t *wbits;   // [n][taps][cwords] sign bits of the weights (1 = w > 0)
+    int cwords;              // ceil(c / 32); unused high bits are 0 in both operands
+    const float *wmean;      // [n] mean |w| per filter
+    int32_t *acc_out;        // optional NCHW int32 accumulators
+    void *y_nhwc;
+    int y_dtype, y_cpitch;
+    float *y_nchw;
+    ConvGeom g;
+    ConvEpilogue ep;
+};
+int launch_conv_xnor(const XnorArgs &a, cudaStream_t s);
+// sign bits of an NHWC (f32/bf16) or NCHW f32 tensor into [b][h][w][cwords]
+int launch_pack_sign_bits(const dnb_tensor *x, uint32_t *bits, int cwords, cudaStream_t s);
+
+}  // namespace dnb
+
+// The plan object behind the C ABI.
+struct dnb_conv_plan {
+    dnb_conv_desc d;
+    int mode;
+    int kernel;              // 0 tc_tf32, 1 tc_bf16, 2 direct_fp32, 3 xnor_popc
+    dnb::ConvGeom g;
+    int n_pad;               // filters rounded up to 16
+    int c_pad;               // input channels rounded up to 8 (cpitch the kernel expects of NHWC input)
+    bool params_set;
+    // derived device tensors
+    float *scale, *shift;    // [n_pad] folded batchnorm / bias
+    void *w_tc;              // [taps][n_pad][c_pad] f32 (TF32-rounded) or bf16
+    float *w_direct;         // [groups][K][npg_pad]
+    uint32_t *w_bits;        // [n][taps][cwords]
+    float *w_mean;           // [n]
+    int npg_pad, cwords;
+    // scratch owned by the plan
+    void *x_nhwc_scratch;    // NHWC copy of an NCHW input handed to a tensor-core plan
+    size_t x_nhwc_bytes;
+    uint32_t *x_bits;        // packed input of an xnor plan
+    size_t x_bits_bytes;
+    int *status;             // device status word of the tensor-core kernel
+    // tensor-core launch block, rebuilt when the input pointer changes
+    dnb::TcArgs tc;
+    const void *tc_x_ptr;
+    int tc_x_cpitch;
+    int device;
+};

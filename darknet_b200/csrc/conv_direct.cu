@@ -1,0 +1,143 @@
+// Direct convolution on the CUDA cores (fp32 FMA, fp32 accumulate).
+//
+// Used where the tensor-core kernel does not apply: very narrow inputs (the
+// 3-channel first layer, which it reads straight from Darknet's NCHW input),
+// grouped convolutions, and DNB_MODE_FP32 networks.  One thread owns one output
+// pixel and FB consecutive filters; the weights of the block's filter slab are
+// staged through shared memory in K chunks together with a (c,kh,kw) table, so
+// the inner loop is one predicated load of x and FB FMAs.  Accumulation runs
+// over k = c*size*size + kh*size + kw in increasing order, the reference's own
+// order (src/im2col.c:25-28, src/gemm.c:81-87).
+#include "common.h"
+#include "conv.h"
+#include "device_utils.cuh"
+
+namespace dnb {
+
+constexpr int FB = 16;         // filters per thread
+constexpr int KCHUNK = 384;    // taps staged per pass: 384*(16*4 + 4) B = 26 KB
+constexpr int DTHREADS = 128;  // pixels per block
+
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(DTHREADS)
+conv_direct_kernel(DirectArgs a)
+{
+    __shared__ __align__(16) float w_s[KCHUNK][FB];
+    __shared__ int tap_s[KCHUNK];
+
+    const ConvGeom &g = a.g;
+    const int cpg = g.c / g.groups;           // input channels per group
+    const int npg = g.n / g.groups;           // filters per group
+    const int fblocks_per_group = (npg + FB - 1) / FB;
+    const int grp = blockIdx.y / fblocks_per_group;
+    const int f0 = (blockIdx.y % fblocks_per_group) * FB;   // first filter within the group
+    const int K = cpg * g.size * g.size;
+    const int ksq = g.size * g.size;
+
+    const long long npix = (long long)g.batch * g.out_h * g.out_w;
+    const long long pix = (long long)blockIdx.x * DTHREADS + threadIdx.x;
+    const bool live = pix < npix;
+    int b = 0, oh = 0, ow = 0;
+    if (live) {
+        ow = (int)(pix % g.out_w);
+        long long t = pix / g.out_w;
+        oh = (int)(t % g.out_h);
+        b = (int)(t / g.out_h);
+    }
+    const int ih0 = oh * g.stride - g.pad, iw0 = ow * g.stride - g.pad;
+    const TX *xb = reinterpret_cast<const TX *>(a.x) + b * a.xs_b + (long long)grp * cpg * a.xs_c;
+
+    float acc[FB];
+#pragma unroll
+    for (int j = 0; j < FB; ++j) acc[j] = 0.f;
+
+    for (int k0 = 0; k0 < K; k0 += KCHUNK) {
+        const int kn = min(KCHUNK, K - k0);
+        __syncthreads();
+        // weights of this slab: packed [group][k][npg_pad], npg_pad a multiple of FB
+        for (int i = threadIdx.x; i < kn * FB; i += DTHREADS) {
+            int kk = i / FB, j = i % FB;
+            w_s[kk][j] = __ldg(a.wpk + ((size_t)grp * K + k0 + kk) * a.npg_pad + f0 + j);
+        }
+        for (int kk = threadIdx.x; kk < kn; kk += DTHREADS) {
+            int k = k0 + kk, c = k / ksq, r = k - c * ksq, kh = r / g.size, kw = r - kh * g.size;
+            tap_s[kk] = (c << 8) | (kh << 4) | kw;
+        }
+        __syncthreads();
+        if (live) {
+            for (int kk = 0; kk < kn; ++kk) {
+                const int t = tap_s[kk];
+                const int c = t >> 8, ih = ih0 + ((t >> 4) & 15), iw = iw0 + (t & 15);
+                float xv = 0.f;
+                if (ih >= 0 && ih < g.h && iw >= 0 && iw < g.w)
+                    xv = to_float<TX>(xb[c * a.xs_c + ih * a.xs_h + iw * a.xs_w]);
+                const float4 *wr = reinterpret_cast<const float4 *>(w_s[kk]);
+#pragma unroll
+                for (int q = 0; q < FB / 4; ++q) {
+                    float4 w4 = wr[q];
+                    acc[4 * q + 0] = fmaf(xv, w4.x, acc[4 * q + 0]);
+                    acc[4 * q + 1] = fmaf(xv, w4.y, acc[4 * q + 1]);
+                    acc[4 * q + 2] = fmaf(xv, w4.z, acc[4 * q + 2]);
+                    acc[4 * q + 3] = fmaf(xv, w4.w, acc[4 * q + 3]);
+                }
+            }
+        }
+    }
+    if (!live) return;
+
+    // Epilogue: folded batchnorm / bias, activation, stores.
+    const int n0 = grp * npg + f0;  // first global filter of this thread
+#pragma unroll
+    for (int j = 0; j < FB; ++j) {
+        const int n = n0 + j;
+        float v = 0.f;
+        if (f0 + j < npg) {
+            v = acc[j] * __ldg(a.ep.scale + n) + __ldg(a.ep.shift + n);
+            v = activate(v, a.ep.activation);
+            if (a.ep.round_tf32) v = round_tf32(v);
+        }
+        acc[j] = v;
+    }
+    if (a.y_nhwc) {
+        TY *dst = reinterpret_cast<TY *>(a.y_nhwc) + (size_t)pix * a.y_cpitch + n0;
+        if (f0 + FB <= npg && (n0 % FB) == 0) {
+            if (sizeof(TY) == 4) {
+#pragma unroll
+                for (int q = 0; q < FB / 4; ++q)
+                    reinterpret_cast<float4 *>(dst)[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+            } else {
+                __align__(16) __nv_bfloat16 h[FB];
+#pragma unroll
+                for (int j = 0; j < FB; ++j) h[j] = __float2bfloat16_rn(acc[j]);
+#pragma unroll
+                for (int q = 0; q < FB / 8; ++q) reinterpret_cast<uint4 *>(dst)[q] = reinterpret_cast<uint4 *>(h)[q];
+            }
+        } else {
+            for (int j = 0; j < FB && f0 + j < npg; ++j) dst[j] = from_float<TY>(acc[j]);
+        }
+    }
+    if (a.y_nchw) {
+        const size_t plane = (size_t)g.out_h * g.out_w;
+        float *dst = a.y_nchw + ((size_t)b * g.n + n0) * plane + (size_t)oh * g.out_w + ow;
+        for (int j = 0; j < FB && f0 + j < npg; ++j) dst[j * plane] = acc[j];
+    }
+}
+
+int launch_conv_direct(const DirectArgs &a, cudaStream_t s)
+{
+    const ConvGeom &g = a.g;
+    if (g.size > 15) DNB_FAIL(DNB_EUNSUPPORTED, "direct conv: kernel size %d > 15", g.size);
+    const long long npix = (long long)g.batch * g.out_h * g.out_w;
+    const int npg = g.n / g.groups;
+    dim3 grid((unsigned)((npix + DTHREADS - 1) / DTHREADS), (unsigned)(g.groups * ((npg + FB - 1) / FB)));
+    if (grid.y > 65535) DNB_FAIL(DNB_EUNSUPPORTED, "direct conv: too many filter blocks (%u)", grid.y);
+    const bool xb = a.x_dtype == DNB_BF16, yb = a.y_dtype == DNB_BF16;
+    if (!xb && !yb) conv_direct_kernel<float, float><<<grid, DTHREADS, 0, s>>>(a);
+    else if (!xb && yb) conv_direct_kernel<float, __nv_bfloat16><<<grid, DTHREADS, 0, s>>>(a);
+    else if (xb && !yb) conv_direct_kernel<__nv_bfloat16, float><<<grid, DTHREADS, 0, s>>>(a);
+    else conv_direct_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, DTHREADS, 0, s>>>(a);
+    DNB_LAUNCH_CHECK("conv_direct");
+    return DNB_OK;
+}
+
+}  // namespace dnb

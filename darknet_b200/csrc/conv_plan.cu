@@ -1,0 +1,368 @@
+// Convolution plans: geometry checks, kernel choice, derived parameter tensors
+// (folded batchnorm, repacked / rounded / bit-packed weights) and the forward
+// dispatch behind dnb_conv_*.
+#include <math.h>
+#include <string.h>
+
+#include <vector>
+
+#include "common.h"
+#include "conv.h"
+
+using namespace dnb;
+
+enum { K_TC_TF32 = 0, K_TC_BF16 = 1, K_DIRECT = 2, K_XNOR = 3 };
+static const char *const kKernelNames[] = {"tc_tf32", "tc_bf16", "direct_fp32", "xnor_popc"};
+
+static float tf32_round_host(float x)
+{
+    // nearest TF32, ties away from zero (the device uses cvt.rna.tf32.f32)
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    if ((u & 0x7f800000u) == 0x7f800000u) return x;
+    u += 0x1000u;
+    u &= ~0x1fffu;
+    memcpy(&x, &u, 4);
+    return x;
+}
+
+static uint16_t bf16_round_host(float x)
+{
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);  // NaN
+    u += 0x7fffu + ((u >> 16) & 1);  // round to nearest even
+    return (uint16_t)(u >> 16);
+}
+
+extern "C" int dnb_conv_plan_create(const dnb_conv_desc *d, int mode, dnb_conv_plan **out)
+{
+    if (!d || !out) DNB_FAIL(DNB_EINVAL, "conv plan: null argument");
+    *out = nullptr;
+    if (mode != DNB_MODE_TF32 && mode != DNB_MODE_BF16 && mode != DNB_MODE_FP32) DNB_FAIL(DNB_EINVAL, "conv plan: mode %d", mode);
+    if (d->batch < 1 || d->h < 1 || d->w < 1 || d->c < 1 || d->n < 1 || d->size < 1 || d->stride < 1 || d->pad < 0 || d->groups < 1)
+        DNB_FAIL(DNB_EINVAL, "conv plan: non-positive geometry (batch %d, %dx%dx%d, n %d, size %d, stride %d, pad %d, groups %d)",
+                 d->batch, d->c, d->h, d->w, d->n, d->size, d->stride, d->pad, d->groups);
+    if (d->c % d->groups || d->n % d->groups) DNB_FAIL(DNB_EINVAL, "conv plan: groups %d does not divide c %d and n %d", d->groups, d->c, d->n);
+    if (d->activation < 0 || d->activation > DNB_SELU) DNB_FAIL(DNB_EINVAL, "conv plan: activation %d", d->activation);
+    if (d->size > 15) DNB_FAIL(DNB_EUNSUPPORTED, "conv plan: kernel size %d > 15", d->size);
+    const int out_h = (d->h + 2 * d->pad - d->size) / d->stride + 1;
+    const int out_w = (d->w + 2 * d->pad - d->size) / d->stride + 1;
+    if (out_h < 1 || out_w < 1) DNB_FAIL(DNB_EINVAL, "conv plan: empty output (%dx%d)", out_w, out_h);
+    if (d->size == 1 && (d->stride != 1 || d->pad != 0))
+        DNB_FAIL(DNB_EUNSUPPORTED, "conv plan: 1x1 kernel with stride %d / pad %d: the reference's CPU path skips im2col for size 1 and "
+                 "multiplies the unstrided image (src/convolutional_layer.c:468-470), so its result is not a convolution; not reproduced", d->stride, d->pad);
+    if (d->xnor && d->groups != 1) DNB_FAIL(DNB_EUNSUPPORTED, "conv plan: xnor with groups %d", d->groups);
+
+    dnb_conv_plan *p = new dnb_conv_plan();
+    memset(p, 0, sizeof(*p));
+    p->d = *d;
+    p->mode = mode;
+    p->g = ConvGeom{d->batch, d->h, d->w, d->c, d->n, d->groups, d->size, d->stride, d->pad, out_h, out_w};
+    p->n_pad = round_up(d->n, 16);
+    p->c_pad = round_up(d->c, 8);
+    p->npg_pad = round_up(d->n / d->groups, 16);
+    p->cwords = (d->c + 31) / 32;
+    if (d->xnor) p->kernel = K_XNOR;
+    else if (mode == DNB_MODE_FP32 || d->groups != 1 || d->c < 8) p->kernel = K_DIRECT;
+    else p->kernel = mode == DNB_MODE_BF16 ? K_TC_BF16 : K_TC_TF32;
+    cudaGetDevice(&p->device);
+    *out = p;
+    return DNB_OK;
+}
+
+extern "C" void dnb_conv_plan_destroy(dnb_conv_plan *p)
+{
+    if (!p) return;
+    cudaFree(p->scale); cudaFree(p->shift); cudaFree(p->w_tc); cudaFree(p->w_direct); cudaFree(p->w_bits);
+    cudaFree(p->w_mean); cudaFree(p->x_nhwc_scratch); cudaFree(p->x_bits); cudaFree(p->status);
+    delete p;
+}
+
+extern "C" const char *dnb_conv_plan_kernel(const dnb_conv_plan *p) { return p ? kKernelNames[p->kernel] : ""; }
+
+template <typename T>
+static int upload(T **dst, const std::vector<T> &src)
+{
+    if (*dst) { cudaFree(*dst); *dst = nullptr; }
+    DNB_CUDA(cudaMalloc((void **)dst, src.size() * sizeof(T)));
+    DNB_CUDA(cudaMemcpy(*dst, src.data(), src.size() * sizeof(T), cudaMemcpyHostToDevice));
+    return DNB_OK;
+}
+
+extern "C" int dnb_conv_plan_set_params(dnb_conv_plan *p, const float *weights, const float *biases, const float *scales,
+                                        const float *mean, const float *var)
+{
+    if (!p || !weights || !biases) DNB_FAIL(DNB_EINVAL, "conv params: null argument");
+    const dnb_conv_desc &d = p->d;
+    if (d.batch_normalize && (!scales || !mean || !var)) DNB_FAIL(DNB_EINVAL, "conv params: batch_normalize layer needs scales, rolling_mean, rolling_variance");
+    const int cpg = d.c / d.groups, npg = d.n / d.groups, taps = d.size * d.size;
+    const size_t K = (size_t)cpg * taps;
+
+    // Folded inference batchnorm.  The CPU reference computes
+    // ((x - mean) / (sqrt(var) + 1e-6f)) * scale + bias (src/blas.c:147-158,
+    // src/batchnorm_layer.c:151-154); folded: x*s + (bias - mean*s).
+    std::vector<float> s(p->n_pad, 0.f), b(p->n_pad, 0.f);
+    for (int n = 0; n < d.n; ++n) {
+        if (d.batch_normalize) {
+            const double sc = (double)scales[n] / (sqrt((double)var[n]) + (double).000001f);
+            s[n] = (float)sc;
+            b[n] = (float)((double)biases[n] - (double)mean[n] * sc);
+        } else {
+            s[n] = 1.f;
+            b[n] = biases[n];
+        }
+    }
+    DNB_TRY(upload(&p->scale, s));
+    DNB_TRY(upload(&p->shift, b));
+
+    if (p->kernel == K_TC_TF32) {
+        std::vector<float> w((size_t)taps * p->n_pad * p->c_pad, 0.f);
+        for (int n = 0; n < d.n; ++n)
+            for (int c = 0; c < d.c; ++c)
+                for (int t = 0; t < taps; ++t)
+                    w[((size_t)t * p->n_pad + n) * p->c_pad + c] = tf32_round_host(weights[((size_t)n * d.c + c) * taps + t]);
+        float *dev = (float *)p->w_tc;
+        DNB_TRY(upload(&dev, w));
+        p->w_tc = dev;
+    } else if (p->kernel == K_TC_BF16) {
+        std::vector<uint16_t> w((size_t)taps * p->n_pad * p->c_pad, 0);
+        for (int n = 0; n < d.n; ++n)
+            for (int c = 0; c < d.c; ++c)
+                for (int t = 0; t < taps; ++t)
+                    w[((size_t)t * p->n_pad + n) * p->c_pad + c] = bf16_round_host(weights[((size_t)n * d.c + c) * taps + t]);
+        uint16_t *dev = (uint16_t *)p->w_tc;
+        DNB_TRY(upload(&dev, w));
+        p->w_tc = dev;
+    } else if (p->kernel == K_DIRECT) {
+        std::vector<float> w((size_t)d.groups * K * p->npg_pad, 0.f);
+        for (int g = 0; g < d.groups; ++g)
+            for (int f = 0; f < npg; ++f)
+                for (size_t k = 0; k < K; ++k)
+                    w[((size_t)g * K + k) * p->npg_pad + f] = weights[((size_t)(g * npg + f)) * K + k];
+        DNB_TRY(upload(&p->w_direct, w));
+    } else {
+        // sign bits (w > 0) and the per-filter mean |w|, accumulated in a float in
+        // index order as binarize_weights does (src/convolutional_layer.c:28-41)
+        std::vector<uint32_t> bits((size_t)d.n * taps * p->cwords, 0u);
+        std::vector<float> m(d.n);
+        for (int n = 0; n < d.n; ++n) {
+            float acc = 0.f;
+            for (size_t k = 0; k < K; ++k) acc += fabsf(weights[(size_t)n * K + k]);
+            m[n] = acc / (float)K;
+            for (int c = 0; c < d.c; ++c)
+                for (int t = 0; t < taps; ++t)
+                    if (weights[((size_t)n * d.c + c) * taps + t] > 0.f)
+                        bits[((size_t)n * taps + t) * p->cwords + c / 32] |= 1u << (c % 32);
+        }
+        DNB_TRY(upload(&p->w_bits, bits));
+        DNB_TRY(upload(&p->w_mean, m));
+    }
+    p->params_set = true;
+    return DNB_OK;
+}
+
+// ------------------------------------------------------------------ tensor-core launch block
+static void pick_pixel_tile(const ConvGeom &g, int *wt, int *ht, int *bt)
+{
+    // wt*ht*bt == 128, powers of two; least padded work, then widest rows.
+    double best = 1e300;
+    for (int w = 1; w <= 128; w *= 2)
+        for (int h = 1; w * h <= 128; h *= 2) {
+            const int b = 128 / (w * h);
+            const double work = (double)round_up(g.out_w, w) * round_up(g.out_h, h) * round_up(g.batch, b);
+            const double score = work * (1.0 + 1e-6 * (128 - w) + 1e-7 * (128 - h));
+            if (score < best) { best = score; *wt = w; *ht = h; *bt = b; }
+        }
+}
+
+static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x)
+{
+    TcArgs &a = p->tc;
+    const ConvGeom &g = p->g;
+    const bool bf16 = p->kernel == K_TC_BF16;
+    const int es = bf16 ? 2 : 4;
+    a.is_bf16 = bf16;
+    const int cbytes = p->c_pad * es;
+    a.row_bytes = cbytes >= 128 ? 128 : (cbytes >= 64 ? 64 : 32);
+    a.bk = a.row_bytes / es;
+    a.c_blocks = (p->c_pad + a.bk - 1) / a.bk;
+    a.taps = g.size * g.size;
+    pick_pixel_tile(g, &a.wt, &a.ht, &a.bt);
+    a.tiles_w = (g.out_w + a.wt - 1) / a.wt;
+    a.tiles_h = (g.out_h + a.ht - 1) / a.ht;
+    a.tiles_b = (g.batch + a.bt - 1) / a.bt;
+    const int ptiles = a.tiles_w * a.tiles_h * a.tiles_b;
+    // filters per tile: multiple of 16 <= 256 with the least padded columns, widest on ties
+    int best_bn = 16;
+    long best_cols = 1L << 60;
+    for (int bn = 16; bn <= 256; bn += 16) {
+        long cols = (long)((p->n_pad + bn - 1) / bn) * bn;
+        if (cols <= best_cols) { best_cols = cols; best_bn = bn; }
+    }
+    a.bn = best_bn;
+    a.n_tiles = (p->n_pad + a.bn - 1) / a.bn;
+    while (ptiles * a.n_tiles < sm_count() && a.bn >= 64 && a.bn % 32 == 0) {  // too few tiles to fill the SMs
+        a.bn /= 2;
+        a.n_tiles = (p->n_pad + a.bn - 1) / a.bn;
+    }
+    a.total_tiles = ptiles * a.n_tiles;
+    a.a_bytes = 128 * a.row_bytes;
+    a.b_bytes = round_up(a.bn * a.row_bytes, 1024);
+    const int max_smem = conv_tc_max_smem();
+    if (max_smem <= 0) DNB_FAIL(DNB_ECUDA, "conv: cannot query shared memory of the current device");
+    int stages = (max_smem - 2048) / (a.a_bytes + a.b_bytes);
+    if (stages > 8) stages = 8;
+    if (stages < 2) DNB_FAIL(DNB_ECUDA, "conv: %d bytes of shared memory are too few for the operand ring", max_smem);
+    a.stages = stages;
+    a.g = g;
+    if (!p->status) {
+        DNB_CUDA(cudaMalloc((void **)&p->status, sizeof(int)));
+        DNB_CUDA(cudaMemset(p->status, 0, sizeof(int)));
+    }
+    a.status = p->status;
+
+    // activation maps: lattice (ph, pw) of the input holds rows ph, ph+stride, ... and columns pw, pw+stride, ...
+    const size_t pix_bytes = (size_t)x->cpitch * es;
+    const int s = g.stride;
+    if (s > 2) DNB_FAIL(DNB_EUNSUPPORTED, "conv: stride %d on the tensor-core path (1 and 2 are covered)", s);
+    for (int ph = 0; ph < s; ++ph)
+        for (int pw = 0; pw < s; ++pw) {
+            const int hl = (g.h - ph + s - 1) / s, wl = (g.w - pw + s - 1) / s;
+            uint64_t dims[4] = {(uint64_t)p->c_pad, (uint64_t)(wl > 0 ? wl : 1), (uint64_t)(hl > 0 ? hl : 1), (uint64_t)g.batch};
+            uint64_t strides[3] = {pix_bytes * s, pix_bytes * g.w * s, pix_bytes * g.w * g.h};
+            uint32_t box[4] = {(uint32_t)a.bk, (uint32_t)a.wt, (uint32_t)a.ht, (uint32_t)a.bt};
+            char *base = (char *)x->data + ((size_t)ph * g.w + pw) * pix_bytes;
+            if (hl <= 0 || wl <= 0) base = (char *)x->data;  // lattice empty: never addressed in-bounds
+            DNB_TRY(encode_tensor_map(&a.tmx[ph * s + pw], bf16, 4, base, dims, strides, box, a.row_bytes));
+        }
+    {
+        uint64_t dims[3] = {(uint64_t)p->c_pad, (uint64_t)p->n_pad, (uint64_t)a.taps};
+        uint64_t strides[2] = {(uint64_t)p->c_pad * es, (uint64_t)p->c_pad * es * p->n_pad};
+        uint32_t box[3] = {(uint32_t)a.bk, (uint32_t)a.bn, 1u};
+        DNB_TRY(encode_tensor_map(&a.tmw, bf16, 3, p->w_tc, dims, strides, box, a.row_bytes));
+    }
+    p->tc_x_ptr = x->data;
+    p->tc_x_cpitch = x->cpitch;
+    return DNB_OK;
+}
+
+// ------------------------------------------------------------------ forward
+static int check_conv_io(const dnb_conv_plan *p, const dnb_tensor *x, const dnb_tensor *y, const dnb_tensor *y2)
+{
+    const ConvGeom &g = p->g;
+    DNB_TRY(check_tensor(x, "conv input"));
+    DNB_TRY(check_tensor(y, "conv output"));
+    if (y2) DNB_TRY(check_tensor(y2, "conv second output"));
+    if (x->n != g.batch || x->c != g.c || x->h != g.h || x->w != g.w)
+        DNB_FAIL(DNB_EINVAL, "conv: input is %dx%dx%dx%d, plan expects %dx%dx%dx%d", x->n, x->c, x->h, x->w, g.batch, g.c, g.h, g.w);
+    const dnb_tensor *outs[2] = {y, y2};
+    for (int i = 0; i < 2; ++i) {
+        const dnb_tensor *o = outs[i];
+        if (!o) continue;
+        if (o->n != g.batch || o->c != g.n || o->h != g.out_h || o->w != g.out_w)
+            DNB_FAIL(DNB_EINVAL, "conv: output is %dx%dx%dx%d, plan produces %dx%dx%dx%d", o->n, o->c, o->h, o->w, g.batch, g.n, g.out_h, g.out_w);
+    }
+    if (y2 && y2->layout == y->layout) DNB_FAIL(DNB_EINVAL, "conv: the second output must use the other layout");
+    return DNB_OK;
+}
+
+static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_tensor *y, const dnb_tensor *y2,
+                             int32_t *acc_out, cudaStream_t s)
+{
+    if (!p) DNB_FAIL(DNB_EINVAL, "conv: null plan");
+    if (!p->params_set) DNB_FAIL(DNB_EINVAL, "conv: dnb_conv_plan_set_params has not been called");
+    const ConvGeom &g = p->g;
+    void *y_nhwc = nullptr;
+    float *y_nchw = nullptr;
+    int y_dtype = DNB_F32, y_cpitch = 0;
+    const dnb_tensor *outs[2] = {y, y2};
+    for (int i = 0; i < 2; ++i) {
+        const dnb_tensor *o = outs[i];
+        if (!o) continue;
+        if (o->layout == DNB_NHWC) { y_nhwc = o->data; y_dtype = o->dtype; y_cpitch = o->cpitch; }
+        else y_nchw = (float *)o->data;
+    }
+    ConvEpilogue ep{p->scale, p->shift, p->d.activation, 0};
+    // f32 channels-last results of a TF32 network feed the next tensor-core layer: round them once here
+    ep.round_tf32 = (p->mode == DNB_MODE_TF32 && y_nhwc && y_dtype == DNB_F32 && !y_nchw) ? 1 : 0;
+
+    if (p->kernel == K_DIRECT) {
+        DirectArgs a;
+        a.x = x->data; a.x_dtype = x->dtype;
+        if (x->layout == DNB_NHWC) { a.xs_c = 1; a.xs_w = x->cpitch; a.xs_h = (long long)g.w * x->cpitch; a.xs_b = (long long)g.h * a.xs_h; }
+        else { a.xs_w = 1; a.xs_h = g.w; a.xs_c = (long long)g.h * g.w; a.xs_b = (long long)g.c * a.xs_c; }
+        a.wpk = p->w_direct; a.npg_pad = p->npg_pad;
+        a.y_nhwc = y_nhwc; a.y_dtype = y_dtype; a.y_cpitch = y_cpitch; a.y_nchw = y_nchw;
+        a.g = g; a.ep = ep;
+        return launch_conv_direct(a, s);
+    }
+    if (p->kernel == K_XNOR) {
+        const size_t need = (size_t)g.batch * g.h * g.w * p->cwords * sizeof(uint32_t);
+        if (need > p->x_bits_bytes) {
+            cudaFree(p->x_bits);
+            p->x_bits = nullptr; p->x_bits_bytes = 0;
+            DNB_CUDA(cudaMalloc((void **)&p->x_bits, need));
+            p->x_bits_bytes = need;
+        }
+        DNB_TRY(launch_pack_sign_bits(x, p->x_bits, p->cwords, s));
+        XnorArgs a;
+        a.xbits = p->x_bits; a.wbits = p->w_bits; a.cwords = p->cwords; a.wmean = p->w_mean; a.acc_out = acc_out;
+        a.y_nhwc = y_nhwc; a.y_dtype = y_dtype; a.y_cpitch = y_cpitch; a.y_nchw = y_nchw;
+        a.g = g; a.ep = ep; a.ep.round_tf32 = 0;
+        return launch_conv_xnor(a, s);
+    }
+    // tensor-core path: channels-last input of the plan's storage type
+    const int want = p->kernel == K_TC_BF16 ? DNB_BF16 : DNB_F32;
+    dnb_tensor xin = *x;
+    if (x->layout == DNB_NCHW) {
+        const size_t need = (size_t)g.batch * g.h * g.w * p->c_pad * elem_size(want);
+        if (need > p->x_nhwc_bytes) {
+            cudaFree(p->x_nhwc_scratch);
+            p->x_nhwc_scratch = nullptr; p->x_nhwc_bytes = 0;
+            DNB_CUDA(cudaMalloc(&p->x_nhwc_scratch, need));
+            p->x_nhwc_bytes = need;
+        }
+        xin.data = p->x_nhwc_scratch; xin.layout = DNB_NHWC; xin.dtype = want; xin.cpitch = p->c_pad;
+        DNB_TRY(launch_convert(x, &xin, want == DNB_F32, 0, 0, s));
+    } else if (x->dtype != want) {
+        DNB_FAIL(DNB_EINVAL, "conv: channels-last input is %s, this plan (%s) reads %s", x->dtype == DNB_BF16 ? "bf16" : "f32",
+                 kKernelNames[p->kernel], want == DNB_BF16 ? "bf16" : "f32");
+    }
+    if (p->tc_x_ptr != xin.data || p->tc_x_cpitch != xin.cpitch) DNB_TRY(build_tc_args(p, &xin));
+    TcArgs &a = p->tc;
+    a.y_nhwc = y_nhwc; a.y_dtype = y_dtype; a.y_cpitch = y_cpitch; a.y_nchw = y_nchw;
+    a.ep = ep;
+    return launch_conv_tc(a, s);
+}
+
+extern "C" int dnb_conv_forward(dnb_conv_plan *p, const dnb_tensor *x, const dnb_tensor *y, const dnb_tensor *y2, void *stream)
+{
+    if (!p) DNB_FAIL(DNB_EINVAL, "conv: null plan");
+    DNB_TRY(check_conv_io(p, x, y, y2));
+    return conv_forward_impl(p, x, y, y2, nullptr, (cudaStream_t)stream);
+}
+
+extern "C" int dnb_conv_xnor_accumulate(dnb_conv_plan *p, const dnb_tensor *x, int32_t *acc, void *stream)
+{
+    if (!p || !acc) DNB_FAIL(DNB_EINVAL, "xnor accumulate: null argument");
+    if (p->kernel != K_XNOR) DNB_FAIL(DNB_EINVAL, "xnor accumulate: the plan is not an xnor plan");
+    DNB_TRY(check_tensor(x, "conv input"));
+    const ConvGeom &g = p->g;
+    if (x->n != g.batch || x->c != g.c || x->h != g.h || x->w != g.w) DNB_FAIL(DNB_EINVAL, "xnor accumulate: input extents differ from the plan");
+    return conv_forward_impl(p, x, nullptr, nullptr, acc, (cudaStream_t)stream);
+}
+
+// Device status word of the tensor-core kernel: 0, or the code of the bounded
+// wait that expired (DNB_ETIMEOUT is returned to the caller in that case).
+extern "C" int dnb_conv_plan_check_status(dnb_conv_plan *p)
+{
+    if (!p || !p->status) return DNB_OK;
+    int v = 0;
+    DNB_CUDA(cudaMemcpy(&v, p->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v) {
+        cudaMemset(p->status, 0, sizeof(int));
+        DNB_FAIL(DNB_ETIMEOUT, "conv: a device-side wait expired (code %d: 101 ring slot free, 102 operands landed, 103 accumulator free, 104 accumulator ready)", v);
+    }
+    return DNB_OK;
+}

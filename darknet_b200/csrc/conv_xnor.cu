@@ -1,0 +1,204 @@
+// XNOR convolution as a bit-packed popcount GEMM.
+//
+// The reference binarises weights to +-mean|w| and inputs to +-1 and then runs
+// the ordinary fp32 im2col + GEMM (src/convolutional_layer.c:451-456, :461-475);
+// zero padding is applied after binarisation, so a tap outside the image adds 0.
+// With signs packed 32 per word (bit = value > 0) the integer accumulator is
+//
+//     acc[pixel][n] = sum over in-image taps of ( C - 2 * popc(xbits ^ wbits) )
+//
+// which is exact.  The layer output is act(bn(mean[n] * acc)).
+//
+// Integer / bit work on the CUDA cores: a 64 pixel x 64 filter block tile, each
+// thread a 4 x 4 micro-tile, operands staged through shared memory one tap and
+// up to 32 words at a time; per word pair one LOP3 (xor-and-mask), one POPC, one
+// IADD.  Bounded by the POPC issue rate and, for wide layers, by HBM on the
+// 32x smaller packed operands; not a tensor-core workload.
+#include "common.h"
+#include "conv.h"
+#include "device_utils.cuh"
+
+namespace dnb {
+
+constexpr int XT = 64;      // pixels per block
+constexpr int XN = 64;      // filters per block
+constexpr int XW = 32;      // words per staged chunk
+constexpr int XTHREADS = 256;
+
+__global__ void __launch_bounds__(XTHREADS)
+conv_xnor_kernel(XnorArgs a)
+{
+    __shared__ uint32_t xs[XW][XT + 1];   // [word][pixel]
+    __shared__ uint32_t ws[XW][XN + 1];   // [word][filter]
+    __shared__ uint32_t mask_s[XT];       // all-ones where the tap is inside the image
+    __shared__ int valid_s[XT];           // in-image taps per pixel
+
+    const ConvGeom &g = a.g;
+    const long long npix = (long long)g.batch * g.out_h * g.out_w;
+    const long long pix0 = (long long)blockIdx.x * XT;
+    const int n0 = blockIdx.y * XN;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // tx: filter quad, ty: pixel quad
+    const int taps = g.size * g.size;
+
+    int pop[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pop[i][j] = 0;
+
+    if (threadIdx.x < XT) valid_s[threadIdx.x] = 0;
+
+    for (int tap = 0; tap < taps; ++tap) {
+        const int kh = tap / g.size, kw = tap - kh * g.size;
+        for (int w0 = 0; w0 < a.cwords; w0 += XW) {
+            const int wn = min(XW, a.cwords - w0);
+            __syncthreads();
+            // stage the input words of this tap: thread -> (pixel, word), words fastest for coalescing
+            for (int i = threadIdx.x; i < XT * XW; i += XTHREADS) {
+                const int p = i / XW, w = i % XW;
+                const long long pix = pix0 + p;
+                uint32_t v = 0, inside = 0;
+                if (pix < npix) {
+                    const int ow = (int)(pix % g.out_w);
+                    const long long t = pix / g.out_w;
+                    const int oh = (int)(t % g.out_h), b = (int)(t / g.out_h);
+                    const int ih = oh * g.stride + kh - g.pad, iw = ow * g.stride + kw - g.pad;
+                    if (ih >= 0 && ih < g.h && iw >= 0 && iw < g.w) {
+                        inside = 0xffffffffu;
+                        if (w < wn) v = __ldg(a.xbits + (((size_t)b * g.h + ih) * g.w + iw) * a.cwords + w0 + w);
+                    }
+                }
+                xs[w][p] = v;
+                if (w == 0) {
+                    mask_s[p] = inside;
+                    if (w0 == 0 && inside) valid_s[p] += 1;
+                }
+            }
+            for (int i = threadIdx.x; i < XN * XW; i += XTHREADS) {
+                const int f = i / XW, w = i % XW;
+                const int n = n0 + f;
+                ws[w][f] = (n < g.n && w < wn) ? __ldg(a.wbits + ((size_t)n * taps + tap) * a.cwords + w0 + w) : 0u;
+            }
+            __syncthreads();
+            uint32_t m[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) m[i] = mask_s[ty * 4 + i];
+            for (int w = 0; w < wn; ++w) {
+                uint32_t xv[4], wv[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) xv[i] = xs[w][ty * 4 + i];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) wv[j] = ws[w][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) pop[i][j] += __popc((xv[i] ^ wv[j]) & m[i]);
+            }
+        }
+    }
+    __syncthreads();
+
+    const size_t plane = (size_t)g.out_h * g.out_w;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const long long pix = pix0 + ty * 4 + i;
+        if (pix >= npix) continue;
+        const int ow = (int)(pix % g.out_w);
+        const long long t = pix / g.out_w;
+        const int oh = (int)(t % g.out_h), b = (int)(t / g.out_h);
+        const int base = valid_s[ty * 4 + i] * g.c;
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            const int acc = base - 2 * pop[i][j];
+            v[j] = 0.f;
+            if (n < g.n) {
+                if (a.acc_out) a.acc_out[((size_t)b * g.n + n) * plane + (size_t)oh * g.out_w + ow] = acc;
+                float r = (float)acc * __ldg(a.wmean + n);
+                r = r * __ldg(a.ep.scale + n) + __ldg(a.ep.shift + n);
+                v[j] = activate(r, a.ep.activation);
+                if (a.y_nchw) a.y_nchw[((size_t)b * g.n + n) * plane + (size_t)oh * g.out_w + ow] = v[j];
+            }
+        }
+        const int nq = n0 + tx * 4;
+        if (a.y_nhwc && nq + 4 <= a.y_cpitch) {
+            if (a.y_dtype == DNB_F32) {
+                *reinterpret_cast<float4 *>(reinterpret_cast<float *>(a.y_nhwc) + (size_t)pix * a.y_cpitch + nq) = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
+                __align__(8) __nv_bfloat16 h[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __float2bfloat16_rn(v[j]);
+                *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(a.y_nhwc) + (size_t)pix * a.y_cpitch + nq) = *reinterpret_cast<uint2 *>(h);
+            }
+        }
+    }
+}
+
+int launch_conv_xnor(const XnorArgs &a, cudaStream_t s)
+{
+    const ConvGeom &g = a.g;
+    const long long npix = (long long)g.batch * g.out_h * g.out_w;
+    dim3 grid((unsigned)((npix + XT - 1) / XT), (unsigned)((round_up(g.n, 8) + XN - 1) / XN));
+    conv_xnor_kernel<<<grid, XTHREADS, 0, s>>>(a);
+    DNB_LAUNCH_CHECK("conv_xnor");
+    return DNB_OK;
+}
+
+// ------------------------------------------------------------------ sign-bit packing
+// NHWC: one warp per (pixel, word): lane = channel, one ballot.
+template <typename T>
+__global__ void pack_bits_nhwc_kernel(const T *__restrict__ x, uint32_t *__restrict__ bits, size_t npix, int C, int Cp, int cwords)
+{
+    const int lane = threadIdx.x & 31;
+    const size_t warp0 = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
+    const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    const size_t total = npix * cwords;
+    for (size_t i = warp0; i < total; i += nwarps) {
+        const size_t p = i / cwords;
+        const int w = (int)(i % cwords), c = w * 32 + lane;
+        const float v = c < C ? to_float<T>(x[p * Cp + c]) : 0.f;
+        const uint32_t word = __ballot_sync(0xffffffffu, v > 0.f);
+        if (lane == 0) bits[i] = word;
+    }
+}
+
+// NCHW: one thread per (pixel, word): 32 strided loads, coalesced across the warp.
+__global__ void pack_bits_nchw_kernel(const float *__restrict__ x, uint32_t *__restrict__ bits, int B, int C, size_t HW, int cwords)
+{
+    const size_t total = (size_t)B * HW * cwords;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t hw = i % HW;
+        const size_t t = i / HW;
+        const int w = (int)(t % cwords), b = (int)(t / cwords);
+        uint32_t word = 0;
+        for (int k = 0; k < 32; ++k) {
+            const int c = w * 32 + k;
+            if (c < C && __ldg(x + ((size_t)b * C + c) * HW + hw) > 0.f) word |= 1u << k;
+        }
+        bits[((size_t)b * HW + hw) * cwords + w] = word;
+    }
+}
+
+int launch_pack_sign_bits(const dnb_tensor *x, uint32_t *bits, int cwords, cudaStream_t s)
+{
+    const size_t npix = (size_t)x->n * x->h * x->w;
+    if (x->layout == DNB_NHWC) {
+        size_t warps = npix * cwords;
+        size_t blocks = (warps * 32 + 255) / 256;
+        size_t cap = (size_t)sm_count() * 8;
+        int grid = (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
+        if (x->dtype == DNB_F32) pack_bits_nhwc_kernel<float><<<grid, 256, 0, s>>>((const float *)x->data, bits, npix, x->c, x->cpitch, cwords);
+        else pack_bits_nhwc_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16 *)x->data, bits, npix, x->c, x->cpitch, cwords);
+    } else {
+        size_t total = npix * cwords;
+        size_t blocks = (total + 255) / 256;
+        size_t cap = (size_t)sm_count() * 8;
+        int grid = (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
+        pack_bits_nchw_kernel<<<grid, 256, 0, s>>>((const float *)x->data, bits, x->n, x->c, (size_t)x->h * x->w, cwords);
+    }
+    DNB_LAUNCH_CHECK("pack_sign_bits");
+    return DNB_OK;
+}
+
+}  // namespace dnb

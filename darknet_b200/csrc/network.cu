@@ -1,0 +1,521 @@
+// The network object: cfg parsing, weights loading and the forward loop for the
+// layer types on the convolutional forward path.  Mirrors the reference's
+// parse_network_cfg (src/parser.c:742-889), load_weights (src/parser.c:1218-1308),
+// forward_network_gpu (src/network.c:762-788) and network_predict
+// (src/network.c:497-508), with activations kept channels-last between layers.
+#include <stdlib.h>
+#include <string.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "common.h"
+#include "conv.h"
+
+using namespace dnb;
+
+namespace {
+
+enum LayerKind { L_CONV, L_MAXPOOL, L_UPSAMPLE, L_SHORTCUT, L_ROUTE, L_YOLO, L_AVGPOOL, L_SOFTMAX };
+const char *const kKindNames[] = {"convolutional", "maxpool", "upsample", "shortcut", "route", "yolo", "avgpool", "softmax"};
+
+struct Layer {
+    LayerKind kind;
+    int c, h, w;                   // input extents
+    int out_c, out_h, out_w;
+    dnb_tensor out;                // device output: NHWC in the network's storage type (yolo: NCHW f32)
+    // convolutional
+    dnb_conv_desc cd;
+    dnb_conv_plan *plan = nullptr;
+    // maxpool / upsample
+    int size = 0, stride = 0, padding = 0;
+    float scale = 1.f;
+    // shortcut / route
+    int from = -1;
+    float alpha = 1.f, beta = 1.f;
+    int activation = DNB_LINEAR;
+    std::vector<int> inputs;
+    // yolo
+    int anchors = 0, classes = 0;
+    float *host_out = nullptr;     // pinned
+    // softmax
+    int groups = 1;
+    float temperature = 1.f;
+    int launches = 1;
+};
+
+typedef std::map<std::string, std::string> Options;
+
+int opt_int(const Options &o, const char *k, int def)
+{
+    auto it = o.find(k);
+    return it == o.end() ? def : atoi(it->second.c_str());
+}
+float opt_float(const Options &o, const char *k, float def)
+{
+    auto it = o.find(k);
+    return it == o.end() ? def : (float)atof(it->second.c_str());
+}
+std::string opt_str(const Options &o, const char *k, const char *def)
+{
+    auto it = o.find(k);
+    return it == o.end() ? std::string(def) : it->second;
+}
+
+// get_activation (src/activations.c:46-63): unknown names fall back to RELU there; here they are rejected.
+int parse_activation(const std::string &s)
+{
+    static const char *const names[] = {"logistic", "relu", "relie", "linear", "ramp", "tanh", "plse",
+                                        "leaky", "elu", "loggy", "stair", "hardtan", "lhtan", "selu"};
+    for (int i = 0; i < 14; ++i)
+        if (s == names[i]) return i;
+    return -1;
+}
+
+std::string trim(const std::string &s)
+{
+    size_t a = s.find_first_not_of(" \t\r\n"), b = s.find_last_not_of(" \t\r\n");
+    return a == std::string::npos ? std::string() : s.substr(a, b - a + 1);
+}
+
+// read_cfg (src/parser.c:891-924): '[' opens a section, '#' ';' and blank lines are skipped, the rest is key=value.
+int split_cfg(const char *text, std::vector<std::pair<std::string, Options>> *sections)
+{
+    const char *p = text;
+    int lineno = 0;
+    while (*p) {
+        const char *e = strchr(p, '\n');
+        std::string line = trim(e ? std::string(p, e - p) : std::string(p));
+        p = e ? e + 1 : p + strlen(p);
+        ++lineno;
+        if (line.empty() || line[0] == '#' || line[0] == ';') continue;
+        if (line[0] == '[') {
+            size_t r = line.find(']');
+            if (r == std::string::npos) DNB_FAIL(DNB_EINVAL, "cfg line %d: unterminated section header", lineno);
+            sections->push_back({trim(line.substr(1, r - 1)), Options()});
+            continue;
+        }
+        size_t eq = line.find('=');
+        if (eq == std::string::npos || sections->empty()) DNB_FAIL(DNB_EINVAL, "cfg line %d: expected key=value inside a section", lineno);
+        sections->back().second[trim(line.substr(0, eq))] = trim(line.substr(eq + 1));
+    }
+    if (sections->empty()) DNB_FAIL(DNB_EINVAL, "cfg has no sections");
+    return DNB_OK;
+}
+
+}  // namespace
+
+struct dnb_network {
+    int mode = DNB_MODE_TF32;
+    int dtype = DNB_F32;             // storage type between layers
+    int batch = 0, h = 0, w = 0, c = 0, inputs = 0, outputs = 0;
+    std::vector<Layer> layers;
+    float *input_dev = nullptr;      // NCHW f32 [batch][inputs]
+    dnb_tensor input_nhwc{};         // only when the first layer needs channels-last input
+    float *out_dev_nchw = nullptr;   // NCHW f32 staging of the output layer when it is not a yolo layer
+    float *out_host = nullptr;       // pinned [batch][outputs]
+    float *export_dev = nullptr;     // scratch for dnb_network_layer_output
+    size_t export_elems = 0;
+    cudaStream_t stream = nullptr;
+    int device = 0;
+    bool weights_loaded = false;
+    std::vector<cudaEvent_t> events;
+};
+
+static int alloc_activation(dnb_network *net, dnb_tensor *t, int c, int h, int w)
+{
+    t->layout = DNB_NHWC;
+    t->dtype = net->dtype;
+    t->n = net->batch; t->c = c; t->h = h; t->w = w;
+    t->cpitch = round_up(c, 8);
+    const size_t bytes = tensor_elems(t) * elem_size(t->dtype);
+    DNB_CUDA(cudaMalloc(&t->data, bytes));
+    DNB_CUDA(cudaMemset(t->data, 0, bytes));  // the cpitch - c padding channels stay zero for the lifetime of the network
+    return DNB_OK;
+}
+
+static int build_network(const char *text, int mode, int batch_override, dnb_network **out)
+{
+    if (!text || !out) DNB_FAIL(DNB_EINVAL, "parse_network_cfg: null argument");
+    *out = nullptr;
+    if (mode != DNB_MODE_TF32 && mode != DNB_MODE_BF16 && mode != DNB_MODE_FP32) DNB_FAIL(DNB_EINVAL, "parse_network_cfg: mode %d", mode);
+    std::vector<std::pair<std::string, Options>> sections;
+    DNB_TRY(split_cfg(text, &sections));
+    if (sections[0].first != "net" && sections[0].first != "network") DNB_FAIL(DNB_EINVAL, "cfg: first section must be [net] or [network]");
+
+    dnb_network *net = new dnb_network();
+    struct Guard { dnb_network *n; ~Guard() { if (n) dnb_free_network(n); } } guard{net};
+    net->mode = mode;
+    net->dtype = mode == DNB_MODE_BF16 ? DNB_BF16 : DNB_F32;
+    DNB_CUDA(cudaGetDevice(&net->device));
+    const Options &no = sections[0].second;
+    // parse_net_options (src/parser.c:655-734): batch /= subdivisions
+    int subdivs = opt_int(no, "subdivisions", 1);
+    if (subdivs < 1) subdivs = 1;
+    net->batch = batch_override > 0 ? batch_override : opt_int(no, "batch", 1) / subdivs;
+    net->h = opt_int(no, "height", 0); net->w = opt_int(no, "width", 0); net->c = opt_int(no, "channels", 0);
+    if (net->batch < 1 || net->h < 1 || net->w < 1 || net->c < 1)
+        DNB_FAIL(DNB_EINVAL, "cfg [net]: need positive batch, height, width, channels (got %d, %d, %d, %d)", net->batch, net->h, net->w, net->c);
+    net->inputs = net->h * net->w * net->c;
+
+    int c = net->c, h = net->h, w = net->w;
+    for (size_t si = 1; si < sections.size(); ++si) {
+        const std::string &type = sections[si].first;
+        const Options &o = sections[si].second;
+        const int index = (int)si - 1;
+        Layer L;
+        L.c = c; L.h = h; L.w = w;
+        if (type == "convolutional" || type == "conv") {
+            L.kind = L_CONV;
+            const int size = opt_int(o, "size", 1);
+            int padding = opt_int(o, "padding", 0);
+            if (opt_int(o, "pad", 0)) padding = size / 2;  // src/parser.c:184-187
+            const int act = parse_activation(opt_str(o, "activation", "logistic"));
+            if (act < 0) DNB_FAIL(DNB_EINVAL, "cfg layer %d: unknown activation '%s'", index, opt_str(o, "activation", "").c_str());
+            L.cd = dnb_conv_desc{net->batch, h, w, c, opt_int(o, "filters", 1), opt_int(o, "groups", 1), size,
+                                 opt_int(o, "stride", 1), padding, opt_int(o, "batch_normalize", 0), act, opt_int(o, "xnor", 0)};
+            if (opt_int(o, "flipped", 0)) DNB_FAIL(DNB_EUNSUPPORTED, "cfg layer %d: flipped weights are not on this path", index);
+            DNB_TRY(dnb_conv_plan_create(&L.cd, mode, &L.plan));
+            L.out_c = L.cd.n; L.out_h = L.plan->g.out_h; L.out_w = L.plan->g.out_w;
+            L.launches = L.plan->kernel == 3 ? 2 : 1;
+        } else if (type == "maxpool" || type == "max") {
+            L.kind = L_MAXPOOL;
+            L.stride = opt_int(o, "stride", 1);
+            L.size = opt_int(o, "size", L.stride);
+            L.padding = opt_int(o, "padding", L.size - 1);  // src/parser.c:485-487
+            if (L.stride < 1 || L.size < 1) DNB_FAIL(DNB_EINVAL, "cfg layer %d: maxpool size %d stride %d", index, L.size, L.stride);
+            L.out_c = c; L.out_h = (h + L.padding - L.size) / L.stride + 1; L.out_w = (w + L.padding - L.size) / L.stride + 1;
+        } else if (type == "upsample") {
+            L.kind = L_UPSAMPLE;
+            L.stride = opt_int(o, "stride", 2);
+            L.scale = opt_float(o, "scale", 1.f);
+            if (L.stride < 1) DNB_FAIL(DNB_EUNSUPPORTED, "cfg layer %d: upsample stride %d (reverse form)", index, L.stride);
+            L.out_c = c; L.out_h = h * L.stride; L.out_w = w * L.stride;
+        } else if (type == "shortcut") {
+            L.kind = L_SHORTCUT;
+            int from = opt_int(o, "from", 0);
+            if (o.find("from") == o.end()) DNB_FAIL(DNB_EINVAL, "cfg layer %d: shortcut without from=", index);
+            if (from < 0) from = index + from;
+            if (from < 0 || from >= index) DNB_FAIL(DNB_EINVAL, "cfg layer %d: shortcut from=%d out of range", index, from);
+            L.from = from;
+            L.activation = parse_activation(opt_str(o, "activation", "linear"));
+            if (L.activation < 0) DNB_FAIL(DNB_EINVAL, "cfg layer %d: unknown activation", index);
+            L.alpha = opt_float(o, "alpha", 1.f); L.beta = opt_float(o, "beta", 1.f);
+            L.out_c = c; L.out_h = h; L.out_w = w;
+        } else if (type == "route") {
+            L.kind = L_ROUTE;
+            std::string ls = opt_str(o, "layers", "");
+            if (ls.empty()) DNB_FAIL(DNB_EINVAL, "cfg layer %d: route must specify input layers", index);
+            size_t pos = 0;
+            int csum = 0;
+            while (pos <= ls.size()) {
+                size_t comma = ls.find(',', pos);
+                int id = atoi(ls.substr(pos, comma == std::string::npos ? std::string::npos : comma - pos).c_str());
+                if (id < 0) id = index + id;
+                if (id < 0 || id >= index) DNB_FAIL(DNB_EINVAL, "cfg layer %d: route input %d out of range", index, id);
+                L.inputs.push_back(id);
+                csum += net->layers[id].out_c;
+                if (comma == std::string::npos) break;
+                pos = comma + 1;
+            }
+            const Layer &first = net->layers[L.inputs[0]];
+            for (int id : L.inputs)
+                if (net->layers[id].out_h != first.out_h || net->layers[id].out_w != first.out_w)
+                    DNB_FAIL(DNB_EUNSUPPORTED, "cfg layer %d: route inputs of unequal width/height", index);
+            L.out_c = csum; L.out_h = first.out_h; L.out_w = first.out_w;
+            L.launches = (int)L.inputs.size();
+        } else if (type == "yolo") {
+            L.kind = L_YOLO;
+            // parse_yolo (src/parser.c:306-345): n = number of mask entries (or num), classes default 20
+            const std::string mask = opt_str(o, "mask", "");
+            int n = opt_int(o, "num", 1);
+            if (!mask.empty()) { n = 1; for (char ch : mask) if (ch == ',') ++n; }
+            L.anchors = n; L.classes = opt_int(o, "classes", 20);
+            if (c != n * (L.classes + 5)) DNB_FAIL(DNB_EINVAL, "cfg layer %d: yolo expects %d channels, input has %d", index, n * (L.classes + 5), c);
+            L.out_c = c; L.out_h = h; L.out_w = w;
+        } else if (type == "avgpool" || type == "avg") {
+            L.kind = L_AVGPOOL;
+            L.out_c = c; L.out_h = 1; L.out_w = 1;
+        } else if (type == "softmax" || type == "soft") {
+            L.kind = L_SOFTMAX;
+            L.groups = opt_int(o, "groups", 1);
+            L.temperature = opt_float(o, "temperature", 1.f);
+            if (o.find("tree") != o.end()) DNB_FAIL(DNB_EUNSUPPORTED, "cfg layer %d: softmax tree", index);
+            if (h != 1 || w != 1) DNB_FAIL(DNB_EUNSUPPORTED, "cfg layer %d: softmax over a %dx%d map", index, w, h);
+            L.out_c = c; L.out_h = 1; L.out_w = 1;
+        } else {
+            DNB_FAIL(DNB_EUNSUPPORTED, "cfg layer %d: section [%s] is outside the convolutional forward path", index, type.c_str());
+        }
+        if (L.out_h < 1 || L.out_w < 1) DNB_FAIL(DNB_EINVAL, "cfg layer %d: empty output", index);
+        // the previous layer's output must be channels-last for every consumer but none reads a yolo output
+        if (index > 0 && net->layers[index - 1].kind == L_YOLO && L.kind != L_ROUTE)
+            DNB_FAIL(DNB_EUNSUPPORTED, "cfg layer %d: a [%s] directly after [yolo]", index, type.c_str());
+        if (L.kind == L_YOLO) {
+            L.out = dnb_tensor{nullptr, DNB_NCHW, DNB_F32, net->batch, L.out_c, L.out_h, L.out_w, 0};
+            const size_t bytes = tensor_elems(&L.out) * sizeof(float);
+            DNB_CUDA(cudaMalloc(&L.out.data, bytes));
+            DNB_CUDA(cudaMallocHost((void **)&L.host_out, bytes));
+        } else {
+            DNB_TRY(alloc_activation(net, &L.out, L.out_c, L.out_h, L.out_w));
+        }
+        net->layers.push_back(L);
+        c = L.out_c; h = L.out_h; w = L.out_w;
+    }
+    if (net->layers.empty()) DNB_FAIL(DNB_EINVAL, "cfg has no layers");
+    for (const Layer &L : net->layers) {
+        if (L.kind == L_SHORTCUT && net->layers[L.from].kind == L_YOLO) DNB_FAIL(DNB_EUNSUPPORTED, "cfg: shortcut from a [yolo] layer");
+        if (L.kind == L_ROUTE)
+            for (int id : L.inputs)
+                if (net->layers[id].kind == L_YOLO) DNB_FAIL(DNB_EUNSUPPORTED, "cfg: route from a [yolo] layer");
+    }
+    const Layer &last = net->layers.back();
+    net->outputs = last.out_c * last.out_h * last.out_w;
+    DNB_CUDA(cudaMalloc((void **)&net->input_dev, (size_t)net->batch * net->inputs * sizeof(float)));
+    DNB_CUDA(cudaMallocHost((void **)&net->out_host, (size_t)net->batch * net->outputs * sizeof(float)));
+    if (last.kind != L_YOLO) DNB_CUDA(cudaMalloc((void **)&net->out_dev_nchw, (size_t)net->batch * net->outputs * sizeof(float)));
+    const Layer &first = net->layers.front();
+    const bool first_reads_nchw = first.kind == L_CONV && (first.plan->kernel == 2 || first.plan->kernel == 3);
+    if (!first_reads_nchw) {
+        dnb_tensor *t = &net->input_nhwc;
+        DNB_TRY(alloc_activation(net, t, net->c, net->h, net->w));
+    }
+    DNB_CUDA(cudaStreamCreateWithFlags(&net->stream, cudaStreamNonBlocking));
+    guard.n = nullptr;
+    *out = net;
+    return DNB_OK;
+}
+
+extern "C" int dnb_parse_network_cfg_text(const char *cfg_text, int mode, int batch_override, dnb_network **net)
+{
+    return build_network(cfg_text, mode, batch_override, net);
+}
+
+extern "C" int dnb_parse_network_cfg(const char *path, int mode, int batch_override, dnb_network **net)
+{
+    if (!path) DNB_FAIL(DNB_EINVAL, "parse_network_cfg: null path");
+    FILE *f = fopen(path, "rb");
+    if (!f) DNB_FAIL(DNB_EIO, "Couldn't open file: %s", path);  // file_error, src/utils.c:281-285
+    std::string text;
+    char buf[4096];
+    size_t n;
+    while ((n = fread(buf, 1, sizeof(buf), f)) > 0) text.append(buf, n);
+    fclose(f);
+    return build_network(text.c_str(), mode, batch_override, net);
+}
+
+extern "C" void dnb_free_network(dnb_network *net)
+{
+    if (!net) return;
+    for (Layer &L : net->layers) {
+        if (L.plan) dnb_conv_plan_destroy(L.plan);
+        cudaFree(L.out.data);
+        if (L.host_out) cudaFreeHost(L.host_out);
+    }
+    cudaFree(net->input_dev); cudaFree(net->input_nhwc.data); cudaFree(net->out_dev_nchw); cudaFree(net->export_dev);
+    if (net->out_host) cudaFreeHost(net->out_host);
+    for (cudaEvent_t e : net->events) cudaEventDestroy(e);
+    if (net->stream) cudaStreamDestroy(net->stream);
+    delete net;
+}
+
+extern "C" int dnb_load_weights(dnb_network *net, const char *path)
+{
+    if (!net || !path) DNB_FAIL(DNB_EINVAL, "load_weights: null argument");
+    FILE *f = fopen(path, "rb");
+    if (!f) DNB_FAIL(DNB_EIO, "Couldn't open file: %s", path);
+    struct Closer { FILE *f; ~Closer() { fclose(f); } } closer{f};
+    int hdr[3];
+    if (fread(hdr, sizeof(int), 3, f) != 3) DNB_FAIL(DNB_EIO, "%s: truncated header", path);
+    // src/parser.c:1234-1241: a 64-bit `seen` from version 0.2 on, a 32-bit one before
+    if ((hdr[0] * 10 + hdr[1]) >= 2 && hdr[0] < 1000 && hdr[1] < 1000) {
+        uint64_t seen;
+        if (fread(&seen, sizeof(seen), 1, f) != 1) DNB_FAIL(DNB_EIO, "%s: truncated header", path);
+    } else {
+        int seen;
+        if (fread(&seen, sizeof(seen), 1, f) != 1) DNB_FAIL(DNB_EIO, "%s: truncated header", path);
+    }
+    if (hdr[0] > 1000 || hdr[1] > 1000) DNB_FAIL(DNB_EUNSUPPORTED, "%s: transposed-weights file versions are not on this path", path);
+    int index = 0;
+    for (Layer &L : net->layers) {
+        if (L.kind == L_CONV) {
+            const dnb_conv_desc &d = L.cd;
+            const size_t nw = (size_t)d.n * (d.c / d.groups) * d.size * d.size;
+            std::vector<float> biases(d.n), scales, mean, var, weights(nw);
+            bool ok = fread(biases.data(), sizeof(float), d.n, f) == (size_t)d.n;
+            if (ok && d.batch_normalize) {
+                scales.resize(d.n); mean.resize(d.n); var.resize(d.n);
+                ok = fread(scales.data(), sizeof(float), d.n, f) == (size_t)d.n &&
+                     fread(mean.data(), sizeof(float), d.n, f) == (size_t)d.n &&
+                     fread(var.data(), sizeof(float), d.n, f) == (size_t)d.n;
+            }
+            ok = ok && fread(weights.data(), sizeof(float), nw, f) == nw;
+            if (!ok) DNB_FAIL(DNB_EIO, "%s: file ends inside layer %d (the reference would silently keep its random initialisation)", path, index);
+            DNB_TRY(dnb_conv_plan_set_params(L.plan, weights.data(), biases.data(), d.batch_normalize ? scales.data() : nullptr,
+                                             d.batch_normalize ? mean.data() : nullptr, d.batch_normalize ? var.data() : nullptr));
+        }
+        ++index;
+    }
+    net->weights_loaded = true;
+    return DNB_OK;
+}
+
+// One layer of forward_network_gpu's loop (src/network.c:772-785).
+static int forward_layer(dnb_network *net, int i, const float *device_input, cudaStream_t s)
+{
+    Layer &L = net->layers[i];
+    dnb_tensor in;
+    if (i == 0) {
+        in = dnb_tensor{(void *)device_input, DNB_NCHW, DNB_F32, net->batch, net->c, net->h, net->w, 0};
+        if (net->input_nhwc.data) {
+            DNB_TRY(launch_convert(&in, &net->input_nhwc, net->mode == DNB_MODE_TF32, 0, 0, s));
+            in = net->input_nhwc;
+        }
+    } else {
+        in = net->layers[i - 1].out;
+    }
+    switch (L.kind) {
+    case L_CONV: return dnb_conv_forward(L.plan, &in, &L.out, nullptr, s);
+    case L_MAXPOOL: return launch_maxpool(&in, &L.out, L.size, L.stride, L.padding, s);
+    case L_UPSAMPLE: return launch_upsample(&in, &L.out, L.stride, L.scale, s);
+    case L_SHORTCUT: return launch_shortcut(&in, &net->layers[L.from].out, &L.out, L.alpha, L.beta, L.activation, s);
+    case L_ROUTE: {
+        std::vector<const dnb_tensor *> ins;
+        for (int id : L.inputs) ins.push_back(&net->layers[id].out);
+        return launch_route(ins.data(), (int)ins.size(), &L.out, s);
+    }
+    case L_YOLO: return launch_convert(&in, &L.out, 0, L.anchors, L.classes, s);
+    case L_AVGPOOL: return launch_avgpool(&in, &L.out, s);
+    case L_SOFTMAX: return launch_softmax(&in, &L.out, L.groups, L.temperature, s);
+    }
+    return DNB_OK;
+}
+
+extern "C" int dnb_network_forward(dnb_network *net, const float *device_input, void *stream)
+{
+    if (!net || !device_input) DNB_FAIL(DNB_EINVAL, "network_forward: null argument");
+    if (!net->weights_loaded) DNB_FAIL(DNB_EINVAL, "network_forward: load_weights has not been called");
+    cudaStream_t s = stream ? (cudaStream_t)stream : net->stream;
+    for (int i = 0; i < (int)net->layers.size(); ++i) DNB_TRY(forward_layer(net, i, device_input, s));
+    return DNB_OK;
+}
+
+extern "C" int dnb_conv_plan_check_status(dnb_conv_plan *p);
+
+extern "C" int dnb_network_predict(dnb_network *net, const float *input, float **output)
+{
+    if (!net || !input || !output) DNB_FAIL(DNB_EINVAL, "network_predict: null argument");
+    cudaStream_t s = net->stream;
+    DNB_CUDA(cudaMemcpyAsync(net->input_dev, input, (size_t)net->batch * net->inputs * sizeof(float), cudaMemcpyHostToDevice, s));
+    DNB_TRY(dnb_network_forward(net, net->input_dev, s));
+    // yolo layers pull their own output (src/yolo_layer.c:360); the output layer is pulled last (src/network.c:786)
+    for (Layer &L : net->layers)
+        if (L.kind == L_YOLO)
+            DNB_CUDA(cudaMemcpyAsync(L.host_out, L.out.data, tensor_elems(&L.out) * sizeof(float), cudaMemcpyDeviceToHost, s));
+    Layer &last = net->layers.back();
+    if (last.kind != L_YOLO) {
+        dnb_tensor o{net->out_dev_nchw, DNB_NCHW, DNB_F32, net->batch, last.out_c, last.out_h, last.out_w, 0};
+        DNB_TRY(launch_convert(&last.out, &o, 0, 0, 0, s));
+        DNB_CUDA(cudaMemcpyAsync(net->out_host, net->out_dev_nchw, (size_t)net->batch * net->outputs * sizeof(float), cudaMemcpyDeviceToHost, s));
+    }
+    DNB_CUDA(cudaStreamSynchronize(s));
+    for (Layer &L : net->layers)
+        if (L.plan) DNB_TRY(dnb_conv_plan_check_status(L.plan));
+    *output = last.kind == L_YOLO ? last.host_out : net->out_host;
+    return DNB_OK;
+}
+
+extern "C" int dnb_network_num_layers(const dnb_network *net) { return net ? (int)net->layers.size() : 0; }
+extern "C" int dnb_network_batch(const dnb_network *net) { return net ? net->batch : 0; }
+extern "C" int dnb_network_inputs(const dnb_network *net) { return net ? net->inputs : 0; }
+extern "C" int dnb_network_outputs(const dnb_network *net) { return net ? net->outputs : 0; }
+
+extern "C" int dnb_network_layer_shape(const dnb_network *net, int i, int *c, int *h, int *w)
+{
+    if (!net || i < 0 || i >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "layer index %d out of range", i);
+    if (c) *c = net->layers[i].out_c;
+    if (h) *h = net->layers[i].out_h;
+    if (w) *w = net->layers[i].out_w;
+    return DNB_OK;
+}
+extern "C" const char *dnb_network_layer_type(const dnb_network *net, int i)
+{
+    return (!net || i < 0 || i >= (int)net->layers.size()) ? "" : kKindNames[net->layers[i].kind];
+}
+extern "C" const char *dnb_network_layer_kernel(const dnb_network *net, int i)
+{
+    if (!net || i < 0 || i >= (int)net->layers.size()) return "";
+    const Layer &L = net->layers[i];
+    return L.plan ? dnb_conv_plan_kernel(L.plan) : kKindNames[L.kind];
+}
+
+extern "C" int dnb_network_layer_output(dnb_network *net, int i, float *host_out)
+{
+    if (!net || !host_out || i < 0 || i >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "layer_output: bad argument");
+    Layer &L = net->layers[i];
+    const size_t elems = (size_t)net->batch * L.out_c * L.out_h * L.out_w;
+    DNB_CUDA(cudaStreamSynchronize(net->stream));
+    if (L.out.layout == DNB_NCHW) {
+        DNB_CUDA(cudaMemcpy(host_out, L.out.data, elems * sizeof(float), cudaMemcpyDeviceToHost));
+        return DNB_OK;
+    }
+    if (elems > net->export_elems) {
+        cudaFree(net->export_dev);
+        net->export_dev = nullptr; net->export_elems = 0;
+        DNB_CUDA(cudaMalloc((void **)&net->export_dev, elems * sizeof(float)));
+        net->export_elems = elems;
+    }
+    dnb_tensor o{net->export_dev, DNB_NCHW, DNB_F32, net->batch, L.out_c, L.out_h, L.out_w, 0};
+    DNB_TRY(launch_convert(&L.out, &o, 0, 0, 0, net->stream));
+    DNB_CUDA(cudaStreamSynchronize(net->stream));
+    DNB_CUDA(cudaMemcpy(host_out, net->export_dev, elems * sizeof(float), cudaMemcpyDeviceToHost));
+    return DNB_OK;
+}
+
+extern "C" int dnb_network_yolo_output(dnb_network *net, int i, const float **host_out)
+{
+    if (!net || !host_out || i < 0 || i >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "yolo_output: bad argument");
+    if (net->layers[i].kind != L_YOLO) DNB_FAIL(DNB_EINVAL, "layer %d is not a [yolo] layer", i);
+    *host_out = net->layers[i].host_out;
+    return DNB_OK;
+}
+
+// numops (examples/darknet.c:81-114): 2 * n * size^2 * c/groups * out_h * out_w per convolution and image.
+extern "C" double dnb_network_flops(const dnb_network *net)
+{
+    double ops = 0;
+    if (!net) return 0;
+    for (const Layer &L : net->layers)
+        if (L.kind == L_CONV)
+            ops += 2.0 * L.cd.n * L.cd.size * L.cd.size * (L.cd.c / L.cd.groups) * L.out_h * L.out_w;
+    return ops * net->batch;
+}
+
+extern "C" int dnb_network_launches(const dnb_network *net)
+{
+    int n = 0;
+    if (!net) return 0;
+    for (const Layer &L : net->layers) n += L.launches;
+    if (net->input_nhwc.data) n += 1;
+    return n;
+}
+
+extern "C" int dnb_network_profile(dnb_network *net, const float *device_input, float *layer_ms)
+{
+    if (!net || !device_input || !layer_ms) DNB_FAIL(DNB_EINVAL, "network_profile: null argument");
+    const int n = (int)net->layers.size();
+    while ((int)net->events.size() < n + 1) {
+        cudaEvent_t e;
+        DNB_CUDA(cudaEventCreate(&e));
+        net->events.push_back(e);
+    }
+    cudaStream_t s = net->stream;
+    for (int i = 0; i < n; ++i) {
+        DNB_CUDA(cudaEventRecord(net->events[i], s));
+        DNB_TRY(forward_layer(net, i, device_input, s));
+    }
+    DNB_CUDA(cudaEventRecord(net->events[n], s));
+    DNB_CUDA(cudaStreamSynchronize(s));
+    for (int i = 0; i < n; ++i) DNB_CUDA(cudaEventElapsedTime(&layer_ms[i], net->events[i], net->events[i + 1]));
+    return DNB_OK;
+}

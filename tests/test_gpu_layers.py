@@ -1,0 +1,383 @@
+"""Per-layer parity on the GPU: every kernel, called through the C ABI on device
+buffers, against the CPU checker (oracle/) on identical seeded inputs.
+
+Tolerances (max |gpu - cpu| / max |cpu| per layer output):
+  integer / copy / compare kernels (maxpool, upsample, route, layout, xnor
+  accumulators): bit-exact;
+  fp32 CUDA-core kernels: 2e-6 (fused multiply-add and fp32 vs double constants);
+  TF32 tensor-core convolution: 1e-2;  BF16: 3e-2.
+"""
+import numpy as np
+import pytest
+import torch
+
+import darknet_b200 as dn
+from conftest import rel_to_max
+from gpu_util import bf16_round, dev_nchw, dev_nhwc, empty_nchw, empty_nhwc, host_from_nhwc, padding_is_zero
+from oracle import network as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL_FP32 = 2e-6
+TOL_TF32 = 1e-2
+TOL_BF16 = 3e-2
+
+
+def rng(seed):
+    return np.random.Generator(np.random.Philox(key=[seed, 77]))
+
+
+# ------------------------------------------------------------------ memory-bound layers
+@pytest.mark.parametrize("shape,size,stride,padding", [
+    ((2, 16, 16, 16), 2, 2, 1), ((2, 24, 13, 13), 2, 1, 1), ((1, 8, 15, 17), 3, 2, 2),
+    ((3, 40, 7, 9), 2, 2, 1), ((1, 64, 112, 112), 2, 2, 1), ((2, 5, 9, 9), 3, 1, 2)])
+@pytest.mark.parametrize("layout", ["nhwc", "nchw", "nhwc_bf16"])
+def test_maxpool(shape, size, stride, padding, layout):
+    x = rng(1).standard_normal(shape, dtype=np.float32)
+    if layout == "nhwc_bf16":
+        x = bf16_round(x)
+    want = orc.maxpool_forward(x, size, stride, padding)
+    n, c, oh, ow = want.shape
+    if layout == "nchw":
+        xt, xd = dev_nchw(x)
+        yt, yd = empty_nchw(n, c, oh, ow)
+        dn.maxpool(xd, yd, size, stride, padding)
+        got = yt.cpu().numpy()
+    else:
+        dt = torch.bfloat16 if layout == "nhwc_bf16" else torch.float32
+        xt, xd = dev_nhwc(x, dt)
+        yt, yd = empty_nhwc(n, c, oh, ow, dt)
+        dn.maxpool(xd, yd, size, stride, padding)
+        got = host_from_nhwc(yt, c)
+        assert padding_is_zero(yt, c)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("shape,stride", [((2, 128, 13, 13), 2), ((1, 256, 19, 19), 2), ((2, 12, 5, 7), 3)])
+@pytest.mark.parametrize("layout", ["nhwc", "nchw", "nhwc_bf16"])
+def test_upsample(shape, stride, layout):
+    x = rng(2).standard_normal(shape, dtype=np.float32)
+    if layout == "nhwc_bf16":
+        x = bf16_round(x)
+    want = orc.upsample_forward(x, stride)
+    n, c, oh, ow = want.shape
+    if layout == "nchw":
+        xt, xd = dev_nchw(x)
+        yt, yd = empty_nchw(n, c, oh, ow)
+        dn.upsample(xd, yd, stride)
+        got = yt.cpu().numpy()
+    else:
+        dt = torch.bfloat16 if layout == "nhwc_bf16" else torch.float32
+        xt, xd = dev_nhwc(x, dt)
+        yt, yd = empty_nhwc(n, c, oh, ow, dt)
+        dn.upsample(xd, yd, stride)
+        got = host_from_nhwc(yt, c)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("xs,adds,act", [
+    ((2, 64, 19, 19), (2, 64, 19, 19), "linear"),     # YOLOv3 residual
+    ((2, 256, 14, 14), (2, 64, 14, 14), "leaky"),     # ResNet: add has fewer channels
+    ((2, 128, 7, 7), (2, 64, 14, 14), "leaky"),       # ResNet: add is twice as large, sampled with stride 2
+    ((1, 16, 8, 8), (1, 16, 4, 4), "linear"),         # add is smaller: scattered with `sample`
+    ((2, 20, 5, 5), (2, 20, 5, 5), "logistic")])
+@pytest.mark.parametrize("layout", ["nhwc", "nchw"])
+def test_shortcut(xs, adds, act, layout):
+    g = rng(3)
+    x = g.standard_normal(xs, dtype=np.float32)
+    add = g.standard_normal(adds, dtype=np.float32)
+    want = orc.shortcut_forward(x, add, 1.0, 1.0, act)
+    n, c, h, w = xs
+    if layout == "nchw":
+        xt, xd = dev_nchw(x)
+        at, ad = dev_nchw(add)
+        yt, yd = empty_nchw(n, c, h, w)
+        dn.shortcut(xd, ad, yd, 1.0, 1.0, act)
+        got = yt.cpu().numpy()
+    else:
+        xt, xd = dev_nhwc(x)
+        at, ad = dev_nhwc(add)
+        yt, yd = empty_nhwc(n, c, h, w)
+        yt.zero_()
+        dn.shortcut(xd, ad, yd, 1.0, 1.0, act)
+        got = host_from_nhwc(yt, c)
+        assert padding_is_zero(yt, c)
+    assert rel_to_max(got, want) < TOL_FP32
+
+
+def test_shortcut_bf16_storage():
+    g = rng(4)
+    x = bf16_round(g.standard_normal((2, 64, 10, 10), dtype=np.float32))
+    add = bf16_round(g.standard_normal((2, 64, 10, 10), dtype=np.float32))
+    want = orc.shortcut_forward(x, add, 1.0, 1.0, "linear")
+    xt, xd = dev_nhwc(x, torch.bfloat16)
+    at, ad = dev_nhwc(add, torch.bfloat16)
+    yt, yd = empty_nhwc(2, 64, 10, 10, torch.bfloat16)
+    dn.shortcut(xd, ad, yd)
+    assert rel_to_max(host_from_nhwc(yt, 64), want) < 2 ** -8
+
+
+@pytest.mark.parametrize("chans,hw", [((256, 512), (19, 19)), ((128, 256, 3), (13, 11)), ((255,), (7, 7)), ((12, 20), (5, 5))])
+@pytest.mark.parametrize("layout", ["nhwc", "nchw"])
+def test_route(chans, hw, layout):
+    g = rng(5)
+    ins = [g.standard_normal((2, c) + hw, dtype=np.float32) for c in chans]
+    want = orc.route_forward(ins)
+    ctot = sum(chans)
+    if layout == "nchw":
+        held = [dev_nchw(a) for a in ins]
+        yt, yd = empty_nchw(2, ctot, *hw)
+        dn.route([d for _, d in held], yd)
+        got = yt.cpu().numpy()
+    else:
+        held = [dev_nhwc(a) for a in ins]
+        yt, yd = empty_nhwc(2, ctot, *hw)
+        yt.zero_()
+        dn.route([d for _, d in held], yd)
+        got = host_from_nhwc(yt, ctot)
+        assert padding_is_zero(yt, ctot)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 17, 19), (1, 255, 13, 13), (2, 64, 8, 8), (1, 33, 5, 70)])
+def test_layout_round_trip(shape):
+    x = rng(6).standard_normal(shape, dtype=np.float32)
+    xt, xd = dev_nchw(x)
+    mt, md = empty_nhwc(*shape)
+    dn.convert(xd, md)
+    assert np.array_equal(host_from_nhwc(mt, shape[1]), x) and padding_is_zero(mt, shape[1])
+    yt, yd = empty_nchw(*shape)
+    dn.convert(md, yd)
+    assert np.array_equal(yt.cpu().numpy(), x)
+    # bf16 storage and TF32 rounding
+    bt, bd = empty_nhwc(*shape, dtype=torch.bfloat16)
+    dn.convert(xd, bd)
+    assert np.array_equal(host_from_nhwc(bt, shape[1]), bf16_round(x))
+    rt, rd = empty_nhwc(*shape)
+    dn.convert(xd, rd, round_tf32=True)
+    r = host_from_nhwc(rt, shape[1])
+    assert (r.view(np.uint32) & 0x1fff).max() == 0 and rel_to_max(r, x) < 2 ** -10
+
+
+@pytest.mark.parametrize("layout", ["nhwc", "nchw"])
+def test_yolo_head(layout):
+    x = rng(7).standard_normal((2, 255, 13, 13), dtype=np.float32)
+    want = orc.yolo_forward(x, 3, 80)
+    xt, xd = dev_nhwc(x) if layout == "nhwc" else dev_nchw(x)
+    yt, yd = empty_nchw(2, 255, 13, 13)
+    dn.yolo(xd, yd, 3, 80)
+    assert rel_to_max(yt.cpu().numpy(), want) < TOL_FP32
+
+
+@pytest.mark.parametrize("layout", ["nhwc", "nchw"])
+def test_avgpool_softmax(layout):
+    x = rng(8).standard_normal((3, 1000, 7, 7), dtype=np.float32)
+    want_a = orc.avgpool_forward(x)
+    want_s = orc.softmax_forward(want_a)
+    if layout == "nchw":
+        xt, xd = dev_nchw(x)
+        at, ad = empty_nchw(3, 1000, 1, 1)
+        st, sd = empty_nchw(3, 1000, 1, 1)
+    else:
+        xt, xd = dev_nhwc(x)
+        at, ad = empty_nhwc(3, 1000, 1, 1)
+        st, sd = empty_nhwc(3, 1000, 1, 1)
+    dn.avgpool(xd, ad)
+    dn.softmax(ad, sd)
+    got_a = at.cpu().numpy() if layout == "nchw" else host_from_nhwc(at, 1000)
+    got_s = st.cpu().numpy() if layout == "nchw" else host_from_nhwc(st, 1000)
+    assert rel_to_max(got_a, want_a) < 1e-5
+    assert rel_to_max(got_s, want_s) < 1e-5
+
+
+# ------------------------------------------------------------------ convolution
+def conv_case(seed, b, c, h, w, n, size, stride=1, pad=None, groups=1, bn=True, act="leaky", dist="normal"):
+    g = rng(seed)
+    pad = size // 2 if pad is None else pad
+    x = g.standard_normal((b, c, h, w), dtype=np.float32) if dist == "normal" else g.random((b, c, h, w), dtype=np.float32)
+    fan = size * size * c // groups
+    wts = g.standard_normal((n, c // groups, size, size), dtype=np.float32) * np.float32(np.sqrt(2.0 / fan))
+    biases = g.standard_normal(n, dtype=np.float32) * np.float32(0.1)
+    if bn:
+        scales = g.uniform(0.9, 1.1, n).astype(np.float32)
+        mean = g.standard_normal(n, dtype=np.float32) * np.float32(0.3)
+        var = g.uniform(0.5, 1.5, n).astype(np.float32)
+    else:
+        scales = mean = var = None
+    return dict(x=x, w=wts, biases=biases, scales=scales, mean=mean, var=var, stride=stride, pad=pad, groups=groups, act=act)
+
+
+def run_conv(case, mode, in_layout="nchw", out_layout="nchw", xnor=False, both=False):
+    x, w = case["x"], case["w"]
+    b, c, h, wd = x.shape
+    n, size = w.shape[0], w.shape[2]
+    plan = dn.ConvPlan(b, c, h, wd, n, size, case["stride"], case["pad"], case["groups"], case["scales"] is not None,
+                       case["act"], xnor, mode)
+    plan.set_params(w, case["biases"], case["scales"], case["mean"], case["var"])
+    store = torch.bfloat16 if mode == dn.MODE_BF16 else torch.float32
+    xt, xd = dev_nchw(x) if in_layout == "nchw" else dev_nhwc(x, store)
+    if out_layout == "nchw":
+        yt, yd = empty_nchw(b, n, plan.out_h, plan.out_w)
+    else:
+        yt, yd = empty_nhwc(b, n, plan.out_h, plan.out_w, store)
+    y2t = y2d = None
+    if both:
+        y2t, y2d = empty_nhwc(b, n, plan.out_h, plan.out_w, store) if out_layout == "nchw" else empty_nchw(b, n, plan.out_h, plan.out_w)
+    plan.forward(xd, yd, y2d)
+    torch.cuda.synchronize()
+    plan.check_status()
+    got = yt.cpu().numpy() if out_layout == "nchw" else host_from_nhwc(yt, n)
+    if out_layout == "nhwc":
+        assert padding_is_zero(yt, n)
+    got2 = None
+    if both:
+        got2 = host_from_nhwc(y2t, n) if out_layout == "nchw" else y2t.cpu().numpy()
+    return plan, got, got2
+
+
+def oracle_conv(case, xnor=False, x=None):
+    return orc.conv_forward(case["x"] if x is None else x, case["w"], case["biases"], case["scales"], case["mean"], case["var"],
+                            stride=case["stride"], pad=case["pad"], groups=case["groups"], activation=case["act"], xnor=xnor)
+
+
+DIRECT_CASES = {
+    "stem3x3_c3": dict(b=2, c=3, h=32, w=32, n=32, size=3, dist="uniform"),
+    "stem7x7_s2_c3": dict(b=2, c=3, h=30, w=30, n=64, size=7, stride=2, dist="uniform"),
+    "groups2": dict(b=2, c=8, h=10, w=10, n=12, size=3, groups=2),
+    "groups4_1x1": dict(b=1, c=16, h=6, w=6, n=40, size=1, groups=4),
+    "k5_nopad": dict(b=1, c=8, h=11, w=11, n=8, size=5, pad=0),
+    "wide_k": dict(b=1, c=96, h=6, w=6, n=20, size=3, act="linear", bn=False),
+}
+
+
+@pytest.mark.parametrize("name", list(DIRECT_CASES))
+@pytest.mark.parametrize("layouts", [("nchw", "nchw"), ("nchw", "nhwc"), ("nhwc", "nhwc")])
+def test_conv_direct_fp32(name, layouts):
+    case = conv_case(100, **DIRECT_CASES[name])
+    plan, got, _ = run_conv(case, dn.MODE_FP32, layouts[0], layouts[1])
+    assert plan.kernel == "direct_fp32"
+    assert rel_to_max(got, oracle_conv(case)) < 1e-5
+
+
+TC_CASES = {
+    "1x1_c32_onetile": dict(b=1, c=32, h=8, w=16, n=16, size=1, bn=False, act="linear"),
+    "1x1_c64": dict(b=2, c=64, h=9, w=9, n=40, size=1),
+    "1x1_c8_sw32": dict(b=1, c=8, h=8, w=8, n=16, size=1),
+    "1x1_c16_sw64": dict(b=1, c=16, h=12, w=12, n=32, size=1),
+    "1x1_c24_ragged_k": dict(b=1, c=24, h=7, w=7, n=16, size=1),
+    "1x1_c48_ragged_k": dict(b=1, c=48, h=7, w=7, n=16, size=1),
+    "3x3_c32": dict(b=1, c=32, h=8, w=16, n=32, size=3),
+    "3x3_c16": dict(b=2, c=16, h=13, w=13, n=32, size=3),
+    "3x3_s2": dict(b=2, c=32, h=16, w=16, n=64, size=3, stride=2),
+    "3x3_s2_odd": dict(b=2, c=16, h=13, w=11, n=24, size=3, stride=2),
+    "3x3_nopad": dict(b=2, c=8, h=9, w=9, n=16, size=3, pad=0),
+    "5x5": dict(b=1, c=8, h=11, w=11, n=8, size=5),
+    "7x7_s2": dict(b=1, c=8, h=20, w=20, n=16, size=7, stride=2),
+    "heads_255": dict(b=2, c=64, h=13, w=13, n=255, size=1, bn=False, act="linear"),
+    "n512_two_ntiles": dict(b=1, c=64, h=13, w=13, n=512, size=3),
+    "n1000_logistic": dict(b=2, c=128, h=3, w=3, n=1000, size=1, bn=False, act="logistic"),
+    "darknet53_mid": dict(b=1, c=256, h=13, w=13, n=512, size=3),
+    "many_tiles": dict(b=4, c=64, h=64, w=64, n=64, size=3),
+    "map19_batch_folded": dict(b=8, c=128, h=19, w=19, n=256, size=3),
+    "k4608": dict(b=2, c=512, h=7, w=7, n=64, size=3),
+}
+
+
+@pytest.mark.parametrize("name", list(TC_CASES))
+def test_conv_tc_tf32(name):
+    case = conv_case(200, **TC_CASES[name])
+    want = oracle_conv(case)
+    plan, got, got2 = run_conv(case, dn.MODE_TF32, "nchw", "nchw", both=True)
+    assert plan.kernel == "tc_tf32"
+    err = rel_to_max(got, want)
+    assert err < TOL_TF32, f"{name}: rel error {err:.3g}"
+    assert np.array_equal(got, got2), "NCHW and NHWC copies of one launch differ"
+    # channels-last in, channels-last out (the layout used between layers)
+    _, got3, _ = run_conv(case, dn.MODE_TF32, "nhwc", "nhwc")
+    assert rel_to_max(got3, want) < TOL_TF32
+
+
+@pytest.mark.parametrize("name", list(TC_CASES))
+def test_conv_tc_bf16(name):
+    case = conv_case(300, **TC_CASES[name])
+    want = oracle_conv(case)
+    plan, got, _ = run_conv(case, dn.MODE_BF16, "nchw", "nchw")
+    assert plan.kernel == "tc_bf16"
+    err = rel_to_max(got, want)
+    assert err < TOL_BF16, f"{name}: rel error {err:.3g}"
+    _, got3, _ = run_conv(case, dn.MODE_BF16, "nhwc", "nhwc")
+    assert rel_to_max(got3, want) < TOL_BF16
+
+
+def test_conv_tc_all_ones_counts_taps():
+    # analytic known answer: ones everywhere -> in-image taps x channels, exact in TF32 and BF16
+    C, H, W, N = 16, 9, 10, 16
+    case = dict(x=np.ones((2, C, H, W), np.float32), w=np.ones((N, C, 3, 3), np.float32), biases=np.zeros(N, np.float32),
+                scales=None, mean=None, var=None, stride=1, pad=1, groups=1, act="linear")
+    ys, xs = np.arange(H), np.arange(W)
+    ny = np.minimum(ys + 1, H - 1) - np.maximum(ys - 1, 0) + 1
+    nx = np.minimum(xs + 1, W - 1) - np.maximum(xs - 1, 0) + 1
+    want = np.broadcast_to((ny[:, None] * nx[None, :] * C).astype(np.float32), (2, N, H, W))
+    for mode in (dn.MODE_TF32, dn.MODE_BF16, dn.MODE_FP32):
+        _, got, _ = run_conv(case, mode)
+        assert np.array_equal(got, want)
+
+
+XNOR_CASES = {
+    "3x3_c64": dict(b=2, c=64, h=10, w=10, n=32, size=3),
+    "3x3_c40_ragged_word": dict(b=2, c=40, h=6, w=7, n=9, size=3),
+    "1x1_c128": dict(b=2, c=128, h=7, w=7, n=64, size=1),
+    "3x3_c1024": dict(b=1, c=1024, h=7, w=7, n=70, size=3),
+    "3x3_s2": dict(b=1, c=32, h=9, w=9, n=16, size=3, stride=2),
+}
+
+
+@pytest.mark.parametrize("name", list(XNOR_CASES))
+@pytest.mark.parametrize("in_layout", ["nchw", "nhwc"])
+def test_conv_xnor(name, in_layout):
+    case = conv_case(400, **XNOR_CASES[name])
+    x, w = case["x"], case["w"]
+    x.reshape(-1)[::7] = 0.0   # exact zeros binarise to -1 (the CPU reference tests x > 0)
+    b, c, h, wd = x.shape
+    n = w.shape[0]
+    plan = dn.ConvPlan(b, c, h, wd, n, w.shape[2], case["stride"], case["pad"], 1, True, case["act"], True, dn.MODE_TF32)
+    plan.set_params(w, case["biases"], case["scales"], case["mean"], case["var"])
+    assert plan.kernel == "xnor_popc"
+    xt, xd = dev_nchw(x) if in_layout == "nchw" else dev_nhwc(x)
+    acc = torch.full((b, n, plan.out_h, plan.out_w), -12345, dtype=torch.int32, device="cuda")
+    plan.xnor_accumulate(xd, acc)
+    want_acc = orc.xnor_accumulate(x, w, stride=case["stride"], pad=case["pad"])
+    assert np.array_equal(acc.cpu().numpy(), want_acc.astype(np.int32)), "popcount accumulators must be bit-exact"
+    yt, yd = empty_nchw(b, n, plan.out_h, plan.out_w)
+    y2t, y2d = empty_nhwc(b, n, plan.out_h, plan.out_w)
+    plan.forward(xd, yd, y2d)
+    want = oracle_conv(case, xnor=True)
+    # the CPU adds +-mean one product at a time in fp32; mean * integer differs from that sum in the last bits
+    assert rel_to_max(yt.cpu().numpy(), want) < 1e-5
+    assert np.array_equal(host_from_nhwc(y2t, n), yt.cpu().numpy()) and padding_is_zero(y2t, n)
+
+
+def test_conv_xnor_power_of_two_mean_is_bit_exact():
+    # with |w| = 2^-3 everywhere the per-filter mean is a power of two, every partial sum on the CPU is
+    # exact, and the whole layer output (bias only, linear) must match bit for bit
+    g = rng(500)
+    x = g.standard_normal((2, 64, 8, 8), dtype=np.float32)
+    w = np.where(g.random((16, 64, 3, 3)) > 0.5, 0.125, -0.125).astype(np.float32)
+    case = dict(x=x, w=w, biases=np.zeros(16, np.float32), scales=None, mean=None, var=None, stride=1, pad=1, groups=1, act="linear")
+    plan = dn.ConvPlan(2, 64, 8, 8, 16, 3, 1, 1, 1, False, "linear", True, dn.MODE_TF32).set_params(w, case["biases"])
+    xt, xd = dev_nchw(x)
+    yt, yd = empty_nchw(2, 16, 8, 8)
+    plan.forward(xd, yd)
+    assert np.array_equal(yt.cpu().numpy(), oracle_conv(case, xnor=True))
+
+
+def test_conv_rejects_mismatched_tensors():
+    plan = dn.ConvPlan(1, 8, 8, 8, 16, 3, 1, 1).set_params(np.zeros((16, 8, 3, 3), np.float32), np.zeros(16, np.float32))
+    xt, xd = dev_nchw(np.zeros((1, 8, 8, 8), np.float32))
+    yt, yd = empty_nchw(1, 16, 7, 8)
+    with pytest.raises(dn.DarknetB200Error):
+        plan.forward(xd, yd)
+    bt, bd = dev_nhwc(np.zeros((1, 8, 8, 8), np.float32), torch.bfloat16)
+    gt, gd = empty_nchw(1, 16, 8, 8)
+    with pytest.raises(dn.DarknetB200Error):
+        plan.forward(bd, gd)   # bf16 input to a TF32 plan

