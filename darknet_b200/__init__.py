@@ -87,6 +87,8 @@ SIGNATURES = {
     "dnb_network_flops": (C.c_double, [_P]),
     "dnb_network_launches": (_I, [_P]),
     "dnb_network_profile": (_I, [_P, _P, _P]),
+    "dnb_network_forward_timed": (_I, [_P, _P, _P, _I]),
+    "dnb_network_timed_ms": (_I, [_P, _I, _P]),
 }
 
 _lib = None

@@ -192,6 +192,14 @@ class Network:
         check(lib().dnb_network_profile(self.handle, C.c_void_p(x_dev.data_ptr()), _ptr(ms)))
         return ms
 
+    def forward_timed(self, x_dev, slot: int = 0, stream=None):
+        check(lib().dnb_network_forward_timed(self.handle, C.c_void_p(x_dev.data_ptr()), _stream(stream), slot))
+
+    def timed_ms(self, slot: int = 0) -> np.ndarray:
+        ms = np.zeros(self.n, np.float32)
+        check(lib().dnb_network_timed_ms(self.handle, slot, _ptr(ms)))
+        return ms
+
     def close(self):
         if self.handle:
             lib().dnb_free_network(self.handle)

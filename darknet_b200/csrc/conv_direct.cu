@@ -113,7 +113,12 @@ conv_direct_kernel(DirectArgs a)
                 for (int q = 0; q < FB / 8; ++q) reinterpret_cast<uint4 *>(dst)[q] = reinterpret_cast<uint4 *>(h)[q];
             }
         } else {
-            for (int j = 0; j < FB && f0 + j < npg; ++j) dst[j] = from_float<TY>(acc[j]);
+            // ragged slab: valid filters, then (after the last filter of the last group) zeros up to cpitch
+            const bool last = grp == g.groups - 1;
+            for (int j = 0; j < FB; ++j) {
+                if (f0 + j < npg) dst[j] = from_float<TY>(acc[j]);
+                else if (last && n0 + j < a.y_cpitch) dst[j] = from_float<TY>(0.f);
+            }
         }
     }
     if (a.y_nchw) {

@@ -500,22 +500,42 @@ extern "C" int dnb_network_launches(const dnb_network *net)
     return n;
 }
 
-extern "C" int dnb_network_profile(dnb_network *net, const float *device_input, float *layer_ms)
+// Forward with a CUDA event between layers, asynchronous like dnb_network_forward.  `slot` selects an
+// independent set of events so that several timed forwards can be in flight before any is read.
+extern "C" int dnb_network_forward_timed(dnb_network *net, const float *device_input, void *stream, int slot)
 {
-    if (!net || !device_input || !layer_ms) DNB_FAIL(DNB_EINVAL, "network_profile: null argument");
+    if (!net || !device_input || slot < 0 || slot > 4096) DNB_FAIL(DNB_EINVAL, "network_forward_timed: bad argument");
+    if (!net->weights_loaded) DNB_FAIL(DNB_EINVAL, "network_forward_timed: load_weights has not been called");
     const int n = (int)net->layers.size();
-    while ((int)net->events.size() < n + 1) {
+    while ((int)net->events.size() < (slot + 1) * (n + 1)) {
         cudaEvent_t e;
         DNB_CUDA(cudaEventCreate(&e));
         net->events.push_back(e);
     }
-    cudaStream_t s = net->stream;
+    cudaStream_t s = stream ? (cudaStream_t)stream : net->stream;
+    cudaEvent_t *ev = &net->events[(size_t)slot * (n + 1)];
     for (int i = 0; i < n; ++i) {
-        DNB_CUDA(cudaEventRecord(net->events[i], s));
+        DNB_CUDA(cudaEventRecord(ev[i], s));
         DNB_TRY(forward_layer(net, i, device_input, s));
     }
-    DNB_CUDA(cudaEventRecord(net->events[n], s));
-    DNB_CUDA(cudaStreamSynchronize(s));
-    for (int i = 0; i < n; ++i) DNB_CUDA(cudaEventElapsedTime(&layer_ms[i], net->events[i], net->events[i + 1]));
+    DNB_CUDA(cudaEventRecord(ev[n], s));
     return DNB_OK;
+}
+
+// Per-layer device time of the timed forward in `slot`, milliseconds; waits for that forward to finish.
+extern "C" int dnb_network_timed_ms(dnb_network *net, int slot, float *layer_ms)
+{
+    if (!net || !layer_ms || slot < 0) DNB_FAIL(DNB_EINVAL, "network_timed_ms: bad argument");
+    const int n = (int)net->layers.size();
+    if ((int)net->events.size() < (slot + 1) * (n + 1)) DNB_FAIL(DNB_EINVAL, "network_timed_ms: slot %d was never recorded", slot);
+    cudaEvent_t *ev = &net->events[(size_t)slot * (n + 1)];
+    DNB_CUDA(cudaEventSynchronize(ev[n]));
+    for (int i = 0; i < n; ++i) DNB_CUDA(cudaEventElapsedTime(&layer_ms[i], ev[i], ev[i + 1]));
+    return DNB_OK;
+}
+
+extern "C" int dnb_network_profile(dnb_network *net, const float *device_input, float *layer_ms)
+{
+    DNB_TRY(dnb_network_forward_timed(net, device_input, nullptr, 0));
+    return dnb_network_timed_ms(net, 0, layer_ms);
 }

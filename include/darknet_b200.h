@@ -251,7 +251,15 @@ double dnb_network_flops(const dnb_network *net);
 /* Number of kernel launches one dnb_network_forward issues. */
 int dnb_network_launches(const dnb_network *net);
 
-/* Per-layer device time of the last dnb_network_profile call, milliseconds. */
+/* dnb_network_forward with a CUDA event recorded between layers; asynchronous.
+ * `slot` (0..4096) names an independent set of events, so that several timed
+ * forwards can be queued before any is read.  dnb_network_timed_ms waits for
+ * the forward recorded in `slot` and returns each layer's device time in
+ * milliseconds.  dnb_network_profile = one timed forward on the network's own
+ * stream, read back at once.  The reference has only a whole-network
+ * wall-clock timer (examples/darknet.c:116-134, the `speed` command). */
+int dnb_network_forward_timed(dnb_network *net, const float *device_input, void *stream, int slot);
+int dnb_network_timed_ms(dnb_network *net, int slot, float *layer_ms);
 int dnb_network_profile(dnb_network *net, const float *device_input, float *layer_ms);
 
 #ifdef __cplusplus

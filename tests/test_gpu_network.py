@@ -134,4 +134,4 @@ def test_xnor_network_teacher_forced(tmp_path):
     net = build(cfg, params, tmp_path, dn.MODE_TF32)
     net.predict(x)
     assert [net.layer_kernel(i) for i in range(net.n)].count("xnor_popc") == 17
-    assert rel_to_max(net.layer_output(0), want[0]) < 1e-5
+    assert rel_to_max(net.layer_output(0), want[0]) < 1e-3   # fp32 stem, stored rounded to TF32 for the next layer
