@@ -27,6 +27,7 @@ int launch_conv_direct(const DirectArgs &a, cudaStream_t s);
 struct alignas(64) TcArgs {
     CUtensorMap tmx[4];   // activation maps: one per (row parity, column parity) lattice of a strided conv
     CUtensorMap tmw;      // weights [taps][n_pad][c_pad], channels innermost
+    CUtensorMap tmy;      // NHWC output, written by TMA stores from the staging rows
     int is_bf16;          // 0: kind::tf32 on f32 operands, 1: kind::f16 on bf16 operands
     int row_bytes;        // bytes of channels per pipeline stage row: 128, 64 or 32 (= swizzle span)
     int bk;               // channels per stage row (row_bytes / element size)
@@ -39,6 +40,9 @@ struct alignas(64) TcArgs {
     int total_tiles;      // n_tiles * tiles_w * tiles_h * tiles_b
     int stages;           // depth of the shared-memory ring
     int a_bytes, b_bytes; // shared-memory bytes of one stage's activation / weight tile (1024-multiples)
+    int store_row_bytes;  // bytes of one staged output row (128, 64 or 32) = swizzle span of tmy
+    int n_pad;            // length of the scale / shift vectors
+    int n_tot;            // n_tiles * bn rounded up: entries of the shared scale / shift copies
     void *y_nhwc;
     int y_dtype, y_cpitch;
     float *y_nchw;
@@ -48,6 +52,7 @@ struct alignas(64) TcArgs {
 };
 int launch_conv_tc(const TcArgs &a, cudaStream_t s);
 size_t conv_tc_smem_bytes(const TcArgs &a);
+size_t conv_tc_fixed_smem(int store_row_bytes, int n_tot);
 int conv_tc_max_smem();
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link).
@@ -99,5 +104,7 @@ struct dnb_conv_plan {
     dnb::TcArgs tc;
     const void *tc_x_ptr;
     int tc_x_cpitch;
+    const void *tc_y_ptr;    // NHWC output the store map was built for
+    int tc_y_cpitch, tc_y_dtype;
     int device;
 };

@@ -176,7 +176,7 @@ static void pick_pixel_tile(const ConvGeom &g, int *wt, int *ht, int *bt)
         }
 }
 
-static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x)
+static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, int y_dtype, int y_cpitch)
 {
     TcArgs &a = p->tc;
     const ConvGeom &g = p->g;
@@ -193,28 +193,46 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x)
     a.tiles_h = (g.out_h + a.ht - 1) / a.ht;
     a.tiles_b = (g.batch + a.bt - 1) / a.bt;
     const int ptiles = a.tiles_w * a.tiles_h * a.tiles_b;
-    // filters per tile: multiple of 16 <= 256 with the least padded columns, widest on ties
-    int best_bn = 16;
-    long best_cols = 1L << 60;
-    for (int bn = 16; bn <= 256; bn += 16) {
-        long cols = (long)((p->n_pad + bn - 1) / bn) * bn;
-        if (cols <= best_cols) { best_cols = cols; best_bn = bn; }
+    // Filters per tile.  One tile when they fit (<= 256).  Otherwise a multiple of 64 (so that every
+    // staged output chunk lies inside one tile), weighing padded MMA columns against operand re-loads.
+    if (p->n_pad <= 256) {
+        a.bn = p->n_pad;
+    } else {
+        double best = 1e300;
+        for (int bn = 64; bn <= 256; bn += 64) {
+            const int nt = (p->n_pad + bn - 1) / bn;
+            const double score = (double)nt * bn + 0.5 * nt * 128;
+            if (score <= best) { best = score; a.bn = bn; }
+        }
     }
-    a.bn = best_bn;
     a.n_tiles = (p->n_pad + a.bn - 1) / a.bn;
-    while (ptiles * a.n_tiles < sm_count() && a.bn >= 64 && a.bn % 32 == 0) {  // too few tiles to fill the SMs
+    while (ptiles * a.n_tiles < sm_count() && a.bn >= 128 && a.bn % 128 == 0) {  // too few tiles to fill the SMs
         a.bn /= 2;
         a.n_tiles = (p->n_pad + a.bn - 1) / a.bn;
     }
     a.total_tiles = ptiles * a.n_tiles;
+    a.n_pad = p->n_pad;
+    a.n_tot = a.n_tiles * a.bn;
     a.a_bytes = 128 * a.row_bytes;
     a.b_bytes = round_up(a.bn * a.row_bytes, 1024);
     const int max_smem = conv_tc_max_smem();
     if (max_smem <= 0) DNB_FAIL(DNB_ECUDA, "conv: cannot query shared memory of the current device");
-    int stages = (max_smem - 2048) / (a.a_bytes + a.b_bytes);
+    // staged output rows: the widest of 128 / 64 / 32 bytes that the output pitch allows and that keeps
+    // at least four ring stages
+    const int out_es = y_dtype == DNB_BF16 ? 2 : 4;
+    const int pitch_bytes = y_nhwc ? y_cpitch * out_es : 32;
+    const int min_srb = 16 * out_es;  // a staged row holds at least one 16-column piece of the accumulator
+    int srb = pitch_bytes >= 128 ? 128 : (pitch_bytes >= 64 ? 64 : 32);
+    if (srb < min_srb) srb = min_srb;  // the box may be wider than a narrow tensor: the TMA unit clips it
+    int stages = 0;
+    for (;; srb /= 2) {
+        stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.n_tot)) / (a.a_bytes + a.b_bytes));
+        if (stages >= 4 || srb == min_srb) break;
+    }
     if (stages > 8) stages = 8;
     if (stages < 2) DNB_FAIL(DNB_ECUDA, "conv: %d bytes of shared memory are too few for the operand ring", max_smem);
     a.stages = stages;
+    a.store_row_bytes = srb;
     a.g = g;
     if (!p->status) {
         DNB_CUDA(cudaMalloc((void **)&p->status, sizeof(int)));
@@ -242,8 +260,18 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x)
         uint32_t box[3] = {(uint32_t)a.bk, (uint32_t)a.bn, 1u};
         DNB_TRY(encode_tensor_map(&a.tmw, bf16, 3, p->w_tc, dims, strides, box, a.row_bytes));
     }
+    if (y_nhwc) {
+        const size_t opix = (size_t)y_cpitch * out_es;
+        uint64_t dims[4] = {(uint64_t)y_cpitch, (uint64_t)g.out_w, (uint64_t)g.out_h, (uint64_t)g.batch};
+        uint64_t strides[3] = {opix, opix * g.out_w, opix * g.out_w * g.out_h};
+        uint32_t box[4] = {(uint32_t)(srb / out_es), (uint32_t)a.wt, (uint32_t)a.ht, (uint32_t)a.bt};
+        DNB_TRY(encode_tensor_map(&a.tmy, y_dtype == DNB_BF16, 4, y_nhwc, dims, strides, box, srb));
+    }
     p->tc_x_ptr = x->data;
     p->tc_x_cpitch = x->cpitch;
+    p->tc_y_ptr = y_nhwc;
+    p->tc_y_cpitch = y_cpitch;
+    p->tc_y_dtype = y_dtype;
     return DNB_OK;
 }
 
@@ -329,7 +357,9 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
         DNB_FAIL(DNB_EINVAL, "conv: channels-last input is %s, this plan (%s) reads %s", x->dtype == DNB_BF16 ? "bf16" : "f32",
                  kKernelNames[p->kernel], want == DNB_BF16 ? "bf16" : "f32");
     }
-    if (p->tc_x_ptr != xin.data || p->tc_x_cpitch != xin.cpitch) DNB_TRY(build_tc_args(p, &xin));
+    if (p->tc_x_ptr != xin.data || p->tc_x_cpitch != xin.cpitch || p->tc_y_ptr != y_nhwc || p->tc_y_cpitch != y_cpitch ||
+        p->tc_y_dtype != y_dtype || !p->status)
+        DNB_TRY(build_tc_args(p, &xin, y_nhwc, y_dtype, y_cpitch));
     TcArgs &a = p->tc;
     a.y_nhwc = y_nhwc; a.y_dtype = y_dtype; a.y_cpitch = y_cpitch; a.y_nchw = y_nchw;
     a.ep = ep;

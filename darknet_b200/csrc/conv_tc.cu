@@ -141,6 +141,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// TMA store of one staged output chunk (shared -> global), bulk-group completion.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2, int c3)
+{
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// barrier among the 128 epilogue threads only (barrier 0 is __syncthreads)
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 // ------------------------------------------------------------------ kernel
 struct TcShared {
     uint64_t full[MAX_STAGES];
@@ -152,7 +165,18 @@ struct TcShared {
 };
 
 enum { WAIT_EMPTY = 101, WAIT_FULL = 102, WAIT_ACC_EMPTY = 103, WAIT_ACC_FULL = 104 };
+enum { ACT_GENERIC = -1 };
 
+template <int ACT>
+__device__ __forceinline__ float act_apply(float x, int runtime_act)
+{
+    if (ACT == DNB_LINEAR) return x;
+    if (ACT == DNB_LEAKY) return fmaxf(x, 0.1f * x);   // x > 0 ? x : 0.1x
+    if (ACT == DNB_LOGISTIC) return 1.f / (1.f + __expf(-x));
+    return activate(x, runtime_act);
+}
+
+template <int ACT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ TcArgs a)
 {
@@ -160,7 +184,11 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     // operand ring, 1024-byte aligned (the 128-byte swizzle pattern repeats every 1024 bytes)
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t stage_bytes = a.a_bytes + a.b_bytes;
-    TcShared *sh = reinterpret_cast<TcShared *>(smem_raw + (ring - smem_u32(smem_raw)) + (size_t)a.stages * stage_bytes);
+    uint8_t *after_ring = smem_raw + (ring - smem_u32(smem_raw)) + (size_t)a.stages * stage_bytes;
+    uint8_t *stage_out = after_ring;                                  // 2 x 128 rows x store_row_bytes
+    float *s_scale = reinterpret_cast<float *>(after_ring + 2 * 128 * a.store_row_bytes);
+    float *s_shift = s_scale + a.n_tot;
+    TcShared *sh = reinterpret_cast<TcShared *>(s_shift + a.n_tot);
     volatile int *abort_flag = &sh->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -181,6 +209,11 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     if (warp == 1) {  // TMEM: all 512 columns (two accumulators of 256), whole warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // per-filter epilogue vectors, once per CTA (zero beyond the layer's filters)
+    for (int i = threadIdx.x; i < a.n_tot; i += TC_THREADS) {
+        s_scale[i] = i < a.n_pad ? __ldg(a.ep.scale + i) : 0.f;
+        s_shift[i] = i < a.n_pad ? __ldg(a.ep.shift + i) : 0.f;
     }
     tc_fence_before();
     __syncthreads();
@@ -223,9 +256,6 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 }
             }
         }
-        // Drain: every load issued above lands in this CTA's shared memory, so wait until the
-        // consumer has released (or an abort was raised for) all stages before the CTA may exit.
-        // The MMA warp's final commit covers the last stages; nothing more to do here.
     } else if (warp == 1) {
         // ---------------- MMA issuer
         const uint32_t fmt = a.is_bf16 ? 1u : 2u;  // BF16 : TF32
@@ -263,64 +293,83 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     } else {
         // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31
         const int quarter = warp & 3;
-        const int m = quarter * 32 + lane;  // pixel index inside the tile = TMEM lane
+        const int m = quarter * 32 + lane;  // pixel index inside the tile = TMEM lane = staging row
         const int wl = m % a.wt, hl = (m / a.wt) % a.ht, bl = m / (a.wt * a.ht);
         const ConvGeom &g = a.g;
+        const bool store_thread = threadIdx.x == 64;
+        const bool out_bf16 = a.y_dtype == DNB_BF16;
+        const int srb = a.store_row_bytes;                       // bytes of one staged row = swizzle span
+        const int cols_per_chunk = srb / (out_bf16 ? 2 : 4);
+        const int q_mask = srb / 16 - 1;
+        const int q_xor = (m >> (srb == 128 ? 0 : (srb == 64 ? 1 : 2))) & q_mask;   // 16-byte chunk swizzle of row m
+        uint32_t chunk_count = 0;
         int it = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++it) {
+        for (int tile = blockIdx.x; tile < a.total_tiles; tile += gridDim.x, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             const int nt = tile % a.n_tiles, pt = tile / a.n_tiles;
-            const int ow = (pt % a.tiles_w) * a.wt + wl;
-            const int oh = ((pt / a.tiles_w) % a.tiles_h) * a.ht + hl;
-            const int b = (pt / ptiles_wh) * a.bt + bl;
+            const int ow0 = (pt % a.tiles_w) * a.wt, oh0 = ((pt / a.tiles_w) % a.tiles_h) * a.ht, b0 = (pt / ptiles_wh) * a.bt;
+            const int ow = ow0 + wl, oh = oh0 + hl, b = b0 + bl;
             const bool pix_ok = ow < g.out_w && oh < g.out_h && b < g.batch;
-            const size_t pix = ((size_t)b * g.out_h + oh) * g.out_w + ow;
 
-            ok = mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, abort_flag, a.status, WAIT_ACC_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, abort_flag, a.status, WAIT_ACC_FULL);
+            epilogue_bar();                 // all four warps agree on the abort flag from here
+            if (*abort_flag) break;
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
-            for (int j0 = 0; j0 < a.bn; j0 += 16) {
-                uint32_t r[16];
-                tmem_ld16(t_row + j0, r);
-                tmem_ld_wait();
-                const int n0 = nt * a.bn + j0;
-                float v[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int n = n0 + j;
-                    float t = 0.f;
-                    if (n < g.n) {
-                        t = __uint_as_float(r[j]) * __ldg(a.ep.scale + n) + __ldg(a.ep.shift + n);
-                        t = activate(t, a.ep.activation);
-                        if (a.ep.round_tf32) t = round_tf32(t);
-                    }
-                    v[j] = t;
+            for (int c0 = 0; c0 < a.bn; c0 += cols_per_chunk) {
+                uint8_t *row = nullptr;
+                if (a.y_nhwc) {
+                    const uint32_t buf = chunk_count & 1;
+                    if (store_thread && chunk_count >= 2) tma_store_wait_read1();   // the store that last read this buffer is done
+                    epilogue_bar();
+                    row = stage_out + (size_t)buf * 128 * srb + (size_t)m * srb;
                 }
-                if (pix_ok) {
-                    if (a.y_nhwc) {
-                        if (a.y_dtype == DNB_F32) {
-                            float *dst = reinterpret_cast<float *>(a.y_nhwc) + pix * a.y_cpitch + n0;
+                for (int p0 = 0; p0 < cols_per_chunk; p0 += 16) {
+                    const int j0 = c0 + p0;            // first column of this piece inside the tile
+                    float v[16];
+                    if (j0 < a.bn) {
+                        uint32_t r[16];
+                        tmem_ld16(t_row + j0, r);
+                        tmem_ld_wait();
+                        const int nl = nt * a.bn + j0;  // first filter of this piece
+                        const float4 *sc4 = reinterpret_cast<const float4 *>(s_scale + nl);
+                        const float4 *sf4 = reinterpret_cast<const float4 *>(s_shift + nl);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float4 sc = sc4[q], sf = sf4[q];
+                            const float scv[4] = {sc.x, sc.y, sc.z, sc.w}, sfv[4] = {sf.x, sf.y, sf.z, sf.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int j = 4 * q + e;
+                                float t = act_apply<ACT>(fmaf(__uint_as_float(r[j]), scv[e], sfv[e]), a.ep.activation);
+                                if (a.ep.round_tf32) t = round_tf32(t);
+                                v[j] = (nl + j < g.n) ? t : 0.f;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                    }
+                    if (row) {
+                        if (!out_bf16) {
+                            const int qb = p0 / 4;     // first 16-byte chunk of this piece in the row
 #pragma unroll
                             for (int q = 0; q < 4; ++q)
-                                if (n0 + 4 * q + 4 <= a.y_cpitch)
-                                    reinterpret_cast<float4 *>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                                *reinterpret_cast<float4 *>(row + (((qb + q) ^ q_xor) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                         } else {
-                            __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(a.y_nhwc) + pix * a.y_cpitch + n0;
+                            const int qb = p0 / 8;
 #pragma unroll
-                            for (int q = 0; q < 2; ++q)
-                                if (n0 + 8 * q + 8 <= a.y_cpitch) {
-                                    __align__(16) __nv_bfloat16 hv[8];
+                            for (int q = 0; q < 2; ++q) {
+                                __align__(16) __nv_bfloat16 hv[8];
 #pragma unroll
-                                    for (int j = 0; j < 8; ++j) hv[j] = __float2bfloat16_rn(v[8 * q + j]);
-                                    reinterpret_cast<uint4 *>(dst)[q] = *reinterpret_cast<uint4 *>(hv);
-                                }
+                                for (int j = 0; j < 8; ++j) hv[j] = __float2bfloat16_rn(v[8 * q + j]);
+                                *reinterpret_cast<uint4 *>(row + (((qb + q) ^ q_xor) << 4)) = *reinterpret_cast<uint4 *>(hv);
+                            }
                         }
                     }
-                    if (a.y_nchw) {
+                    if (a.y_nchw && pix_ok && j0 < a.bn) {
+                        const int n0 = nt * a.bn + j0;
                         const size_t plane = (size_t)g.out_h * g.out_w;
                         float *dst = a.y_nchw + ((size_t)b * g.n + n0) * plane + (size_t)oh * g.out_w + ow;
 #pragma unroll
@@ -328,14 +377,29 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                             if (n0 + j < g.n) dst[j * plane] = v[j];
                     }
                 }
+                if (a.y_nhwc) {
+                    fence_async_smem();            // staged rows visible to the TMA unit
+                    epilogue_bar();
+                    if (store_thread) {
+                        // the TMA unit clips the box at the tensor's extents: ragged tiles need no predicates
+                        tma_store_4d(&a.tmy, smem_u32(stage_out + (size_t)(chunk_count & 1) * 128 * srb), nt * a.bn + c0, ow0, oh0, b0);
+                        tma_store_commit();
+                    }
+                    ++chunk_count;
+                }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[acc]));
         }
+        if (store_thread) tma_store_wait_all();
     }
 
     // ---------------- teardown (also the abort path)
+    if (*abort_flag) {   // give loads that are still in flight time to land before shared memory is released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 4000000LL) { }
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -345,9 +409,14 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
 }
 
 // ------------------------------------------------------------------ host side
+size_t conv_tc_fixed_smem(int store_row_bytes, int n_tot)
+{
+    return 1024 + 2 * 128 * (size_t)store_row_bytes + 2 * sizeof(float) * (size_t)n_tot + sizeof(TcShared) + 64;
+}
+
 size_t conv_tc_smem_bytes(const TcArgs &a)
 {
-    return 1024 + (size_t)a.stages * (a.a_bytes + a.b_bytes) + sizeof(TcShared) + 64;
+    return (size_t)a.stages * (a.a_bytes + a.b_bytes) + conv_tc_fixed_smem(a.store_row_bytes, a.n_tot);
 }
 
 int conv_tc_max_smem()
@@ -365,11 +434,20 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
     int dev = 0;
     DNB_CUDA(cudaGetDevice(&dev));
     if (configured_for != dev) {
-        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, conv_tc_max_smem()));
+        const int m = conv_tc_max_smem();
+        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<DNB_LINEAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, m));
+        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<DNB_LEAKY>, cudaFuncAttributeMaxDynamicSharedMemorySize, m));
+        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<DNB_LOGISTIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, m));
+        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<ACT_GENERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, m));
         configured_for = dev;
     }
     int grid = a.total_tiles < sm_count() ? a.total_tiles : sm_count();
-    conv_tc_kernel<<<grid, TC_THREADS, smem, s>>>(a);
+    switch (a.ep.activation) {
+    case DNB_LINEAR: conv_tc_kernel<DNB_LINEAR><<<grid, TC_THREADS, smem, s>>>(a); break;
+    case DNB_LEAKY: conv_tc_kernel<DNB_LEAKY><<<grid, TC_THREADS, smem, s>>>(a); break;
+    case DNB_LOGISTIC: conv_tc_kernel<DNB_LOGISTIC><<<grid, TC_THREADS, smem, s>>>(a); break;
+    default: conv_tc_kernel<ACT_GENERIC><<<grid, TC_THREADS, smem, s>>>(a); break;
+    }
     DNB_LAUNCH_CHECK("conv_tc");
     return DNB_OK;
 }

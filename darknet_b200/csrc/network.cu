@@ -395,7 +395,7 @@ extern "C" int dnb_network_forward(dnb_network *net, const float *device_input, 
 {
     if (!net || !device_input) DNB_FAIL(DNB_EINVAL, "network_forward: null argument");
     if (!net->weights_loaded) DNB_FAIL(DNB_EINVAL, "network_forward: load_weights has not been called");
-    cudaStream_t s = stream ? (cudaStream_t)stream : net->stream;
+    cudaStream_t s = (cudaStream_t)stream;  // NULL is the legacy default stream, as everywhere in CUDA
     for (int i = 0; i < (int)net->layers.size(); ++i) DNB_TRY(forward_layer(net, i, device_input, s));
     return DNB_OK;
 }
@@ -454,7 +454,7 @@ extern "C" int dnb_network_layer_output(dnb_network *net, int i, float *host_out
     if (!net || !host_out || i < 0 || i >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "layer_output: bad argument");
     Layer &L = net->layers[i];
     const size_t elems = (size_t)net->batch * L.out_c * L.out_h * L.out_w;
-    DNB_CUDA(cudaStreamSynchronize(net->stream));
+    DNB_CUDA(cudaDeviceSynchronize());  // the forward may have run on any stream
     if (L.out.layout == DNB_NCHW) {
         DNB_CUDA(cudaMemcpy(host_out, L.out.data, elems * sizeof(float), cudaMemcpyDeviceToHost));
         return DNB_OK;
@@ -512,7 +512,7 @@ extern "C" int dnb_network_forward_timed(dnb_network *net, const float *device_i
         DNB_CUDA(cudaEventCreate(&e));
         net->events.push_back(e);
     }
-    cudaStream_t s = stream ? (cudaStream_t)stream : net->stream;
+    cudaStream_t s = (cudaStream_t)stream;
     cudaEvent_t *ev = &net->events[(size_t)slot * (n + 1)];
     for (int i = 0; i < n; ++i) {
         DNB_CUDA(cudaEventRecord(ev[i], s));
@@ -536,6 +536,6 @@ extern "C" int dnb_network_timed_ms(dnb_network *net, int slot, float *layer_ms)
 
 extern "C" int dnb_network_profile(dnb_network *net, const float *device_input, float *layer_ms)
 {
-    DNB_TRY(dnb_network_forward_timed(net, device_input, nullptr, 0));
+    DNB_TRY(dnb_network_forward_timed(net, device_input, net->stream, 0));
     return dnb_network_timed_ms(net, 0, layer_ms);
 }

@@ -222,7 +222,8 @@ void dnb_free_network(dnb_network *net);
 int dnb_network_predict(dnb_network *net, const float *input, float **output);
 
 /* The device-resident part alone: input already on the device (NCHW f32,
- * batch*inputs floats), no host copies, asynchronous on `stream`. */
+ * batch*inputs floats), no host copies, asynchronous on `stream` (NULL = the
+ * legacy default stream). */
 int dnb_network_forward(dnb_network *net, const float *device_input, void *stream);
 
 /* Geometry queries (net->n, net->batch, net->inputs, net->outputs; layer
