@@ -14,7 +14,7 @@ struct DirectArgs {
     int x_dtype;
     long long xs_b, xs_c, xs_h, xs_w;    // element strides of x
     const float *wpk;                    // weights [groups][K][npg_pad], K = c/groups*size*size
-    int npg_pad;                         // filters per group rounded up to 16
+    int npg_pad;                         // filters per group rounded up to 32
     void *y_nhwc;                        // optional NHWC output
     int y_dtype, y_cpitch;
     float *y_nchw;                       // optional NCHW f32 output
@@ -47,6 +47,9 @@ struct alignas(64) TcArgs {
     int y_dtype, y_cpitch;
     float *y_nchw;
     int *status;          // device word: 0, or the code of the wait that expired
+    long long *prof;      // 16 cycle counters of CTA 0, accumulated when debug bit 256 is set
+    int debug;            // experiments: 1 skip activation loads, 2 skip weight loads, 4 skip MMAs, 8 skip TMEM loads,
+                          // 16 skip output stores, 32 skip output staging
     ConvGeom g;
     ConvEpilogue ep;
 };

@@ -2,20 +2,25 @@
 //
 // Used where the tensor-core kernel does not apply: very narrow inputs (the
 // 3-channel first layer, which it reads straight from Darknet's NCHW input),
-// grouped convolutions, and DNB_MODE_FP32 networks.  One thread owns one output
-// pixel and FB consecutive filters; the weights of the block's filter slab are
+// grouped convolutions, and DNB_MODE_FP32 networks.
+//
+// A block owns 128 consecutive output pixels and a slab of FB = 32 filters; a
+// thread owns one pixel and all 32 filters of the slab.  The slab's weights are
 // staged through shared memory in K chunks together with a (c,kh,kw) table, so
-// the inner loop is one predicated load of x and FB FMAs.  Accumulation runs
-// over k = c*size*size + kh*size + kw in increasing order, the reference's own
-// order (src/im2col.c:25-28, src/gemm.c:81-87).
+// the inner loop is one predicated, warp-coalesced load of x and 32 FMAs fed by
+// broadcast 16-byte shared loads.  Accumulation runs over
+// k = c*size*size + kh*size + kw in increasing order, the reference's own order
+// (src/im2col.c:25-28, src/gemm.c:81-87).  Results go through a shared tile so
+// that the global stores are 16-byte and contiguous across the warp in either
+// output layout (a pixel's channel run for NHWC, a filter's pixel run for NCHW).
 #include "common.h"
 #include "conv.h"
 #include "device_utils.cuh"
 
 namespace dnb {
 
-constexpr int FB = 16;         // filters per thread
-constexpr int KCHUNK = 384;    // taps staged per pass: 384*(16*4 + 4) B = 26 KB
+constexpr int FB = 32;         // filters per thread / per block slab
+constexpr int KCHUNK = 192;    // taps staged per pass: 192 * (32*4 + 4) B = 25 KB
 constexpr int DTHREADS = 128;  // pixels per block
 
 template <typename TX, typename TY>
@@ -24,6 +29,7 @@ conv_direct_kernel(DirectArgs a)
 {
     __shared__ __align__(16) float w_s[KCHUNK][FB];
     __shared__ int tap_s[KCHUNK];
+    __shared__ __align__(16) float out_s[DTHREADS][FB + 4];   // +4 floats: rows stay 16-byte aligned, banks spread
 
     const ConvGeom &g = a.g;
     const int cpg = g.c / g.groups;           // input channels per group
@@ -35,7 +41,8 @@ conv_direct_kernel(DirectArgs a)
     const int ksq = g.size * g.size;
 
     const long long npix = (long long)g.batch * g.out_h * g.out_w;
-    const long long pix = (long long)blockIdx.x * DTHREADS + threadIdx.x;
+    const long long pix0 = (long long)blockIdx.x * DTHREADS;
+    const long long pix = pix0 + threadIdx.x;
     const bool live = pix < npix;
     int b = 0, oh = 0, ow = 0;
     if (live) {
@@ -83,48 +90,56 @@ conv_direct_kernel(DirectArgs a)
             }
         }
     }
-    if (!live) return;
 
-    // Epilogue: folded batchnorm / bias, activation, stores.
-    const int n0 = grp * npg + f0;  // first global filter of this thread
+    // Epilogue: folded batchnorm / bias, activation, into the shared tile.
+    const int n0 = grp * npg + f0;  // first global filter of this slab
 #pragma unroll
     for (int j = 0; j < FB; ++j) {
-        const int n = n0 + j;
         float v = 0.f;
         if (f0 + j < npg) {
-            v = acc[j] * __ldg(a.ep.scale + n) + __ldg(a.ep.shift + n);
+            v = acc[j] * __ldg(a.ep.scale + n0 + j) + __ldg(a.ep.shift + n0 + j);
             v = activate(v, a.ep.activation);
             if (a.ep.round_tf32) v = round_tf32(v);
         }
-        acc[j] = v;
+        out_s[threadIdx.x][j] = v;
     }
+    __syncthreads();
+    const int live_pix = (int)min((long long)DTHREADS, npix - pix0);
+    const int nvalid = min(FB, npg - f0);                  // filters of this slab that exist
+
     if (a.y_nhwc) {
-        TY *dst = reinterpret_cast<TY *>(a.y_nhwc) + (size_t)pix * a.y_cpitch + n0;
-        if (f0 + FB <= npg && (n0 % FB) == 0) {
-            if (sizeof(TY) == 4) {
+        // Channels [n0, n0 + cols) of every pixel; the last slab of the last group also writes the zero
+        // padding up to cpitch.  16-byte pieces, consecutive threads -> consecutive pieces of a pixel.
+        const bool last = grp == g.groups - 1 && f0 + FB >= npg;
+        const int cols = last ? min(FB, a.y_cpitch - n0) : nvalid;
+        constexpr int EPV = 16 / sizeof(TY);               // elements per 16-byte piece
+        if (cols % EPV == 0 && n0 % EPV == 0) {
+            const int pieces = cols / EPV;
+            TY *base = reinterpret_cast<TY *>(a.y_nhwc) + (size_t)pix0 * a.y_cpitch + n0;
+            for (int i = threadIdx.x; i < live_pix * pieces; i += DTHREADS) {
+                const int p = i / pieces, q = i - p * pieces;
+                const float *src = &out_s[p][q * EPV];
+                if (sizeof(TY) == 4) {
+                    *reinterpret_cast<float4 *>(base + (size_t)p * a.y_cpitch + q * EPV) = *reinterpret_cast<const float4 *>(src);
+                } else {
+                    __align__(16) __nv_bfloat16 h[8];
 #pragma unroll
-                for (int q = 0; q < FB / 4; ++q)
-                    reinterpret_cast<float4 *>(dst)[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
-            } else {
-                __align__(16) __nv_bfloat16 h[FB];
-#pragma unroll
-                for (int j = 0; j < FB; ++j) h[j] = __float2bfloat16_rn(acc[j]);
-#pragma unroll
-                for (int q = 0; q < FB / 8; ++q) reinterpret_cast<uint4 *>(dst)[q] = reinterpret_cast<uint4 *>(h)[q];
+                    for (int e = 0; e < 8; ++e) h[e] = __float2bfloat16_rn(src[e]);
+                    *reinterpret_cast<uint4 *>(base + (size_t)p * a.y_cpitch + q * EPV) = *reinterpret_cast<uint4 *>(h);
+                }
             }
         } else {
-            // ragged slab: valid filters, then (after the last filter of the last group) zeros up to cpitch
-            const bool last = grp == g.groups - 1;
-            for (int j = 0; j < FB; ++j) {
-                if (f0 + j < npg) dst[j] = from_float<TY>(acc[j]);
-                else if (last && n0 + j < a.y_cpitch) dst[j] = from_float<TY>(0.f);
+            TY *base = reinterpret_cast<TY *>(a.y_nhwc) + (size_t)pix0 * a.y_cpitch + n0;
+            for (int i = threadIdx.x; i < live_pix * cols; i += DTHREADS) {
+                const int p = i / cols, j = i - p * cols;
+                base[(size_t)p * a.y_cpitch + j] = from_float<TY>(out_s[p][j]);
             }
         }
     }
-    if (a.y_nchw) {
+    if (a.y_nchw && live) {
         const size_t plane = (size_t)g.out_h * g.out_w;
         float *dst = a.y_nchw + ((size_t)b * g.n + n0) * plane + (size_t)oh * g.out_w + ow;
-        for (int j = 0; j < FB && f0 + j < npg; ++j) dst[j * plane] = acc[j];
+        for (int j = 0; j < nvalid; ++j) dst[j * plane] = out_s[threadIdx.x][j];
     }
 }
 

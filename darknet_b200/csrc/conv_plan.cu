@@ -2,6 +2,7 @@
 // (folded batchnorm, repacked / rounded / bit-packed weights) and the forward
 // dispatch behind dnb_conv_*.
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <vector>
@@ -61,7 +62,7 @@ extern "C" int dnb_conv_plan_create(const dnb_conv_desc *d, int mode, dnb_conv_p
     p->g = ConvGeom{d->batch, d->h, d->w, d->c, d->n, d->groups, d->size, d->stride, d->pad, out_h, out_w};
     p->n_pad = round_up(d->n, 16);
     p->c_pad = round_up(d->c, 8);
-    p->npg_pad = round_up(d->n / d->groups, 16);
+    p->npg_pad = round_up(d->n / d->groups, 32);
     p->cwords = (d->c + 31) / 32;
     if (d->xnor) p->kernel = K_XNOR;
     else if (mode == DNB_MODE_FP32 || d->groups != 1 || d->c < 8) p->kernel = K_DIRECT;
@@ -189,6 +190,11 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     a.c_blocks = (p->c_pad + a.bk - 1) / a.bk;
     a.taps = g.size * g.size;
     pick_pixel_tile(g, &a.wt, &a.ht, &a.bt);
+    if (const char *e = getenv("DNB_TC_TILE")) {  // experiment: "wt,ht,bt"
+        int w_ = 0, h_ = 0, b_ = 0;
+        if (sscanf(e, "%d,%d,%d", &w_, &h_, &b_) == 3 && w_ * h_ * b_ == 128) { a.wt = w_; a.ht = h_; a.bt = b_; }
+    }
+    a.debug = getenv("DNB_TC_DEBUG") ? atoi(getenv("DNB_TC_DEBUG")) : 0;
     a.tiles_w = (g.out_w + a.wt - 1) / a.wt;
     a.tiles_h = (g.out_h + a.ht - 1) / a.ht;
     a.tiles_b = (g.batch + a.bt - 1) / a.bt;
@@ -205,6 +211,11 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
             if (score <= best) { best = score; a.bn = bn; }
         }
     }
+    // Tuning knobs for experiments: DNB_TC_BN (filters per tile, a multiple of 64) and DNB_TC_STAGES.
+    if (const char *e = getenv("DNB_TC_BN")) {
+        const int v = atoi(e);
+        if (v >= 64 && v <= 256 && v % 64 == 0 && p->n_pad > v) a.bn = v;
+    }
     a.n_tiles = (p->n_pad + a.bn - 1) / a.bn;
     while (ptiles * a.n_tiles < sm_count() && a.bn >= 128 && a.bn % 128 == 0) {  // too few tiles to fill the SMs
         a.bn /= 2;
@@ -219,7 +230,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     if (max_smem <= 0) DNB_FAIL(DNB_ECUDA, "conv: cannot query shared memory of the current device");
     // staged output rows: the widest of 128 / 64 / 32 bytes that the output pitch allows and that keeps
     // at least four ring stages
-    const int out_es = y_dtype == DNB_BF16 ? 2 : 4;
+    const int out_es = bf16 ? 2 : 4;   // channels-last output uses the plan's storage type
     const int pitch_bytes = y_nhwc ? y_cpitch * out_es : 32;
     const int min_srb = 16 * out_es;  // a staged row holds at least one 16-column piece of the accumulator
     int srb = pitch_bytes >= 128 ? 128 : (pitch_bytes >= 64 ? 64 : 32);
@@ -230,15 +241,20 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
         if (stages >= 4 || srb == min_srb) break;
     }
     if (stages > 8) stages = 8;
+    if (const char *e = getenv("DNB_TC_STAGES")) {
+        const int v = atoi(e);
+        if (v >= 2 && v <= stages) stages = v;
+    }
     if (stages < 2) DNB_FAIL(DNB_ECUDA, "conv: %d bytes of shared memory are too few for the operand ring", max_smem);
     a.stages = stages;
     a.store_row_bytes = srb;
     a.g = g;
     if (!p->status) {
-        DNB_CUDA(cudaMalloc((void **)&p->status, sizeof(int)));
-        DNB_CUDA(cudaMemset(p->status, 0, sizeof(int)));
+        DNB_CUDA(cudaMalloc((void **)&p->status, 32 * sizeof(long long)));   // status word + 16 cycle counters
+        DNB_CUDA(cudaMemset(p->status, 0, 32 * sizeof(long long)));
     }
     a.status = p->status;
+    a.prof = reinterpret_cast<long long *>(p->status) + 8;
 
     // activation maps: lattice (ph, pw) of the input holds rows ph, ph+stride, ... and columns pw, pw+stride, ...
     const size_t pix_bytes = (size_t)x->cpitch * es;
@@ -265,7 +281,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
         uint64_t dims[4] = {(uint64_t)y_cpitch, (uint64_t)g.out_w, (uint64_t)g.out_h, (uint64_t)g.batch};
         uint64_t strides[3] = {opix, opix * g.out_w, opix * g.out_w * g.out_h};
         uint32_t box[4] = {(uint32_t)(srb / out_es), (uint32_t)a.wt, (uint32_t)a.ht, (uint32_t)a.bt};
-        DNB_TRY(encode_tensor_map(&a.tmy, y_dtype == DNB_BF16, 4, y_nhwc, dims, strides, box, srb));
+        DNB_TRY(encode_tensor_map(&a.tmy, bf16, 4, y_nhwc, dims, strides, box, srb));
     }
     p->tc_x_ptr = x->data;
     p->tc_x_cpitch = x->cpitch;
@@ -357,6 +373,8 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
         DNB_FAIL(DNB_EINVAL, "conv: channels-last input is %s, this plan (%s) reads %s", x->dtype == DNB_BF16 ? "bf16" : "f32",
                  kKernelNames[p->kernel], want == DNB_BF16 ? "bf16" : "f32");
     }
+    if (y_nhwc && y_dtype != want)
+        DNB_FAIL(DNB_EINVAL, "conv: a %s plan writes channels-last output as %s", kKernelNames[p->kernel], want == DNB_BF16 ? "bf16" : "f32");
     if (p->tc_x_ptr != xin.data || p->tc_x_cpitch != xin.cpitch || p->tc_y_ptr != y_nhwc || p->tc_y_cpitch != y_cpitch ||
         p->tc_y_dtype != y_dtype || !p->status)
         DNB_TRY(build_tc_args(p, &xin, y_nhwc, y_dtype, y_cpitch));
@@ -394,5 +412,16 @@ extern "C" int dnb_conv_plan_check_status(dnb_conv_plan *p)
         cudaMemset(p->status, 0, sizeof(int));
         DNB_FAIL(DNB_ETIMEOUT, "conv: a device-side wait expired (code %d: 101 ring slot free, 102 operands landed, 103 accumulator free, 104 accumulator ready)", v);
     }
+    return DNB_OK;
+}
+
+// Cycle counters of CTA 0 of the tensor-core kernel, accumulated over every launch made while the
+// environment variable DNB_TC_DEBUG had bit 256 set; 16 values, see the P_* slots in conv_tc.cu.
+extern "C" int dnb_conv_plan_cycle_profile(dnb_conv_plan *p, long long *out16)
+{
+    if (!p || !out16) DNB_FAIL(DNB_EINVAL, "cycle profile: null argument");
+    for (int i = 0; i < 16; ++i) out16[i] = 0;
+    if (!p->status) return DNB_OK;
+    DNB_CUDA(cudaMemcpy(out16, reinterpret_cast<long long *>(p->status) + 8, 16 * sizeof(long long), cudaMemcpyDeviceToHost));
     return DNB_OK;
 }

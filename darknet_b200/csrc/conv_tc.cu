@@ -65,14 +65,29 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return done;
 }
 
-// Bounded wait.  Returns false when the wait expired or another role aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+// Bounded wait by ONE polling lane per warp; the result is broadcast to the warp.  Returns false when
+// the wait expired or another role aborted.  Polling goes through shared memory, which the tensor
+// cores read their operands from: one lane per warp polls, with a hardware suspend hint, and waiters
+// that are not latency-critical back off with nanosleep between polls.
+__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+    return done;
+}
+
+// Bounded wait for a loop that a single thread runs (the TMA and MMA roles): no warp traffic at all.
+__device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    long long t0 = clock64();
+    const long long t0 = clock64();
     int spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0xff) == 0) {
+    while (!mbar_try_wait_hint(bar, parity, 1000u)) {
+        if ((++spins & 0x3f) == 0) {
             if (*abort_flag) return false;
             if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
                 *abort_flag = 1;
@@ -82,6 +97,32 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
     return true;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
+                                          unsigned backoff_ns = 0)
+{
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        if (!mbar_try_wait(bar, parity)) {
+            const long long t0 = clock64();
+            int spins = 0;
+            while (!mbar_try_wait_hint(bar, parity, 2000u)) {
+                if (backoff_ns) __nanosleep(backoff_ns);
+                if ((++spins & 0x3f) == 0) {
+                    if (*abort_flag) { ok = 0; break; }
+                    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                        *abort_flag = 1;
+                        atomicCAS(status, 0, code);
+                        ok = 0;
+                        break;
+                    }
+                }
+            }
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
 }
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3)
@@ -110,9 +151,12 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int row_bytes)
     return d;
 }
 
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate, int is_bf16)
+// The operand kind is a template parameter on purpose: with a run-time `if` the compiler predicates BOTH
+// tcgen05.mma instructions, and the predicated-off one still occupies the tensor pipe's issue path.
+template <bool IS_BF16>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
 {
-    if (is_bf16) {
+    if (IS_BF16) {
         asm volatile(
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
@@ -167,16 +211,29 @@ struct TcShared {
 enum { WAIT_EMPTY = 101, WAIT_FULL = 102, WAIT_ACC_EMPTY = 103, WAIT_ACC_FULL = 104 };
 enum { ACT_GENERIC = -1 };
 
+// Cycle accounting of CTA 0 (debug bit 256): slot indices into TcArgs::prof.
+enum { P_TOTAL = 0, P_PROD_WAIT, P_PROD_ISSUE, P_MMA_WAIT_ACC, P_MMA_WAIT_FULL, P_MMA_FENCE, P_MMA_ISSUE, P_MMA_COMMIT,
+       P_EPI_WAIT_ACC, P_EPI_LD, P_EPI_MATH, P_EPI_STORE, P_EPI_ARRIVE, P_KITERS, P_TILES };
+#define PROF_T0() long long pt_ = prof_on ? clock64() : 0
+#define PROF_ADD(slot) do { if (prof_on) { long long n_ = clock64(); pacc[slot] += n_ - pt_; pt_ = n_; } } while (0)
+
+// The 14-way activation switch stays out of line: inlined into the unrolled epilogue it multiplies the
+// kernel's code size, and an epilogue that does not fit the instruction cache starves the MMA warp.
+__device__ __noinline__ float activate_out_of_line(float x, int a) { return activate(x, a); }
+
 template <int ACT>
 __device__ __forceinline__ float act_apply(float x, int runtime_act)
 {
     if (ACT == DNB_LINEAR) return x;
     if (ACT == DNB_LEAKY) return fmaxf(x, 0.1f * x);   // x > 0 ? x : 0.1x
-    if (ACT == DNB_LOGISTIC) return 1.f / (1.f + __expf(-x));
-    return activate(x, runtime_act);
+    return activate_out_of_line(x, runtime_act);
 }
 
-template <int ACT>
+// ACT: activation folded at compile time (DNB_LINEAR, DNB_LEAKY) or ACT_GENERIC (runtime switch).
+// CPC: output columns per staged chunk (16, 32 or 64); OUT_BF16: storage type of the operands and of the
+// NHWC output (bf16 for BF16 plans, f32 with TF32 products otherwise).
+// One staged row is CPC * sizeof(output element) bytes = the swizzle span of the store map.
+template <int ACT, int CPC, bool OUT_BF16>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ TcArgs a)
 {
@@ -186,12 +243,17 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     const uint32_t stage_bytes = a.a_bytes + a.b_bytes;
     uint8_t *after_ring = smem_raw + (ring - smem_u32(smem_raw)) + (size_t)a.stages * stage_bytes;
     uint8_t *stage_out = after_ring;                                  // 2 x 128 rows x store_row_bytes
-    float *s_scale = reinterpret_cast<float *>(after_ring + 2 * 128 * a.store_row_bytes);
-    float *s_shift = s_scale + a.n_tot;
-    TcShared *sh = reinterpret_cast<TcShared *>(s_shift + a.n_tot);
+    float *s_scale = reinterpret_cast<float *>(after_ring + 2 * 128 * (CPC * (OUT_BF16 ? 2 : 4)));
+    float *s_shift = s_scale + a.n_tot + 64;
+    TcShared *sh = reinterpret_cast<TcShared *>(s_shift + a.n_tot + 64);
     volatile int *abort_flag = &sh->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool prof_on = (a.debug & 256) && blockIdx.x == 0 && (threadIdx.x == 0 || threadIdx.x == 32 || threadIdx.x == 64);
+    long long pacc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) pacc[i] = 0;
+    const long long kernel_t0 = clock64();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
@@ -211,7 +273,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // per-filter epilogue vectors, once per CTA (zero beyond the layer's filters)
-    for (int i = threadIdx.x; i < a.n_tot; i += TC_THREADS) {
+    for (int i = threadIdx.x; i < a.n_tot + 64; i += TC_THREADS) {
         s_scale[i] = i < a.n_pad ? __ldg(a.ep.scale + i) : 0.f;
         s_shift[i] = i < a.n_pad ? __ldg(a.ep.shift + i) : 0.f;
     }
@@ -220,181 +282,242 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
 
-    const int k_iters = a.taps * a.c_blocks;
-    const int ptiles_wh = a.tiles_w * a.tiles_h;
+    // Kernel parameters live in the constant bank, and every asm statement below is a compiler memory
+    // barrier: anything read through `a` inside a loop would be re-fetched each iteration.  The loops
+    // therefore work on register copies only.
+    const int taps = a.taps, c_blocks = a.c_blocks, k_iters = taps * c_blocks;
+    const int n_tiles = a.n_tiles, total_tiles = a.total_tiles, stages = a.stages, bn = a.bn, bk = a.bk;
+    const int tiles_w = a.tiles_w, tiles_h = a.tiles_h, ptiles_wh = tiles_w * tiles_h;
+    const int wt = a.wt, ht = a.ht, bt = a.bt, row_bytes = a.row_bytes;
+    const uint32_t a_bytes = a.a_bytes;
+    const int grid_stride = gridDim.x;
 
     if (warp == 0) {
         // ---------------- TMA producer
+        const int ksize = a.g.size, cstride = a.g.stride, cpad = a.g.pad;
+        const uint32_t tx_bytes = 128u * row_bytes + (uint32_t)bn * row_bytes;
+        const CUtensorMap *maps = a.tmx;
+        const CUtensorMap *wmap = &a.tmw;
+        int *status = a.status;
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x) {
-            const int nt = tile % a.n_tiles, pt = tile / a.n_tiles;
-            const int ow0 = (pt % a.tiles_w) * a.wt;
-            const int oh0 = ((pt / a.tiles_w) % a.tiles_h) * a.ht;
-            const int b0 = (pt / ptiles_wh) * a.bt;
-            for (int tap = 0; tap < a.taps && ok; ++tap) {
-                const int kh = tap / a.g.size, kw = tap - kh * a.g.size;
+        // one thread runs the whole loop; the other lanes wait at the __syncwarp below
+        const int dbg = a.debug;
+        for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok && !(dbg & 2); tile += grid_stride) {
+            const int nt = tile % n_tiles, pt = tile / n_tiles;
+            const int ow0 = (pt % tiles_w) * wt;
+            const int oh0 = ((pt / tiles_w) % tiles_h) * ht;
+            const int b0 = (pt / ptiles_wh) * bt;
+            const int n0 = nt * bn;
+            int kh = 0, kw = 0;
+            for (int tap = 0; tap < taps && ok; ++tap) {
                 // input row = oh*stride + kh - pad = stride*(oh + q) + parity
-                const int dh = kh - a.g.pad, dw = kw - a.g.pad;
-                const int ph = ((dh % a.g.stride) + a.g.stride) % a.g.stride, qh = (dh - ph) / a.g.stride;
-                const int pw = ((dw % a.g.stride) + a.g.stride) % a.g.stride, qw = (dw - pw) / a.g.stride;
-                const CUtensorMap *mx = &a.tmx[ph * a.g.stride + pw];
-                for (int cb = 0; cb < a.c_blocks; ++cb) {
-                    ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, a.status, WAIT_EMPTY);
-                    ok = __all_sync(0xffffffffu, ok);
+                const int dh = kh - cpad, dw = kw - cpad;
+                int ph = 0, qh = dh, pw = 0, qw = dw;
+                if (cstride == 2) { ph = dh & 1; qh = (dh - ph) >> 1; pw = dw & 1; qw = (dw - pw) >> 1; }
+                const CUtensorMap *mx = maps + (ph * cstride + pw);
+                for (int cb = 0; cb < c_blocks; ++cb) {
+                    PROF_T0();
+                    ok = mbar_wait_thread(smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, status, WAIT_EMPTY);
+                    PROF_ADD(P_PROD_WAIT);
                     if (!ok) break;
-                    if (lane == 0) {
+                    {
                         const uint32_t bar = smem_u32(&sh->full[stage]);
-                        const uint32_t sa = ring + stage * stage_bytes, sb = sa + a.a_bytes;
-                        mbar_expect_tx(bar, 128u * a.row_bytes + (uint32_t)a.bn * a.row_bytes);
-                        tma_load_4d(sa, mx, bar, cb * a.bk, ow0 + qw, oh0 + qh, b0);
-                        tma_load_3d(sb, &a.tmw, bar, cb * a.bk, nt * a.bn, tap);
+                        const uint32_t sa = ring + stage * stage_bytes, sb = sa + a_bytes;
+                        if (dbg & 1) { mbar_arrive(bar); }   // experiment: no loads
+                        else {
+                        mbar_expect_tx(bar, tx_bytes);
+                        tma_load_4d(sa, mx, bar, cb * bk, ow0 + qw, oh0 + qh, b0);
+                        tma_load_3d(sb, wmap, bar, cb * bk, n0, tap);
+                        }
                     }
-                    __syncwarp();
-                    if (++stage == a.stages) { stage = 0; phase ^= 1; }
+                    PROF_ADD(P_PROD_ISSUE);
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
+                if (++kw == ksize) { kw = 0; ++kh; }
             }
         }
+        __syncwarp();
     } else if (warp == 1) {
         // ---------------- MMA issuer
-        const uint32_t fmt = a.is_bf16 ? 1u : 2u;  // BF16 : TF32
-        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a.bn >> 3) << 17) | ((128u >> 4) << 24);
-        const int k_steps = a.row_bytes / 32;  // one MMA consumes 32 bytes of K per row
+        constexpr bool is_bf16 = OUT_BF16;       // operands and channels-last output share the storage type
+        const uint32_t fmt = is_bf16 ? 1u : 2u;  // BF16 : TF32
+        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bn >> 3) << 17) | ((128u >> 4) << 24);
+        const int k_steps = row_bytes / 32;  // one MMA consumes 32 bytes of K per row
+        // descriptor of ring slot 0; slot s adds s * stage_bytes / 16 to the address field
+        const uint64_t da0 = make_smem_desc(ring, row_bytes), db0 = make_smem_desc(ring + a_bytes, row_bytes);
+        const uint32_t slot_step = stage_bytes >> 4;
+        int *status = a.status;
         int stage = 0;
         uint32_t phase = 0;
         int it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++it) {
+        const int dbg = a.debug;
+        for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok; tile += grid_stride, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            ok = mbar_wait(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1, abort_flag, a.status, WAIT_ACC_EMPTY);
-            ok = __all_sync(0xffffffffu, ok);
+            PROF_T0();
+            ok = mbar_wait_thread(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1, abort_flag, status, WAIT_ACC_EMPTY);
+            PROF_ADD(P_MMA_WAIT_ACC);
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * 256;
             for (int ki = 0; ki < k_iters; ++ki) {
-                ok = mbar_wait(smem_u32(&sh->full[stage]), phase, abort_flag, a.status, WAIT_FULL);
-                ok = __all_sync(0xffffffffu, ok);
+                pt_ = prof_on ? clock64() : 0;
+                if (!(dbg & 2)) ok = mbar_wait_thread(smem_u32(&sh->full[stage]), phase, abort_flag, status, WAIT_FULL);
+                PROF_ADD(P_MMA_WAIT_FULL);
                 if (!ok) break;
-                tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t sa = ring + stage * stage_bytes, sb = sa + a.a_bytes;
-                    const uint64_t da = make_smem_desc(sa, a.row_bytes), db = make_smem_desc(sb, a.row_bytes);
-                    for (int k = 0; k < k_steps; ++k)
-                        umma(d_tmem, da + 2 * k, db + 2 * k, idesc, (ki | k) != 0, a.is_bf16);
+                if (!(dbg & 4)) tc_fence_after();
+                PROF_ADD(P_MMA_FENCE);
+                {
+                    const uint64_t da = da0 + (uint64_t)(stage * slot_step), db = db0 + (uint64_t)(stage * slot_step);
+                    if (k_steps == 4) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) umma<is_bf16>(d_tmem, da + 2 * k, db + 2 * k, idesc, (ki | k) != 0);
+                    } else {
+                        for (int k = 0; k < k_steps; ++k) umma<is_bf16>(d_tmem, da + 2 * k, db + 2 * k, idesc, (ki | k) != 0);
+                    }
+                    PROF_ADD(P_MMA_ISSUE);
                     umma_commit(smem_u32(&sh->empty[stage]));  // frees the stage when these MMAs retire
                     if (ki == k_iters - 1) umma_commit(smem_u32(&sh->acc_full[acc]));
+                    PROF_ADD(P_MMA_COMMIT);
+                    pacc[P_KITERS] += 1;
                 }
-                __syncwarp();
-                if (++stage == a.stages) { stage = 0; phase ^= 1; }
+                if (++stage == stages) { stage = 0; phase ^= 1; }
             }
         }
+        __syncwarp();
     } else {
         // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31
         const int quarter = warp & 3;
         const int m = quarter * 32 + lane;  // pixel index inside the tile = TMEM lane = staging row
-        const int wl = m % a.wt, hl = (m / a.wt) % a.ht, bl = m / (a.wt * a.ht);
-        const ConvGeom &g = a.g;
+        const int wl = m % wt, hl = (m / wt) % ht, bl = m / (wt * ht);
+        const ConvGeom g = a.g;   // register copy
+        void *const y_nhwc = a.y_nhwc;
+        float *const y_nchw = a.y_nchw;
+        const int runtime_act = a.ep.activation, do_round = a.ep.round_tf32;
+        const CUtensorMap *ymap = &a.tmy;
+        int *status = a.status;
         const bool store_thread = threadIdx.x == 64;
-        const bool out_bf16 = a.y_dtype == DNB_BF16;
-        const int srb = a.store_row_bytes;                       // bytes of one staged row = swizzle span
-        const int cols_per_chunk = srb / (out_bf16 ? 2 : 4);
-        const int q_mask = srb / 16 - 1;
+        constexpr bool out_bf16 = OUT_BF16;
+        constexpr int srb = CPC * (OUT_BF16 ? 2 : 4);            // bytes of one staged row = swizzle span
+        constexpr int cols_per_chunk = CPC;
+        constexpr int q_mask = srb / 16 - 1;
         const int q_xor = (m >> (srb == 128 ? 0 : (srb == 64 ? 1 : 2))) & q_mask;   // 16-byte chunk swizzle of row m
         uint32_t chunk_count = 0;
         int it = 0;
-        for (int tile = blockIdx.x; tile < a.total_tiles; tile += gridDim.x, ++it) {
+        for (int tile = blockIdx.x; tile < total_tiles; tile += grid_stride, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            const int nt = tile % a.n_tiles, pt = tile / a.n_tiles;
-            const int ow0 = (pt % a.tiles_w) * a.wt, oh0 = ((pt / a.tiles_w) % a.tiles_h) * a.ht, b0 = (pt / ptiles_wh) * a.bt;
+            const int nt = tile % n_tiles, pt = tile / n_tiles;
+            const int ow0 = (pt % tiles_w) * wt, oh0 = ((pt / tiles_w) % tiles_h) * ht, b0 = (pt / ptiles_wh) * bt;
             const int ow = ow0 + wl, oh = oh0 + hl, b = b0 + bl;
             const bool pix_ok = ow < g.out_w && oh < g.out_h && b < g.batch;
 
-            mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, abort_flag, a.status, WAIT_ACC_FULL);
+            PROF_T0();
+            mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, abort_flag, status, WAIT_ACC_FULL, 32);
             epilogue_bar();                 // all four warps agree on the abort flag from here
+            PROF_ADD(P_EPI_WAIT_ACC);
+            pacc[P_TILES] += 1;
             if (*abort_flag) break;
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
-            for (int c0 = 0; c0 < a.bn; c0 += cols_per_chunk) {
-                uint8_t *row = nullptr;
-                if (a.y_nhwc) {
-                    const uint32_t buf = chunk_count & 1;
-                    if (store_thread && chunk_count >= 2) tma_store_wait_read1();   // the store that last read this buffer is done
-                    epilogue_bar();
-                    row = stage_out + (size_t)buf * 128 * srb + (size_t)m * srb;
-                }
-                for (int p0 = 0; p0 < cols_per_chunk; p0 += 16) {
-                    const int j0 = c0 + p0;            // first column of this piece inside the tile
-                    float v[16];
-                    if (j0 < a.bn) {
-                        uint32_t r[16];
-                        tmem_ld16(t_row + j0, r);
-                        tmem_ld_wait();
-                        const int nl = nt * a.bn + j0;  // first filter of this piece
-                        const float4 *sc4 = reinterpret_cast<const float4 *>(s_scale + nl);
-                        const float4 *sf4 = reinterpret_cast<const float4 *>(s_shift + nl);
+            // One staged chunk of CPC columns per iteration: CPC/16 TMEM loads in flight, one wait, the
+            // arithmetic, the staged row, the store.  The loop is deliberately NOT unrolled: its body has to
+            // stay resident in the instruction cache next to the MMA warp's loop.
+            const size_t plane = (size_t)g.out_h * g.out_w;
+            const int dbg_e = a.debug;   // experiment bits: 8 skip the whole drain, 16 skip TMEM loads, 32 skip stores
+#pragma unroll 1
+            for (int c0 = 0; c0 < ((dbg_e & 8) ? 0 : bn); c0 += CPC) {
+                uint32_t r[CPC];
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const float4 sc = sc4[q], sf = sf4[q];
-                            const float scv[4] = {sc.x, sc.y, sc.z, sc.w}, sfv[4] = {sf.x, sf.y, sf.z, sf.w};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const int j = 4 * q + e;
-                                float t = act_apply<ACT>(fmaf(__uint_as_float(r[j]), scv[e], sfv[e]), a.ep.activation);
-                                if (a.ep.round_tf32) t = round_tf32(t);
-                                v[j] = (nl + j < g.n) ? t : 0.f;
-                            }
-                        }
+                for (int u = 0; u < CPC / 16; ++u) {
+                    if (c0 + 16 * u < bn && !(dbg_e & 16)) {
+                        tmem_ld16(t_row + c0 + 16 * u, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * u]));
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                    }
-                    if (row) {
-                        if (!out_bf16) {
-                            const int qb = p0 / 4;     // first 16-byte chunk of this piece in the row
-#pragma unroll
-                            for (int q = 0; q < 4; ++q)
-                                *reinterpret_cast<float4 *>(row + (((qb + q) ^ q_xor) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                        } else {
-                            const int qb = p0 / 8;
-#pragma unroll
-                            for (int q = 0; q < 2; ++q) {
-                                __align__(16) __nv_bfloat16 hv[8];
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) hv[j] = __float2bfloat16_rn(v[8 * q + j]);
-                                *reinterpret_cast<uint4 *>(row + (((qb + q) ^ q_xor) << 4)) = *reinterpret_cast<uint4 *>(hv);
-                            }
-                        }
-                    }
-                    if (a.y_nchw && pix_ok && j0 < a.bn) {
-                        const int n0 = nt * a.bn + j0;
-                        const size_t plane = (size_t)g.out_h * g.out_w;
-                        float *dst = a.y_nchw + ((size_t)b * g.n + n0) * plane + (size_t)oh * g.out_w + ow;
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (n0 + j < g.n) dst[j * plane] = v[j];
+                        for (int j = 0; j < 16; ++j) r[16 * u + j] = 0u;
                     }
                 }
-                if (a.y_nhwc) {
-                    fence_async_smem();            // staged rows visible to the TMA unit
-                    epilogue_bar();
-                    if (store_thread) {
-                        // the TMA unit clips the box at the tensor's extents: ragged tiles need no predicates
-                        tma_store_4d(&a.tmy, smem_u32(stage_out + (size_t)(chunk_count & 1) * 128 * srb), nt * a.bn + c0, ow0, oh0, b0);
-                        tma_store_commit();
+                tmem_ld_wait();
+                PROF_ADD(P_EPI_LD);
+                // epilogue arithmetic in place: r[] becomes the output values (as float bits); the shared
+                // scale / shift copies are zero beyond the layer's filters and padded by 64 entries
+                const int nl0 = nt * bn + c0;                 // first filter of this chunk
+                const int nvalid = min(bn - c0, g.n - nl0);   // columns of this chunk that are real filters
+                const float4 *sc4 = reinterpret_cast<const float4 *>(s_scale + nl0);
+                const float4 *sf4 = reinterpret_cast<const float4 *>(s_shift + nl0);
+#pragma unroll
+                for (int q = 0; q < CPC / 4; ++q) {
+                    const float4 sc = sc4[q], sf = sf4[q];
+                    const float scv[4] = {sc.x, sc.y, sc.z, sc.w}, sfv[4] = {sf.x, sf.y, sf.z, sf.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = 4 * q + e;
+                        float t = act_apply<ACT>(fmaf(__uint_as_float(r[j]), scv[e], sfv[e]), runtime_act);
+                        if (do_round) t = round_tf32(t);
+                        r[j] = __float_as_uint(j < nvalid ? t : 0.f);
                     }
-                    ++chunk_count;
                 }
+                PROF_ADD(P_EPI_MATH);
+                const uint32_t buf = chunk_count & 1;
+                if (store_thread && chunk_count >= 2) tma_store_wait_read1();   // the store that last read this buffer is done
+                epilogue_bar();
+                uint8_t *row = stage_out + (size_t)buf * 128 * srb + (size_t)m * srb;
+                if (!out_bf16) {
+#pragma unroll
+                    for (int q = 0; q < srb / 16; ++q)         // 16-byte pieces of 4 floats
+                        *reinterpret_cast<uint4 *>(row + ((q ^ q_xor) << 4)) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < srb / 16; ++q) {       // 16-byte pieces of 8 bf16
+                        const int j = 8 * q;
+                        uint4 pk;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                        pk.x = *reinterpret_cast<uint32_t *>(&h0); pk.y = *reinterpret_cast<uint32_t *>(&h1);
+                        pk.z = *reinterpret_cast<uint32_t *>(&h2); pk.w = *reinterpret_cast<uint32_t *>(&h3);
+                        *reinterpret_cast<uint4 *>(row + ((q ^ q_xor) << 4)) = pk;
+                    }
+                }
+                fence_async_smem();            // staged rows visible to the TMA unit
+                epilogue_bar();
+                if (store_thread) {
+                    // the TMA unit clips the box at the tensor's extents: ragged tiles need no predicates
+                    if (y_nhwc && !(dbg_e & 32)) tma_store_4d(ymap, smem_u32(stage_out + (size_t)buf * 128 * srb), nl0, ow0, oh0, b0);
+                    tma_store_commit();
+                }
+                if (y_nchw && pix_ok) {
+                    // Darknet-layout copy: this thread's pixel, one filter plane per staged column, read
+                    // back from the staged row (a rolled loop: registers cannot be indexed dynamically)
+                    float *dst = y_nchw + ((size_t)b * g.n + nl0) * plane + (size_t)oh * g.out_w + ow;
+                    const int cols = min(CPC, g.n - nl0);
+                    for (int j = 0; j < cols; ++j) {
+                        float v;
+                        if (!out_bf16) v = *reinterpret_cast<const float *>(row + ((((j >> 2) ^ q_xor) << 4) | ((j & 3) << 2)));
+                        else v = __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(row + ((((j >> 3) ^ q_xor) << 4) | ((j & 7) << 1))));
+                        dst[(size_t)j * plane] = v;
+                    }
+                }
+                ++chunk_count;
+                PROF_ADD(P_EPI_STORE);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[acc]));
+            PROF_ADD(P_EPI_ARRIVE);
         }
         if (store_thread) tma_store_wait_all();
     }
 
+    if (prof_on) {   // three threads of CTA 0 own disjoint slots
+        pacc[P_TOTAL] = threadIdx.x == 0 ? clock64() - kernel_t0 : 0;
+        for (int i = 0; i < 16; ++i)
+            if (pacc[i]) a.prof[i] += pacc[i];
+    }
     // ---------------- teardown (also the abort path)
     if (*abort_flag) {   // give loads that are still in flight time to land before shared memory is released
         const long long t0 = clock64();
@@ -411,7 +534,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
 // ------------------------------------------------------------------ host side
 size_t conv_tc_fixed_smem(int store_row_bytes, int n_tot)
 {
-    return 1024 + 2 * 128 * (size_t)store_row_bytes + 2 * sizeof(float) * (size_t)n_tot + sizeof(TcShared) + 64;
+    return 1024 + 2 * 128 * (size_t)store_row_bytes + 2 * sizeof(float) * ((size_t)n_tot + 64) + sizeof(TcShared) + 64;
 }
 
 size_t conv_tc_smem_bytes(const TcArgs &a)
@@ -429,25 +552,35 @@ int conv_tc_max_smem()
 
 int launch_conv_tc(const TcArgs &a, cudaStream_t s)
 {
-    static thread_local int configured_for = -1;
     const size_t smem = conv_tc_smem_bytes(a);
-    int dev = 0;
-    DNB_CUDA(cudaGetDevice(&dev));
-    if (configured_for != dev) {
-        const int m = conv_tc_max_smem();
-        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<DNB_LINEAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, m));
-        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<DNB_LEAKY>, cudaFuncAttributeMaxDynamicSharedMemorySize, m));
-        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<DNB_LOGISTIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, m));
-        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<ACT_GENERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, m));
-        configured_for = dev;
-    }
-    int grid = a.total_tiles < sm_count() ? a.total_tiles : sm_count();
+    const bool obf = a.is_bf16 != 0;
+    const int cpc = a.store_row_bytes / (obf ? 2 : 4);
+    if (cpc != 16 && cpc != 32 && cpc != 64) DNB_FAIL(DNB_EINVAL, "conv_tc: staged row of %d bytes", a.store_row_bytes);
+    const int grid = a.total_tiles < sm_count() ? a.total_tiles : sm_count();
+    const int max_smem = conv_tc_max_smem();
+    // one instantiation per (activation, columns per staged chunk, output type); the opt-in for large
+    // dynamic shared memory is per kernel symbol and cheap, so it is set on every launch
+#define DNB_TC_LAUNCH(ACT, CPC, OBF)                                                                                       \
+    do {                                                                                                                   \
+        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<ACT, CPC, OBF>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)); \
+        conv_tc_kernel<ACT, CPC, OBF><<<grid, TC_THREADS, smem, s>>>(a);                                                  \
+    } while (0)
+#define DNB_TC_LAUNCH_ACT(ACT)                                        \
+    do {                                                              \
+        if (!obf && cpc == 32) DNB_TC_LAUNCH(ACT, 32, false);         \
+        else if (!obf && cpc == 16) DNB_TC_LAUNCH(ACT, 16, false);    \
+        else if (obf && cpc == 64) DNB_TC_LAUNCH(ACT, 64, true);      \
+        else if (obf && cpc == 32) DNB_TC_LAUNCH(ACT, 32, true);      \
+        else if (obf && cpc == 16) DNB_TC_LAUNCH(ACT, 16, true);      \
+        else DNB_FAIL(DNB_EINVAL, "conv_tc: no kernel for %d columns per chunk", cpc); \
+    } while (0)
     switch (a.ep.activation) {
-    case DNB_LINEAR: conv_tc_kernel<DNB_LINEAR><<<grid, TC_THREADS, smem, s>>>(a); break;
-    case DNB_LEAKY: conv_tc_kernel<DNB_LEAKY><<<grid, TC_THREADS, smem, s>>>(a); break;
-    case DNB_LOGISTIC: conv_tc_kernel<DNB_LOGISTIC><<<grid, TC_THREADS, smem, s>>>(a); break;
-    default: conv_tc_kernel<ACT_GENERIC><<<grid, TC_THREADS, smem, s>>>(a); break;
+    case DNB_LINEAR: DNB_TC_LAUNCH_ACT(DNB_LINEAR); break;
+    case DNB_LEAKY: DNB_TC_LAUNCH_ACT(DNB_LEAKY); break;
+    default: DNB_TC_LAUNCH_ACT(ACT_GENERIC); break;
     }
+#undef DNB_TC_LAUNCH_ACT
+#undef DNB_TC_LAUNCH
     DNB_LAUNCH_CHECK("conv_tc");
     return DNB_OK;
 }

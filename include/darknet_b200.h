@@ -142,6 +142,16 @@ int dnb_conv_xnor_accumulate(dnb_conv_plan *plan, const dnb_tensor *x, int32_t *
  * counterpart (its kernels have no waits). */
 int dnb_conv_plan_check_status(dnb_conv_plan *plan);
 
+/* Diagnostics: cycle counters of thread block 0 of the tensor-core kernel,
+ * accumulated over the launches made while the environment variable
+ * DNB_TC_DEBUG had bit 256 set when the plan first ran.  out16[0] total cycles,
+ * [1..2] loader warp (waiting for a free ring slot, issuing copies), [3..7] MMA
+ * warp (waiting for a free accumulator, for operands, fence, issuing MMAs,
+ * commits), [8..12] epilogue (waiting for the accumulator, TMEM loads,
+ * arithmetic, staging + stores, release), [13] ring iterations, [14] tiles.
+ * The reference has no counterpart. */
+int dnb_conv_plan_cycle_profile(dnb_conv_plan *plan, long long *out16);
+
 /* Name of the kernel a plan dispatches to ("tc_tf32", "tc_bf16", "direct_fp32",
  * "xnor_popc"); static storage. */
 const char *dnb_conv_plan_kernel(const dnb_conv_plan *plan);
