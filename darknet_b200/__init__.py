@@ -61,7 +61,6 @@ SIGNATURES = {
     "dnb_conv_xnor_accumulate": (_I, [_P, _TP, _P, _P]),
     "dnb_conv_plan_check_status": (_I, [_P]),
     "dnb_conv_plan_kernel": (C.c_char_p, [_P]),
-    "dnb_conv_plan_cycle_profile": (_I, [_P, C.POINTER(C.c_longlong)]),
     "dnb_maxpool_forward": (_I, [_TP, _TP, _I, _I, _I, _P]),
     "dnb_upsample_forward": (_I, [_TP, _TP, _I, _F, _P]),
     "dnb_shortcut_forward": (_I, [_TP, _TP, _TP, _F, _F, _I, _P]),

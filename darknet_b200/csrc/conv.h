@@ -47,9 +47,6 @@ struct alignas(64) TcArgs {
     int y_dtype, y_cpitch;
     float *y_nchw;
     int *status;          // device word: 0, or the code of the wait that expired
-    long long *prof;      // 16 cycle counters of CTA 0, accumulated when debug bit 256 is set
-    int debug;            // experiments: 1 skip activation loads, 2 skip weight loads, 4 skip MMAs, 8 skip TMEM loads,
-                          // 16 skip output stores, 32 skip output staging
     ConvGeom g;
     ConvEpilogue ep;
 };

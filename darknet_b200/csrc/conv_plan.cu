@@ -65,7 +65,7 @@ extern "C" int dnb_conv_plan_create(const dnb_conv_desc *d, int mode, dnb_conv_p
     p->npg_pad = round_up(d->n / d->groups, 32);
     p->cwords = (d->c + 31) / 32;
     if (d->xnor) p->kernel = K_XNOR;
-    else if (mode == DNB_MODE_FP32 || d->groups != 1 || d->c < 8) p->kernel = K_DIRECT;
+    else if (mode == DNB_MODE_FP32 || d->groups != 1) p->kernel = K_DIRECT;
     else p->kernel = mode == DNB_MODE_BF16 ? K_TC_BF16 : K_TC_TF32;
     cudaGetDevice(&p->device);
     *out = p;
@@ -190,11 +190,6 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     a.c_blocks = (p->c_pad + a.bk - 1) / a.bk;
     a.taps = g.size * g.size;
     pick_pixel_tile(g, &a.wt, &a.ht, &a.bt);
-    if (const char *e = getenv("DNB_TC_TILE")) {  // experiment: "wt,ht,bt"
-        int w_ = 0, h_ = 0, b_ = 0;
-        if (sscanf(e, "%d,%d,%d", &w_, &h_, &b_) == 3 && w_ * h_ * b_ == 128) { a.wt = w_; a.ht = h_; a.bt = b_; }
-    }
-    a.debug = getenv("DNB_TC_DEBUG") ? atoi(getenv("DNB_TC_DEBUG")) : 0;
     a.tiles_w = (g.out_w + a.wt - 1) / a.wt;
     a.tiles_h = (g.out_h + a.ht - 1) / a.ht;
     a.tiles_b = (g.batch + a.bt - 1) / a.bt;
@@ -250,11 +245,10 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     a.store_row_bytes = srb;
     a.g = g;
     if (!p->status) {
-        DNB_CUDA(cudaMalloc((void **)&p->status, 32 * sizeof(long long)));   // status word + 16 cycle counters
-        DNB_CUDA(cudaMemset(p->status, 0, 32 * sizeof(long long)));
+        DNB_CUDA(cudaMalloc((void **)&p->status, sizeof(int)));
+        DNB_CUDA(cudaMemset(p->status, 0, sizeof(int)));
     }
     a.status = p->status;
-    a.prof = reinterpret_cast<long long *>(p->status) + 8;
 
     // activation maps: lattice (ph, pw) of the input holds rows ph, ph+stride, ... and columns pw, pw+stride, ...
     const size_t pix_bytes = (size_t)x->cpitch * es;
@@ -412,16 +406,5 @@ extern "C" int dnb_conv_plan_check_status(dnb_conv_plan *p)
         cudaMemset(p->status, 0, sizeof(int));
         DNB_FAIL(DNB_ETIMEOUT, "conv: a device-side wait expired (code %d: 101 ring slot free, 102 operands landed, 103 accumulator free, 104 accumulator ready)", v);
     }
-    return DNB_OK;
-}
-
-// Cycle counters of CTA 0 of the tensor-core kernel, accumulated over every launch made while the
-// environment variable DNB_TC_DEBUG had bit 256 set; 16 values, see the P_* slots in conv_tc.cu.
-extern "C" int dnb_conv_plan_cycle_profile(dnb_conv_plan *p, long long *out16)
-{
-    if (!p || !out16) DNB_FAIL(DNB_EINVAL, "cycle profile: null argument");
-    for (int i = 0; i < 16; ++i) out16[i] = 0;
-    if (!p->status) return DNB_OK;
-    DNB_CUDA(cudaMemcpy(out16, reinterpret_cast<long long *>(p->status) + 8, 16 * sizeof(long long), cudaMemcpyDeviceToHost));
     return DNB_OK;
 }

@@ -211,11 +211,6 @@ struct TcShared {
 enum { WAIT_EMPTY = 101, WAIT_FULL = 102, WAIT_ACC_EMPTY = 103, WAIT_ACC_FULL = 104 };
 enum { ACT_GENERIC = -1 };
 
-// Cycle accounting of CTA 0 (debug bit 256): slot indices into TcArgs::prof.
-enum { P_TOTAL = 0, P_PROD_WAIT, P_PROD_ISSUE, P_MMA_WAIT_ACC, P_MMA_WAIT_FULL, P_MMA_FENCE, P_MMA_ISSUE, P_MMA_COMMIT,
-       P_EPI_WAIT_ACC, P_EPI_LD, P_EPI_MATH, P_EPI_STORE, P_EPI_ARRIVE, P_KITERS, P_TILES };
-#define PROF_T0() long long pt_ = prof_on ? clock64() : 0
-#define PROF_ADD(slot) do { if (prof_on) { long long n_ = clock64(); pacc[slot] += n_ - pt_; pt_ = n_; } } while (0)
 
 // The 14-way activation switch stays out of line: inlined into the unrolled epilogue it multiplies the
 // kernel's code size, and an epilogue that does not fit the instruction cache starves the MMA warp.
@@ -249,11 +244,6 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     volatile int *abort_flag = &sh->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool prof_on = (a.debug & 256) && blockIdx.x == 0 && (threadIdx.x == 0 || threadIdx.x == 32 || threadIdx.x == 64);
-    long long pacc[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) pacc[i] = 0;
-    const long long kernel_t0 = clock64();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
@@ -293,18 +283,17 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     const int grid_stride = gridDim.x;
 
     if (warp == 0) {
-        // ---------------- TMA producer
+        // ---------------- TMA producer: one thread runs the loop, the other lanes wait at the __syncwarp
         const int ksize = a.g.size, cstride = a.g.stride, cpad = a.g.pad;
         const uint32_t tx_bytes = 128u * row_bytes + (uint32_t)bn * row_bytes;
         const CUtensorMap *maps = a.tmx;
         const CUtensorMap *wmap = &a.tmw;
         int *status = a.status;
+        const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        // one thread runs the whole loop; the other lanes wait at the __syncwarp below
-        const int dbg = a.debug;
-        for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok && !(dbg & 2); tile += grid_stride) {
+        for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok; tile += grid_stride) {
             const int nt = tile % n_tiles, pt = tile / n_tiles;
             const int ow0 = (pt % tiles_w) * wt;
             const int oh0 = ((pt / tiles_w) % tiles_h) * ht;
@@ -318,21 +307,13 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 if (cstride == 2) { ph = dh & 1; qh = (dh - ph) >> 1; pw = dw & 1; qw = (dw - pw) >> 1; }
                 const CUtensorMap *mx = maps + (ph * cstride + pw);
                 for (int cb = 0; cb < c_blocks; ++cb) {
-                    PROF_T0();
-                    ok = mbar_wait_thread(smem_u32(&sh->empty[stage]), phase ^ 1, abort_flag, status, WAIT_EMPTY);
-                    PROF_ADD(P_PROD_WAIT);
+                    ok = mbar_wait_thread(empty0 + 8 * stage, phase ^ 1, abort_flag, status, WAIT_EMPTY);
                     if (!ok) break;
-                    {
-                        const uint32_t bar = smem_u32(&sh->full[stage]);
-                        const uint32_t sa = ring + stage * stage_bytes, sb = sa + a_bytes;
-                        if (dbg & 1) { mbar_arrive(bar); }   // experiment: no loads
-                        else {
-                        mbar_expect_tx(bar, tx_bytes);
-                        tma_load_4d(sa, mx, bar, cb * bk, ow0 + qw, oh0 + qh, b0);
-                        tma_load_3d(sb, wmap, bar, cb * bk, n0, tap);
-                        }
-                    }
-                    PROF_ADD(P_PROD_ISSUE);
+                    const uint32_t bar = full0 + 8 * stage;
+                    const uint32_t sa = ring + stage * stage_bytes;
+                    mbar_expect_tx(bar, tx_bytes);
+                    tma_load_4d(sa, mx, bar, cb * bk, ow0 + qw, oh0 + qh, b0);
+                    tma_load_3d(sa + a_bytes, wmap, bar, cb * bk, n0, tap);
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
                 if (++kw == ksize) { kw = 0; ++kh; }
@@ -340,52 +321,47 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         }
         __syncwarp();
     } else if (warp == 1) {
-        // ---------------- MMA issuer
+        // ---------------- MMA issuer: one thread.  Its instruction stream per ring slot has to stay well
+        // below the 4 x 128 cycles the tensor pipe needs for the slot's MMAs, so everything is in registers:
+        // barrier addresses and operand descriptors advance by constants, the accumulator-ready commit
+        // sits after the k loop.
         constexpr bool is_bf16 = OUT_BF16;       // operands and channels-last output share the storage type
         const uint32_t fmt = is_bf16 ? 1u : 2u;  // BF16 : TF32
         const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bn >> 3) << 17) | ((128u >> 4) << 24);
-        const int k_steps = row_bytes / 32;  // one MMA consumes 32 bytes of K per row
-        // descriptor of ring slot 0; slot s adds s * stage_bytes / 16 to the address field
+        const int k_steps = row_bytes / 32;      // one MMA consumes 32 bytes of K per row
         const uint64_t da0 = make_smem_desc(ring, row_bytes), db0 = make_smem_desc(ring + a_bytes, row_bytes);
-        const uint32_t slot_step = stage_bytes >> 4;
+        const uint64_t slot_step = stage_bytes >> 4;   // descriptor address field counts 16-byte units
+        const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
         int *status = a.status;
         int stage = 0;
         uint32_t phase = 0;
+        uint64_t da = da0, db = db0;
         int it = 0;
         bool ok = true;
-        const int dbg = a.debug;
         for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok; tile += grid_stride, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            PROF_T0();
             ok = mbar_wait_thread(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1, abort_flag, status, WAIT_ACC_EMPTY);
-            PROF_ADD(P_MMA_WAIT_ACC);
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * 256;
             for (int ki = 0; ki < k_iters; ++ki) {
-                pt_ = prof_on ? clock64() : 0;
-                if (!(dbg & 2)) ok = mbar_wait_thread(smem_u32(&sh->full[stage]), phase, abort_flag, status, WAIT_FULL);
-                PROF_ADD(P_MMA_WAIT_FULL);
+                ok = mbar_wait_thread(full0 + 8 * stage, phase, abort_flag, status, WAIT_FULL);
                 if (!ok) break;
-                if (!(dbg & 4)) tc_fence_after();
-                PROF_ADD(P_MMA_FENCE);
-                {
-                    const uint64_t da = da0 + (uint64_t)(stage * slot_step), db = db0 + (uint64_t)(stage * slot_step);
-                    if (k_steps == 4) {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) umma<is_bf16>(d_tmem, da + 2 * k, db + 2 * k, idesc, (ki | k) != 0);
-                    } else {
-                        for (int k = 0; k < k_steps; ++k) umma<is_bf16>(d_tmem, da + 2 * k, db + 2 * k, idesc, (ki | k) != 0);
-                    }
-                    PROF_ADD(P_MMA_ISSUE);
-                    umma_commit(smem_u32(&sh->empty[stage]));  // frees the stage when these MMAs retire
-                    if (ki == k_iters - 1) umma_commit(smem_u32(&sh->acc_full[acc]));
-                    PROF_ADD(P_MMA_COMMIT);
-                    pacc[P_KITERS] += 1;
+                tc_fence_after();
+                if (k_steps == 4) {
+                    umma<is_bf16>(d_tmem, da, db, idesc, ki != 0);
+                    umma<is_bf16>(d_tmem, da + 2, db + 2, idesc, 1u);
+                    umma<is_bf16>(d_tmem, da + 4, db + 4, idesc, 1u);
+                    umma<is_bf16>(d_tmem, da + 6, db + 6, idesc, 1u);
+                } else {
+                    for (int k = 0; k < k_steps; ++k) umma<is_bf16>(d_tmem, da + 2 * k, db + 2 * k, idesc, (ki | k) != 0);
                 }
-                if (++stage == stages) { stage = 0; phase ^= 1; }
+                umma_commit(empty0 + 8 * stage);   // frees the slot when these MMAs retire
+                da += slot_step; db += slot_step;
+                if (++stage == stages) { stage = 0; phase ^= 1; da = da0; db = db0; }
             }
+            if (ok) umma_commit(smem_u32(&sh->acc_full[acc]));   // accumulator complete when all MMAs above retire
         }
         __syncwarp();
     } else {
@@ -415,11 +391,8 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             const int ow = ow0 + wl, oh = oh0 + hl, b = b0 + bl;
             const bool pix_ok = ow < g.out_w && oh < g.out_h && b < g.batch;
 
-            PROF_T0();
             mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, abort_flag, status, WAIT_ACC_FULL, 32);
             epilogue_bar();                 // all four warps agree on the abort flag from here
-            PROF_ADD(P_EPI_WAIT_ACC);
-            pacc[P_TILES] += 1;
             if (*abort_flag) break;
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
@@ -427,13 +400,12 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             // arithmetic, the staged row, the store.  The loop is deliberately NOT unrolled: its body has to
             // stay resident in the instruction cache next to the MMA warp's loop.
             const size_t plane = (size_t)g.out_h * g.out_w;
-            const int dbg_e = a.debug;   // experiment bits: 8 skip the whole drain, 16 skip TMEM loads, 32 skip stores
 #pragma unroll 1
-            for (int c0 = 0; c0 < ((dbg_e & 8) ? 0 : bn); c0 += CPC) {
+            for (int c0 = 0; c0 < bn; c0 += CPC) {
                 uint32_t r[CPC];
 #pragma unroll
                 for (int u = 0; u < CPC / 16; ++u) {
-                    if (c0 + 16 * u < bn && !(dbg_e & 16)) {
+                    if (c0 + 16 * u < bn) {
                         tmem_ld16(t_row + c0 + 16 * u, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * u]));
                     } else {
 #pragma unroll
@@ -441,7 +413,6 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                     }
                 }
                 tmem_ld_wait();
-                PROF_ADD(P_EPI_LD);
                 // epilogue arithmetic in place: r[] becomes the output values (as float bits); the shared
                 // scale / shift copies are zero beyond the layer's filters and padded by 64 entries
                 const int nl0 = nt * bn + c0;                 // first filter of this chunk
@@ -460,7 +431,6 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                         r[j] = __float_as_uint(j < nvalid ? t : 0.f);
                     }
                 }
-                PROF_ADD(P_EPI_MATH);
                 const uint32_t buf = chunk_count & 1;
                 if (store_thread && chunk_count >= 2) tma_store_wait_read1();   // the store that last read this buffer is done
                 epilogue_bar();
@@ -487,7 +457,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 epilogue_bar();
                 if (store_thread) {
                     // the TMA unit clips the box at the tensor's extents: ragged tiles need no predicates
-                    if (y_nhwc && !(dbg_e & 32)) tma_store_4d(ymap, smem_u32(stage_out + (size_t)buf * 128 * srb), nl0, ow0, oh0, b0);
+                    if (y_nhwc) tma_store_4d(ymap, smem_u32(stage_out + (size_t)buf * 128 * srb), nl0, ow0, oh0, b0);
                     tma_store_commit();
                 }
                 if (y_nchw && pix_ok) {
@@ -503,21 +473,14 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                     }
                 }
                 ++chunk_count;
-                PROF_ADD(P_EPI_STORE);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[acc]));
-            PROF_ADD(P_EPI_ARRIVE);
         }
         if (store_thread) tma_store_wait_all();
     }
 
-    if (prof_on) {   // three threads of CTA 0 own disjoint slots
-        pacc[P_TOTAL] = threadIdx.x == 0 ? clock64() - kernel_t0 : 0;
-        for (int i = 0; i < 16; ++i)
-            if (pacc[i]) a.prof[i] += pacc[i];
-    }
     // ---------------- teardown (also the abort path)
     if (*abort_flag) {   // give loads that are still in flight time to land before shared memory is released
         const long long t0 = clock64();

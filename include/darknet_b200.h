@@ -123,7 +123,8 @@ int dnb_conv_plan_set_params(dnb_conv_plan *plan, const float *weights, const fl
  * (src/batchnorm_layer.c:231-233) or add_bias_gpu (src/blas_kernels.cu:69), and
  * activate_array_gpu (src/activation_kernels.cu:196-200): one launch.
  * x: input, NCHW f32 or NHWC (f32 for TF32/FP32/xnor plans, bf16 for BF16 plans).
- * y: output, NCHW f32 or NHWC (f32 or bf16).  y2: optional second copy of the
+ * y: output, NCHW f32 or NHWC in the plan's storage type (f32, or bf16 for BF16
+ * plans).  y2: optional second copy of the
  * output in the other layout (NULL for none).  stream: a cudaStream_t (NULL =
  * default stream). */
 int dnb_conv_forward(dnb_conv_plan *plan, const dnb_tensor *x, const dnb_tensor *y,
@@ -141,16 +142,6 @@ int dnb_conv_xnor_accumulate(dnb_conv_plan *plan, const dnb_tensor *x, int32_t *
  * kernel then left early and its output is incomplete.  The reference has no
  * counterpart (its kernels have no waits). */
 int dnb_conv_plan_check_status(dnb_conv_plan *plan);
-
-/* Diagnostics: cycle counters of thread block 0 of the tensor-core kernel,
- * accumulated over the launches made while the environment variable
- * DNB_TC_DEBUG had bit 256 set when the plan first ran.  out16[0] total cycles,
- * [1..2] loader warp (waiting for a free ring slot, issuing copies), [3..7] MMA
- * warp (waiting for a free accumulator, for operands, fence, issuing MMAs,
- * commits), [8..12] epilogue (waiting for the accumulator, TMEM loads,
- * arithmetic, staging + stores, release), [13] ring iterations, [14] tiles.
- * The reference has no counterpart. */
-int dnb_conv_plan_cycle_profile(dnb_conv_plan *plan, long long *out16);
 
 /* Name of the kernel a plan dispatches to ("tc_tf32", "tc_bf16", "direct_fp32",
  * "xnor_popc"); static storage. */
