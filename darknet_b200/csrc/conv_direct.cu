@@ -98,7 +98,7 @@ conv_direct_kernel(DirectArgs a)
         float v = 0.f;
         if (f0 + j < npg) {
             v = acc[j] * __ldg(a.ep.scale + n0 + j) + __ldg(a.ep.shift + n0 + j);
-            v = activate(v, a.ep.activation);
+            v = activate_fast(v, a.ep.activation);
             if (a.ep.round_tf32) v = round_tf32(v);
         }
         out_s[threadIdx.x][j] = v;
@@ -143,6 +143,121 @@ conv_direct_kernel(DirectArgs a)
     }
 }
 
+// First-layer specialisation: 3 input channels, 3x3, stride 1, pad 1 (the RGB stems of YOLOv3,
+// YOLOv3-tiny and Darknet-19).  Everything is compile-time, so the 36 input values of a thread's two
+// neighbouring output pixels are loaded up front (independent loads in flight instead of one
+// load-use chain per tap) and every broadcast weight load feeds two FMAs.  256 pixels per block.
+constexpr int SPIX = 2;                       // output pixels per thread, adjacent in x
+constexpr int STHREADS = 128;
+
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(STHREADS)
+conv_stem3x3_kernel(DirectArgs a)
+{
+    __shared__ __align__(16) float w_s[27][FB];
+    __shared__ __align__(16) float out_s[STHREADS * SPIX][FB + 4];
+
+    const ConvGeom g = a.g;
+    const int f0 = blockIdx.y * FB;
+    for (int i = threadIdx.x; i < 27 * FB; i += STHREADS) w_s[i / FB][i % FB] = __ldg(a.wpk + (size_t)(i / FB) * a.npg_pad + f0 + (i % FB));
+
+    // pixel pairs never straddle a row: out_w is padded to even per row by the launcher's grid math
+    const int pairs_per_row = (g.out_w + 1) / 2;
+    const long long npairs = (long long)g.batch * g.out_h * pairs_per_row;
+    const long long pair = (long long)blockIdx.x * STHREADS + threadIdx.x;
+    const bool live = pair < npairs;
+    int b = 0, oh = 0, ow = 0;
+    if (live) {
+        ow = (int)(pair % pairs_per_row) * 2;
+        long long t = pair / pairs_per_row;
+        oh = (int)(t % g.out_h);
+        b = (int)(t / g.out_h);
+    }
+    const TX *xb = reinterpret_cast<const TX *>(a.x) + b * a.xs_b;
+    float xv[3][3][4];
+#pragma unroll
+    for (int c = 0; c < 3; ++c)
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int ih = oh + r - 1, iw = ow + q - 1;
+                const bool in = live && ih >= 0 && ih < g.h && iw >= 0 && iw < g.w;
+                xv[c][r][q] = in ? to_float<TX>(xb[c * a.xs_c + ih * a.xs_h + iw * a.xs_w]) : 0.f;
+            }
+    __syncthreads();
+
+    float acc0[FB], acc1[FB];
+#pragma unroll
+    for (int j = 0; j < FB; ++j) { acc0[j] = 0.f; acc1[j] = 0.f; }
+#pragma unroll
+    for (int c = 0; c < 3; ++c)
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+            for (int q = 0; q < 3; ++q) {
+                const float4 *wr = reinterpret_cast<const float4 *>(w_s[(c * 3 + r) * 3 + q]);
+                const float x0 = xv[c][r][q], x1 = xv[c][r][q + 1];
+#pragma unroll
+                for (int v = 0; v < FB / 4; ++v) {
+                    const float4 w4 = wr[v];
+                    acc0[4 * v + 0] = fmaf(x0, w4.x, acc0[4 * v + 0]); acc1[4 * v + 0] = fmaf(x1, w4.x, acc1[4 * v + 0]);
+                    acc0[4 * v + 1] = fmaf(x0, w4.y, acc0[4 * v + 1]); acc1[4 * v + 1] = fmaf(x1, w4.y, acc1[4 * v + 1]);
+                    acc0[4 * v + 2] = fmaf(x0, w4.z, acc0[4 * v + 2]); acc1[4 * v + 2] = fmaf(x1, w4.z, acc1[4 * v + 2]);
+                    acc0[4 * v + 3] = fmaf(x0, w4.w, acc0[4 * v + 3]); acc1[4 * v + 3] = fmaf(x1, w4.w, acc1[4 * v + 3]);
+                }
+            }
+    const int nvalid = min(FB, g.n - f0);
+#pragma unroll
+    for (int j = 0; j < FB; ++j) {
+        float v0 = 0.f, v1 = 0.f;
+        if (j < nvalid) {
+            const float sc = __ldg(a.ep.scale + f0 + j), sh = __ldg(a.ep.shift + f0 + j);
+            v0 = activate_fast(acc0[j] * sc + sh, a.ep.activation);
+            v1 = activate_fast(acc1[j] * sc + sh, a.ep.activation);
+            if (a.ep.round_tf32) { v0 = round_tf32(v0); v1 = round_tf32(v1); }
+        }
+        out_s[2 * threadIdx.x][j] = v0;
+        out_s[2 * threadIdx.x + 1][j] = v1;
+    }
+    __syncthreads();
+
+    // stores: slot s of the block = pair (s / 2), pixel (s % 2); its flat pixel index is computed per slot
+    const long long pair0 = (long long)blockIdx.x * STHREADS;
+    const bool last = f0 + FB >= g.n;
+    const int cols = last ? min(FB, (a.y_nhwc ? a.y_cpitch : g.n) - f0) : nvalid;
+    if (a.y_nhwc) {
+        constexpr int EPV = 16 / sizeof(TY);
+        const int pieces = (cols + EPV - 1) / EPV;    // cpitch and FB are multiples of 8: whole pieces
+        for (int i = threadIdx.x; i < STHREADS * SPIX * pieces; i += STHREADS) {
+            const int slot = i / pieces, q = i - slot * pieces;
+            const long long pr = pair0 + (slot >> 1);
+            if (pr >= npairs) continue;
+            const int pw = (int)(pr % pairs_per_row) * 2 + (slot & 1);
+            if (pw >= g.out_w) continue;
+            const long long rowid = pr / pairs_per_row;   // b * out_h + oh
+            TY *dst = reinterpret_cast<TY *>(a.y_nhwc) + ((size_t)rowid * g.out_w + pw) * a.y_cpitch + f0 + q * EPV;
+            const float *src = &out_s[slot][q * EPV];
+            if (sizeof(TY) == 4) {
+                *reinterpret_cast<float4 *>(dst) = *reinterpret_cast<const float4 *>(src);
+            } else {
+                __align__(16) __nv_bfloat16 h[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) h[e] = __float2bfloat16_rn(src[e]);
+                *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<uint4 *>(h);
+            }
+        }
+    }
+    if (a.y_nchw && live) {
+        const size_t plane = (size_t)g.out_h * g.out_w;
+        float *dst = a.y_nchw + ((size_t)b * g.n + f0) * plane + (size_t)oh * g.out_w + ow;
+        for (int j = 0; j < nvalid; ++j) {
+            dst[j * plane] = out_s[2 * threadIdx.x][j];
+            if (ow + 1 < g.out_w) dst[j * plane + 1] = out_s[2 * threadIdx.x + 1][j];
+        }
+    }
+}
+
 int launch_conv_direct(const DirectArgs &a, cudaStream_t s)
 {
     const ConvGeom &g = a.g;
@@ -152,6 +267,15 @@ int launch_conv_direct(const DirectArgs &a, cudaStream_t s)
     dim3 grid((unsigned)((npix + DTHREADS - 1) / DTHREADS), (unsigned)(g.groups * ((npg + FB - 1) / FB)));
     if (grid.y > 65535) DNB_FAIL(DNB_EUNSUPPORTED, "direct conv: too many filter blocks (%u)", grid.y);
     const bool xb = a.x_dtype == DNB_BF16, yb = a.y_dtype == DNB_BF16;
+    if (g.c == 3 && g.size == 3 && g.stride == 1 && g.pad == 1 && g.groups == 1 && !xb &&
+        (!a.y_nhwc || (a.y_cpitch % 8 == 0))) {
+        const long long npairs = (long long)g.batch * g.out_h * ((g.out_w + 1) / 2);
+        dim3 sgrid((unsigned)((npairs + STHREADS - 1) / STHREADS), (unsigned)((g.n + FB - 1) / FB));
+        if (yb) conv_stem3x3_kernel<float, __nv_bfloat16><<<sgrid, STHREADS, 0, s>>>(a);
+        else conv_stem3x3_kernel<float, float><<<sgrid, STHREADS, 0, s>>>(a);
+        DNB_LAUNCH_CHECK("conv_stem3x3");
+        return DNB_OK;
+    }
     if (!xb && !yb) conv_direct_kernel<float, float><<<grid, DTHREADS, 0, s>>>(a);
     else if (!xb && yb) conv_direct_kernel<float, __nv_bfloat16><<<grid, DTHREADS, 0, s>>>(a);
     else if (xb && !yb) conv_direct_kernel<__nv_bfloat16, float><<<grid, DTHREADS, 0, s>>>(a);

@@ -65,7 +65,7 @@ extern "C" int dnb_conv_plan_create(const dnb_conv_desc *d, int mode, dnb_conv_p
     p->npg_pad = round_up(d->n / d->groups, 32);
     p->cwords = (d->c + 31) / 32;
     if (d->xnor) p->kernel = K_XNOR;
-    else if (mode == DNB_MODE_FP32 || d->groups != 1) p->kernel = K_DIRECT;
+    else if (mode == DNB_MODE_FP32 || d->groups != 1 || d->c < 8) p->kernel = K_DIRECT;
     else p->kernel = mode == DNB_MODE_BF16 ? K_TC_BF16 : K_TC_TF32;
     cudaGetDevice(&p->device);
     *out = p;

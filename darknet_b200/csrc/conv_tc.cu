@@ -212,16 +212,12 @@ enum { WAIT_EMPTY = 101, WAIT_FULL = 102, WAIT_ACC_EMPTY = 103, WAIT_ACC_FULL = 
 enum { ACT_GENERIC = -1 };
 
 
-// The 14-way activation switch stays out of line: inlined into the unrolled epilogue it multiplies the
-// kernel's code size, and an epilogue that does not fit the instruction cache starves the MMA warp.
-__device__ __noinline__ float activate_out_of_line(float x, int a) { return activate(x, a); }
-
 template <int ACT>
 __device__ __forceinline__ float act_apply(float x, int runtime_act)
 {
     if (ACT == DNB_LINEAR) return x;
     if (ACT == DNB_LEAKY) return fmaxf(x, 0.1f * x);   // x > 0 ? x : 0.1x
-    return activate_out_of_line(x, runtime_act);
+    return activate_call(x, runtime_act);   // the 14-way switch, out of line
 }
 
 // ACT: activation folded at compile time (DNB_LINEAR, DNB_LEAKY) or ACT_GENERIC (runtime switch).

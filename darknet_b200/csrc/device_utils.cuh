@@ -43,6 +43,16 @@ __device__ __forceinline__ float activate(float x, int a)
     return 0.f;
 }
 
+// Same function for hot loops: the two common activations inline, the 14-way switch out of line (inlined
+// into an unrolled epilogue it multiplies the code size).
+static __device__ __noinline__ float activate_call(float x, int a) { return activate(x, a); }
+__device__ __forceinline__ float activate_fast(float x, int a)
+{
+    if (a == DNB_LEAKY) return fmaxf(x, 0.1f * x);   // x > 0 ? x : 0.1x
+    if (a == DNB_LINEAR) return x;
+    return activate_call(x, a);
+}
+
 // Round an fp32 value to the nearest TF32 (10-bit mantissa) value, ties away
 // from zero, and return it as fp32 bits with the low 13 mantissa bits clear.
 __device__ __forceinline__ float round_tf32(float x)
