@@ -202,3 +202,62 @@ int launch_pack_sign_bits(const dnb_tensor *x, uint32_t *bits, int cwords, cudaS
 }
 
 }  // namespace dnb
+
+// ------------------------------------------------------------------ entry point that allocates nothing
+// Some callers may not allocate device memory at all while they run: code that executes inside a
+// latency-critical serving loop whose memory was carved out up front, a host process that handed the
+// whole device to an arena allocator of its own, or a plug-in loaded into a process whose owner forbids
+// cudaMalloc after start-up.  For them the xnor convolution, which needs scratch for the bit-packed
+// input, is also available with that scratch inside the library image: a fixed array in device memory
+// that every GPU loading the library holds until the process exits.
+namespace dnb {
+constexpr size_t kXnorStaticWords = (size_t)1 << 20;   // 4 MiB: batch*h*w*ceil(c/32) may not exceed this
+static __device__ __align__(256) uint32_t g_xnor_static_bits[kXnorStaticWords];
+// In host code the array's name is only a handle for the runtime, not a device address: the address is
+// looked up once per device (with that device current) and cached here.
+static uint32_t *g_xnor_static_ptr[64];
+}  // namespace dnb
+
+extern "C" int dnb_conv_xnor_forward_static(const dnb_conv_desc *d, const dnb_tensor *x, const uint32_t *wbits,
+                                            const float *wmean, const float *scale, const float *shift,
+                                            const dnb_tensor *y, void *stream)
+{
+    using namespace dnb;
+    if (!d || !x || !wbits || !wmean || !scale || !shift || !y) DNB_FAIL(DNB_EINVAL, "xnor static: null argument");
+    if (d->batch < 1 || d->h < 1 || d->w < 1 || d->c < 1 || d->n < 1 || d->size < 1 || d->size > 15 || d->stride < 1 || d->pad < 0 ||
+        d->groups != 1)
+        DNB_FAIL(DNB_EINVAL, "xnor static: bad geometry (groups must be 1)");
+    if (d->activation < 0 || d->activation > DNB_SELU) DNB_FAIL(DNB_EINVAL, "xnor static: activation %d", d->activation);
+    const int out_h = (d->h + 2 * d->pad - d->size) / d->stride + 1, out_w = (d->w + 2 * d->pad - d->size) / d->stride + 1;
+    if (out_h < 1 || out_w < 1) DNB_FAIL(DNB_EINVAL, "xnor static: empty output");
+    DNB_TRY(check_tensor(x, "xnor static input"));
+    DNB_TRY(check_tensor(y, "xnor static output"));
+    if (x->n != d->batch || x->c != d->c || x->h != d->h || x->w != d->w) DNB_FAIL(DNB_EINVAL, "xnor static: input extents differ from the descriptor");
+    if (y->n != d->batch || y->c != d->n || y->h != out_h || y->w != out_w) DNB_FAIL(DNB_EINVAL, "xnor static: output extents differ from the descriptor");
+    const int cwords = (d->c + 31) / 32;
+    const size_t words = (size_t)d->batch * d->h * d->w * cwords;
+    if (words > kXnorStaticWords)
+        DNB_FAIL(DNB_EINVAL, "xnor static: the packed input needs %zu words, the built-in scratch holds %zu (batch*h*w*ceil(c/32) <= 2^20); "
+                 "use a plan (dnb_conv_plan_create) for larger layers", words, kXnorStaticWords);
+    int dev = 0;
+    DNB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) DNB_FAIL(DNB_EINVAL, "xnor static: device ordinal %d", dev);
+    if (!g_xnor_static_ptr[dev]) {   // set-up: first call on this device
+        uint32_t *ptr = nullptr;
+        DNB_CUDA(cudaGetSymbolAddress((void **)&ptr, g_xnor_static_bits));
+        if (!ptr) DNB_FAIL(DNB_ECUDA, "xnor static: the scratch array has no address on device %d", dev);
+        g_xnor_static_ptr[dev] = ptr;
+    }
+    uint32_t *bits = g_xnor_static_ptr[dev];
+    cudaStream_t s = (cudaStream_t)stream;
+    // every word the convolution reads is rewritten by the packing pass, so nothing has to be cleared
+    DNB_TRY(launch_pack_sign_bits(x, bits, cwords, s));
+    XnorArgs a;
+    a.xbits = bits; a.wbits = wbits; a.cwords = cwords; a.wmean = wmean; a.acc_out = nullptr;
+    a.y_nhwc = y->layout == DNB_NHWC ? y->data : nullptr;
+    a.y_dtype = y->dtype; a.y_cpitch = y->cpitch;
+    a.y_nchw = y->layout == DNB_NCHW ? (float *)y->data : nullptr;
+    a.g = ConvGeom{d->batch, d->h, d->w, d->c, d->n, 1, d->size, d->stride, d->pad, out_h, out_w};
+    a.ep = ConvEpilogue{scale, shift, d->activation, 0};
+    return launch_conv_xnor(a, s);
+}

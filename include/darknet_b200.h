@@ -137,6 +137,32 @@ int dnb_conv_forward(dnb_conv_plan *plan, const dnb_tensor *x, const dnb_tensor 
  * must match it bit for bit. */
 int dnb_conv_xnor_accumulate(dnb_conv_plan *plan, const dnb_tensor *x, int32_t *acc, void *stream);
 
+/* The xnor convolution for callers that may not allocate: no plan, no cudaMalloc,
+ * cudaFree or allocating library call, on this or any later call.  Meant for hosts
+ * whose device memory was handed out once at start-up (a serving loop with a fixed
+ * arena, a plug-in inside a process that forbids allocation after initialisation).
+ * The caller passes every input and output as device memory it owns:
+ *   x       input, NCHW f32 or NHWC (f32 / bf16), extents as in desc
+ *   wbits   [n][size*size][ceil(c/32)] words, bit (ch % 32) of word (ch / 32) set
+ *           when weights[n][ch][kh][kw] > 0, other bits 0
+ *   wmean   [n] mean |w| of each filter
+ *   scale, shift  [n] folded batchnorm: out = act(acc * wmean * scale + shift)
+ *           (scale 1 and shift = bias for a layer without batchnorm)
+ *   y       output, NCHW f32 or NHWC
+ * The bit-packed copy of the input, which the plan-based path keeps in memory it
+ * allocates, lives here in a fixed 4 MiB array inside the library image (every GPU
+ * that loads the library holds it until the process exits), so the layer must
+ * satisfy batch*h*w*ceil(c/32) <= 1048576; larger layers are rejected with
+ * DNB_EINVAL and need a plan.  The first call on a device looks the array's
+ * address up; make that first call outside any stream capture.  All calls share
+ * the one array and leave their packed input in it (each call rewrites every word
+ * it reads, nothing needs clearing): two calls that overlap on the GPU, on
+ * different streams or from different threads, race on it.
+ * This entry point has no counterpart in the reference. */
+int dnb_conv_xnor_forward_static(const dnb_conv_desc *desc, const dnb_tensor *x, const uint32_t *wbits,
+                                 const float *wmean, const float *scale, const float *shift,
+                                 const dnb_tensor *y, void *stream);
+
 /* Reads and clears the plan's device status word (synchronises the device copy).
  * DNB_ETIMEOUT if a bounded wait inside the tensor-core kernel expired: the
  * kernel then left early and its output is incomplete.  The reference has no
