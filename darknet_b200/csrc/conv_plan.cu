@@ -230,10 +230,15 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     const int min_srb = 16 * out_es;  // a staged row holds at least one 16-column piece of the accumulator
     int srb = pitch_bytes >= 128 ? 128 : (pitch_bytes >= 64 ? 64 : 32);
     if (srb < min_srb) srb = min_srb;  // the box may be wider than a narrow tensor: the TMA unit clips it
+    if (const char *e = getenv("DNB_TC_SRB")) {   // tuning knob: widest staged row to try (128, 64 or 32)
+        const int v = atoi(e);
+        if ((v == 128 || v == 64 || v == 32) && v >= min_srb && v < srb) srb = v;
+    }
+    const int min_stages = getenv("DNB_TC_MIN_STAGES") ? atoi(getenv("DNB_TC_MIN_STAGES")) : 4;
     int stages = 0;
     for (;; srb /= 2) {
         stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.n_tot)) / (a.a_bytes + a.b_bytes));
-        if (stages >= 4 || srb == min_srb) break;
+        if (stages >= min_stages || srb == min_srb) break;
     }
     if (stages > 8) stages = 8;
     if (const char *e = getenv("DNB_TC_STAGES")) {

