@@ -163,6 +163,7 @@ class CpuReference:
                 finally:
                     os.dup2(saved, 2)
                     os.close(devnull)
+                self.R.L.ref_set_threads(os.cpu_count() or 1)   # torchrun exports OMP_NUM_THREADS=1: use every host core
                 self.cores = self.R.L.ref_max_threads()
                 self.kind = "reference"
             else:

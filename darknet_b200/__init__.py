@@ -59,6 +59,7 @@ SIGNATURES = {
     "dnb_conv_plan_set_params": (_I, [_P, _P, _P, _P, _P, _P]),
     "dnb_conv_forward": (_I, [_P, _TP, _TP, _TP, _P]),
     "dnb_conv_xnor_accumulate": (_I, [_P, _TP, _P, _P]),
+    "dnb_conv_shortcut_forward": (_I, [_P, _TP, _TP, _TP, _F, _F, _I, _P]),
     "dnb_conv_plan_check_status": (_I, [_P]),
     "dnb_conv_xnor_forward_static": (_I, [C.POINTER(ConvDesc), _TP, _P, _P, _P, _P, _TP, _P]),
     "dnb_conv_plan_kernel": (C.c_char_p, [_P]),

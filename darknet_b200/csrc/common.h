@@ -73,6 +73,12 @@ struct ConvEpilogue {
     const float *shift;   // [n_pad] folded shift b'
     int activation;       // dnb_activation
     int round_tf32;       // round f32 NHWC results to TF32-nearest
+    // optional fused residual (the [shortcut] layer that follows the convolution):
+    // out = act2(alpha * act(conv) + beta * residual), residual channels-last, same extents as the output
+    const void *residual;
+    int res_cpitch;
+    int activation2;
+    float alpha, beta;
 };
 
 struct ConvGeom {

@@ -28,6 +28,7 @@ struct alignas(64) TcArgs {
     CUtensorMap tmx[4];   // activation maps: one per (row parity, column parity) lattice of a strided conv
     CUtensorMap tmw;      // weights [taps][n_pad][c_pad], channels innermost
     CUtensorMap tmy;      // NHWC output, written by TMA stores from the staging rows
+    CUtensorMap tmr;      // fused residual (same extents and box as tmy), loaded tile by tile in the epilogue
     int is_bf16;          // 0: kind::tf32 on f32 operands, 1: kind::f16 on bf16 operands
     int row_bytes;        // bytes of channels per pipeline stage row: 128, 64 or 32 (= swizzle span)
     int bk;               // channels per stage row (row_bytes / element size)
@@ -52,7 +53,7 @@ struct alignas(64) TcArgs {
 };
 int launch_conv_tc(const TcArgs &a, cudaStream_t s);
 size_t conv_tc_smem_bytes(const TcArgs &a);
-size_t conv_tc_fixed_smem(int store_row_bytes, int n_tot);
+size_t conv_tc_fixed_smem(int store_row_bytes, int n_tot, int with_residual);
 int conv_tc_max_smem();
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link).
@@ -105,6 +106,8 @@ struct dnb_conv_plan {
     const void *tc_x_ptr;
     int tc_x_cpitch;
     const void *tc_y_ptr;    // NHWC output the store map was built for
+    const void *tc_res_ptr;  // fused residual the load map was built for (NULL: none)
+    int tc_res_cpitch;
     int tc_y_cpitch, tc_y_dtype;
     int device;
 };

@@ -156,6 +156,7 @@ conv_stem3x3_kernel(DirectArgs a)
 {
     __shared__ __align__(16) float w_s[27][FB];
     __shared__ __align__(16) float out_s[STHREADS * SPIX][FB + 4];
+    __shared__ long long pix_s[STHREADS * SPIX];   // flat output pixel of every slot, -1 when outside the tensor
 
     const ConvGeom g = a.g;
     const int f0 = blockIdx.y * FB;
@@ -163,15 +164,20 @@ conv_stem3x3_kernel(DirectArgs a)
 
     // pixel pairs never straddle a row: out_w is padded to even per row by the launcher's grid math
     const int pairs_per_row = (g.out_w + 1) / 2;
-    const long long npairs = (long long)g.batch * g.out_h * pairs_per_row;
-    const long long pair = (long long)blockIdx.x * STHREADS + threadIdx.x;
+    const unsigned npairs = (unsigned)g.batch * g.out_h * pairs_per_row;   // < 2^31, checked by the launcher
+    const unsigned pair = blockIdx.x * STHREADS + threadIdx.x;
     const bool live = pair < npairs;
     int b = 0, oh = 0, ow = 0;
     if (live) {
         ow = (int)(pair % pairs_per_row) * 2;
-        long long t = pair / pairs_per_row;
+        const unsigned t = pair / pairs_per_row;
         oh = (int)(t % g.out_h);
         b = (int)(t / g.out_h);
+    }
+    {
+        const long long p0 = ((long long)b * g.out_h + oh) * g.out_w + ow;
+        pix_s[2 * threadIdx.x] = live ? p0 : -1;
+        pix_s[2 * threadIdx.x + 1] = (live && ow + 1 < g.out_w) ? p0 + 1 : -1;
     }
     const TX *xb = reinterpret_cast<const TX *>(a.x) + b * a.xs_b;
     float xv[3][3][4];
@@ -222,21 +228,19 @@ conv_stem3x3_kernel(DirectArgs a)
     }
     __syncthreads();
 
-    // stores: slot s of the block = pair (s / 2), pixel (s % 2); its flat pixel index is computed per slot
-    const long long pair0 = (long long)blockIdx.x * STHREADS;
+    // stores: slot s of the block = pair (s / 2), pixel (s % 2).  Each thread published the flat pixel index
+    // of its two slots (or -1) in shared memory, so the store loop needs no divisions.
     const bool last = f0 + FB >= g.n;
     const int cols = last ? min(FB, (a.y_nhwc ? a.y_cpitch : g.n) - f0) : nvalid;
     if (a.y_nhwc) {
         constexpr int EPV = 16 / sizeof(TY);
         const int pieces = (cols + EPV - 1) / EPV;    // cpitch and FB are multiples of 8: whole pieces
-        for (int i = threadIdx.x; i < STHREADS * SPIX * pieces; i += STHREADS) {
+        const int total = STHREADS * SPIX * pieces;
+        for (int i = threadIdx.x; i < total; i += STHREADS) {
             const int slot = i / pieces, q = i - slot * pieces;
-            const long long pr = pair0 + (slot >> 1);
-            if (pr >= npairs) continue;
-            const int pw = (int)(pr % pairs_per_row) * 2 + (slot & 1);
-            if (pw >= g.out_w) continue;
-            const long long rowid = pr / pairs_per_row;   // b * out_h + oh
-            TY *dst = reinterpret_cast<TY *>(a.y_nhwc) + ((size_t)rowid * g.out_w + pw) * a.y_cpitch + f0 + q * EPV;
+            const long long pix = pix_s[slot];
+            if (pix < 0) continue;
+            TY *dst = reinterpret_cast<TY *>(a.y_nhwc) + (size_t)pix * a.y_cpitch + f0 + q * EPV;
             const float *src = &out_s[slot][q * EPV];
             if (sizeof(TY) == 4) {
                 *reinterpret_cast<float4 *>(dst) = *reinterpret_cast<const float4 *>(src);
@@ -270,6 +274,7 @@ int launch_conv_direct(const DirectArgs &a, cudaStream_t s)
     if (g.c == 3 && g.size == 3 && g.stride == 1 && g.pad == 1 && g.groups == 1 && !xb &&
         (!a.y_nhwc || (a.y_cpitch % 8 == 0))) {
         const long long npairs = (long long)g.batch * g.out_h * ((g.out_w + 1) / 2);
+        if (npairs >= (1LL << 31)) DNB_FAIL(DNB_EUNSUPPORTED, "first-layer kernel: %lld pixel pairs", npairs);
         dim3 sgrid((unsigned)((npairs + STHREADS - 1) / STHREADS), (unsigned)((g.n + FB - 1) / FB));
         if (yb) conv_stem3x3_kernel<float, __nv_bfloat16><<<sgrid, STHREADS, 0, s>>>(a);
         else conv_stem3x3_kernel<float, float><<<sgrid, STHREADS, 0, s>>>(a);

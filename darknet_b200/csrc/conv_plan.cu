@@ -177,7 +177,8 @@ static void pick_pixel_tile(const ConvGeom &g, int *wt, int *ht, int *bt)
         }
 }
 
-static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, int y_dtype, int y_cpitch)
+static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, int y_dtype, int y_cpitch,
+                         const void *residual, int res_cpitch)
 {
     TcArgs &a = p->tc;
     const ConvGeom &g = p->g;
@@ -237,7 +238,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     const int min_stages = getenv("DNB_TC_MIN_STAGES") ? atoi(getenv("DNB_TC_MIN_STAGES")) : 4;
     int stages = 0;
     for (;; srb /= 2) {
-        stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.n_tot)) / (a.a_bytes + a.b_bytes));
+        stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.n_tot, residual != nullptr)) / (a.a_bytes + a.b_bytes));
         if (stages >= min_stages || srb == min_srb) break;
     }
     if (stages > 8) stages = 8;
@@ -281,12 +282,20 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
         uint64_t strides[3] = {opix, opix * g.out_w, opix * g.out_w * g.out_h};
         uint32_t box[4] = {(uint32_t)(srb / out_es), (uint32_t)a.wt, (uint32_t)a.ht, (uint32_t)a.bt};
         DNB_TRY(encode_tensor_map(&a.tmy, bf16, 4, y_nhwc, dims, strides, box, srb));
+        if (residual) {
+            const size_t rpix = (size_t)res_cpitch * out_es;
+            uint64_t rdims[4] = {(uint64_t)res_cpitch, (uint64_t)g.out_w, (uint64_t)g.out_h, (uint64_t)g.batch};
+            uint64_t rstrides[3] = {rpix, rpix * g.out_w, rpix * g.out_w * g.out_h};
+            DNB_TRY(encode_tensor_map(&a.tmr, bf16, 4, const_cast<void *>(residual), rdims, rstrides, box, srb));
+        }
     }
     p->tc_x_ptr = x->data;
     p->tc_x_cpitch = x->cpitch;
     p->tc_y_ptr = y_nhwc;
     p->tc_y_cpitch = y_cpitch;
     p->tc_y_dtype = y_dtype;
+    p->tc_res_ptr = residual;
+    p->tc_res_cpitch = res_cpitch;
     return DNB_OK;
 }
 
@@ -310,8 +319,14 @@ static int check_conv_io(const dnb_conv_plan *p, const dnb_tensor *x, const dnb_
     return DNB_OK;
 }
 
+struct Residual {
+    const dnb_tensor *add = nullptr;
+    float alpha = 1.f, beta = 1.f;
+    int activation = DNB_LINEAR;
+};
+
 static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_tensor *y, const dnb_tensor *y2,
-                             int32_t *acc_out, cudaStream_t s)
+                             int32_t *acc_out, cudaStream_t s, const Residual *res = nullptr)
 {
     if (!p) DNB_FAIL(DNB_EINVAL, "conv: null plan");
     if (!p->params_set) DNB_FAIL(DNB_EINVAL, "conv: dnb_conv_plan_set_params has not been called");
@@ -326,7 +341,13 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
         if (o->layout == DNB_NHWC) { y_nhwc = o->data; y_dtype = o->dtype; y_cpitch = o->cpitch; }
         else y_nchw = (float *)o->data;
     }
-    ConvEpilogue ep{p->scale, p->shift, p->d.activation, 0};
+    ConvEpilogue ep{p->scale, p->shift, p->d.activation, 0, nullptr, 0, DNB_LINEAR, 1.f, 1.f};
+    if (res && res->add) {
+        if (p->kernel != K_TC_TF32 && p->kernel != K_TC_BF16)
+            DNB_FAIL(DNB_EUNSUPPORTED, "conv + shortcut: only tensor-core plans fuse the residual (this plan is %s)", kKernelNames[p->kernel]);
+        ep.residual = res->add->data; ep.res_cpitch = res->add->cpitch; ep.activation2 = res->activation;
+        ep.alpha = res->alpha; ep.beta = res->beta;
+    }
     // f32 channels-last results of a TF32 network feed the next tensor-core layer: round them once here
     ep.round_tf32 = (p->mode == DNB_MODE_TF32 && y_nhwc && y_dtype == DNB_F32 && !y_nchw) ? 1 : 0;
 
@@ -375,8 +396,8 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
     if (y_nhwc && y_dtype != want)
         DNB_FAIL(DNB_EINVAL, "conv: a %s plan writes channels-last output as %s", kKernelNames[p->kernel], want == DNB_BF16 ? "bf16" : "f32");
     if (p->tc_x_ptr != xin.data || p->tc_x_cpitch != xin.cpitch || p->tc_y_ptr != y_nhwc || p->tc_y_cpitch != y_cpitch ||
-        p->tc_y_dtype != y_dtype || !p->status)
-        DNB_TRY(build_tc_args(p, &xin, y_nhwc, y_dtype, y_cpitch));
+        p->tc_y_dtype != y_dtype || !p->status || p->tc_res_ptr != ep.residual || p->tc_res_cpitch != ep.res_cpitch)
+        DNB_TRY(build_tc_args(p, &xin, y_nhwc, y_dtype, y_cpitch, ep.residual, ep.res_cpitch));
     TcArgs &a = p->tc;
     a.y_nhwc = y_nhwc; a.y_dtype = y_dtype; a.y_cpitch = y_cpitch; a.y_nchw = y_nchw;
     a.ep = ep;
@@ -388,6 +409,25 @@ extern "C" int dnb_conv_forward(dnb_conv_plan *p, const dnb_tensor *x, const dnb
     if (!p) DNB_FAIL(DNB_EINVAL, "conv: null plan");
     DNB_TRY(check_conv_io(p, x, y, y2));
     return conv_forward_impl(p, x, y, y2, nullptr, (cudaStream_t)stream);
+}
+
+// Convolution followed by the residual add of a [shortcut] layer, one launch:
+// y = act2(alpha * act(conv(x)) + beta * add).
+extern "C" int dnb_conv_shortcut_forward(dnb_conv_plan *p, const dnb_tensor *x, const dnb_tensor *add, const dnb_tensor *y,
+                                         float alpha, float beta, int activation2, void *stream)
+{
+    if (!p || !add) DNB_FAIL(DNB_EINVAL, "conv + shortcut: null argument");
+    DNB_TRY(check_conv_io(p, x, y, nullptr));
+    DNB_TRY(check_tensor(add, "conv + shortcut residual"));
+    if (activation2 < 0 || activation2 > DNB_SELU) DNB_FAIL(DNB_EINVAL, "conv + shortcut: activation %d", activation2);
+    const int want = p->kernel == K_TC_BF16 ? DNB_BF16 : DNB_F32;
+    if (add->layout != DNB_NHWC || y->layout != DNB_NHWC || add->dtype != want)
+        DNB_FAIL(DNB_EINVAL, "conv + shortcut: residual and output must be channels-last in the plan's storage type");
+    if (add->n != y->n || add->c != y->c || add->h != y->h || add->w != y->w)
+        DNB_FAIL(DNB_EUNSUPPORTED, "conv + shortcut: the residual must have the output's extents (other shapes: dnb_shortcut_forward)");
+    Residual r;
+    r.add = add; r.alpha = alpha; r.beta = beta; r.activation = activation2;
+    return conv_forward_impl(p, x, y, nullptr, nullptr, (cudaStream_t)stream, &r);
 }
 
 extern "C" int dnb_conv_xnor_accumulate(dnb_conv_plan *p, const dnb_tensor *x, int32_t *acc, void *stream)

@@ -204,11 +204,12 @@ struct TcShared {
     uint64_t empty[MAX_STAGES];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
+    uint64_t res_full[2];      // residual tile landed in its staging buffer
     uint32_t tmem_base;
     int abort_flag;
 };
 
-enum { WAIT_EMPTY = 101, WAIT_FULL = 102, WAIT_ACC_EMPTY = 103, WAIT_ACC_FULL = 104 };
+enum { WAIT_EMPTY = 101, WAIT_FULL = 102, WAIT_ACC_EMPTY = 103, WAIT_ACC_FULL = 104, WAIT_RESIDUAL = 105 };
 enum { ACT_GENERIC = -1 };
 
 
@@ -234,7 +235,8 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     const uint32_t stage_bytes = a.a_bytes + a.b_bytes;
     uint8_t *after_ring = smem_raw + (ring - smem_u32(smem_raw)) + (size_t)a.stages * stage_bytes;
     uint8_t *stage_out = after_ring;                                  // 2 x 128 rows x store_row_bytes
-    float *s_scale = reinterpret_cast<float *>(after_ring + 2 * 128 * (CPC * (OUT_BF16 ? 2 : 4)));
+    uint8_t *stage_res = after_ring + 2 * 128 * (CPC * (OUT_BF16 ? 2 : 4));   // 2 more buffers when a residual is fused
+    float *s_scale = reinterpret_cast<float *>(stage_res + (a.ep.residual ? 2 * 128 * (CPC * (OUT_BF16 ? 2 : 4)) : 0));
     float *s_shift = s_scale + a.n_tot + 64;
     TcShared *sh = reinterpret_cast<TcShared *>(s_shift + a.n_tot + 64);
     volatile int *abort_flag = &sh->abort_flag;
@@ -249,6 +251,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&sh->acc_full[i]), 1);
             mbar_init(smem_u32(&sh->acc_empty[i]), 4);
+            mbar_init(smem_u32(&sh->res_full[i]), 1);
         }
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -369,6 +372,10 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         void *const y_nhwc = a.y_nhwc;
         float *const y_nchw = a.y_nchw;
         const int runtime_act = a.ep.activation, do_round = a.ep.round_tf32;
+        const bool residual = a.ep.residual != nullptr;
+        const CUtensorMap *rmap = &a.tmr;
+        const int act2 = a.ep.activation2;
+        const float res_alpha = a.ep.alpha, res_beta = a.ep.beta;
         const CUtensorMap *ymap = &a.tmy;
         int *status = a.status;
         const bool store_thread = threadIdx.x == 64;
@@ -386,6 +393,13 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             const int ow0 = (pt % tiles_w) * wt, oh0 = ((pt / tiles_w) % tiles_h) * ht, b0 = (pt / ptiles_wh) * bt;
             const int ow = ow0 + wl, oh = oh0 + hl, b = b0 + bl;
             const bool pix_ok = ow < g.out_w && oh < g.out_h && b < g.batch;
+            if (residual && store_thread) {
+                // residual tile of the first chunk: requested before the accumulator is even ready.  The buffer's
+                // previous readers (two chunks ago) are past the barriers of the chunk in between.
+                const uint32_t rb = chunk_count & 1, bar = smem_u32(&sh->res_full[rb]);
+                mbar_expect_tx(bar, 128u * srb);
+                tma_load_4d(smem_u32(stage_res + (size_t)rb * 128 * srb), rmap, bar, nt * bn, ow0, oh0, b0);
+            }
 
             mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, abort_flag, status, WAIT_ACC_FULL, 32);
             epilogue_bar();                 // all four warps agree on the abort flag from here
@@ -399,6 +413,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
 #pragma unroll 1
             for (int c0 = 0; c0 < bn; c0 += CPC) {
                 uint32_t r[CPC];
+                constexpr int RES_V = CPC * (OUT_BF16 ? 2 : 4) / 16;      // 16-byte pieces of a staged row
 #pragma unroll
                 for (int u = 0; u < CPC / 16; ++u) {
                     if (c0 + 16 * u < bn) {
@@ -409,6 +424,15 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                     }
                 }
                 tmem_ld_wait();
+                uint4 res[RES_V];
+                if (residual) {
+                    // this chunk's residual tile (TMA zero-fills pixels and channels outside the tensor)
+                    const uint32_t rb = chunk_count & 1;
+                    mbar_wait(smem_u32(&sh->res_full[rb]), (chunk_count >> 1) & 1, abort_flag, status, WAIT_RESIDUAL);
+                    const uint8_t *rrow = stage_res + (size_t)rb * 128 * srb + (size_t)m * srb;
+#pragma unroll
+                    for (int q = 0; q < RES_V; ++q) res[q] = *reinterpret_cast<const uint4 *>(rrow + ((q ^ q_xor) << 4));
+                }
                 // epilogue arithmetic in place: r[] becomes the output values (as float bits); the shared
                 // scale / shift copies are zero beyond the layer's filters and padded by 64 entries
                 const int nl0 = nt * bn + c0;                 // first filter of this chunk
@@ -423,6 +447,20 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                     for (int e = 0; e < 4; ++e) {
                         const int j = 4 * q + e;
                         float t = act_apply<ACT>(fmaf(__uint_as_float(r[j]), scv[e], sfv[e]), runtime_act);
+                        if (residual) {
+                            float rv = 0.f;
+                            {
+                                if (!OUT_BF16) {
+                                    const uint4 v4 = res[j / 4];
+                                    rv = __uint_as_float((j & 3) == 0 ? v4.x : (j & 3) == 1 ? v4.y : (j & 3) == 2 ? v4.z : v4.w);
+                                } else {
+                                    const uint4 v4 = res[j / 8];
+                                    const uint32_t wd = ((j >> 1) & 3) == 0 ? v4.x : ((j >> 1) & 3) == 1 ? v4.y : ((j >> 1) & 3) == 2 ? v4.z : v4.w;
+                                    rv = __uint_as_float((j & 1) ? (wd & 0xffff0000u) : (wd << 16));
+                                }
+                            }
+                            t = activate_fast(res_alpha * t + res_beta * rv, act2);
+                        }
                         if (do_round) t = round_tf32(t);
                         r[j] = __float_as_uint(j < nvalid ? t : 0.f);
                     }
@@ -430,6 +468,12 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 const uint32_t buf = chunk_count & 1;
                 if (store_thread && chunk_count >= 2) tma_store_wait_read1();   // the store that last read this buffer is done
                 epilogue_bar();
+                if (residual && store_thread && c0 + CPC < bn) {
+                    // next chunk's residual tile into the other buffer: every thread finished reading it one chunk ago
+                    const uint32_t nb = (chunk_count + 1) & 1, bar = smem_u32(&sh->res_full[nb]);
+                    mbar_expect_tx(bar, 128u * srb);
+                    tma_load_4d(smem_u32(stage_res + (size_t)nb * 128 * srb), rmap, bar, nt * bn + c0 + CPC, ow0, oh0, b0);
+                }
                 uint8_t *row = stage_out + (size_t)buf * 128 * srb + (size_t)m * srb;
                 if (!out_bf16) {
 #pragma unroll
@@ -491,14 +535,14 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
 }
 
 // ------------------------------------------------------------------ host side
-size_t conv_tc_fixed_smem(int store_row_bytes, int n_tot)
+size_t conv_tc_fixed_smem(int store_row_bytes, int n_tot, int with_residual)
 {
-    return 1024 + 2 * 128 * (size_t)store_row_bytes + 2 * sizeof(float) * ((size_t)n_tot + 64) + sizeof(TcShared) + 64;
+    return 1024 + (with_residual ? 4 : 2) * 128 * (size_t)store_row_bytes + 2 * sizeof(float) * ((size_t)n_tot + 64) + sizeof(TcShared) + 64;
 }
 
 size_t conv_tc_smem_bytes(const TcArgs &a)
 {
-    return (size_t)a.stages * (a.a_bytes + a.b_bytes) + conv_tc_fixed_smem(a.store_row_bytes, a.n_tot);
+    return (size_t)a.stages * (a.a_bytes + a.b_bytes) + conv_tc_fixed_smem(a.store_row_bytes, a.n_tot, a.ep.residual != nullptr);
 }
 
 int conv_tc_max_smem()

@@ -43,6 +43,8 @@ struct Layer {
     int groups = 1;
     float temperature = 1.f;
     int launches = 1;
+    // a convolution that also performs the [shortcut] layer right after it, and that shortcut layer
+    bool fuses_next_shortcut = false, fused_into_prev = false;
 };
 
 typedef std::map<std::string, std::string> Options;
@@ -269,6 +271,29 @@ static int build_network(const char *text, int mode, int batch_override, dnb_net
             for (int id : L.inputs)
                 if (net->layers[id].kind == L_YOLO) DNB_FAIL(DNB_EUNSUPPORTED, "cfg: route from a [yolo] layer");
     }
+    // Fuse "convolution, then [shortcut] of equal shape" into the convolution's epilogue when nothing else
+    // reads the convolution's own output: one pass over the activations instead of three.
+    // DNB_FUSE_SHORTCUT=0 keeps every layer separate (every layer's output stays readable).
+    const bool fuse = getenv("DNB_FUSE_SHORTCUT") ? atoi(getenv("DNB_FUSE_SHORTCUT")) != 0 : true;
+    for (int i = 0; fuse && i + 1 < (int)net->layers.size(); ++i) {
+        Layer &C = net->layers[i], &S = net->layers[i + 1];
+        if (C.kind != L_CONV || !C.plan || (C.plan->kernel != 0 && C.plan->kernel != 1) || S.kind != L_SHORTCUT || S.from == i) continue;
+        const Layer &F = net->layers[S.from];
+        if (F.kind == L_YOLO || F.out_c != S.out_c || F.out_h != S.out_h || F.out_w != S.out_w) continue;
+        bool read_elsewhere = false;
+        for (int j = i + 2; j < (int)net->layers.size(); ++j) {
+            const Layer &L = net->layers[j];
+            if (L.kind == L_SHORTCUT && L.from == i) read_elsewhere = true;
+            if (L.kind == L_ROUTE)
+                for (int id : L.inputs) if (id == i) read_elsewhere = true;
+        }
+        if (read_elsewhere) continue;
+        C.fuses_next_shortcut = true;
+        S.fused_into_prev = true;
+        S.launches = 0;
+        cudaFree(C.out.data);      // never written: the convolution stores straight into the shortcut's output
+        C.out.data = nullptr;
+    }
     const Layer &last = net->layers.back();
     net->outputs = last.out_c * last.out_h * last.out_w;
     DNB_CUDA(cudaMalloc((void **)&net->input_dev, (size_t)net->batch * net->inputs * sizeof(float)));
@@ -380,10 +405,17 @@ static int forward_layer(dnb_network *net, int i, const float *device_input, cud
         in = net->layers[i - 1].out;
     }
     switch (L.kind) {
-    case L_CONV: return dnb_conv_forward(L.plan, &in, &L.out, nullptr, s);
+    case L_CONV:
+        if (L.fuses_next_shortcut) {
+            Layer &S = net->layers[i + 1];
+            return dnb_conv_shortcut_forward(L.plan, &in, &net->layers[S.from].out, &S.out, S.alpha, S.beta, S.activation, s);
+        }
+        return dnb_conv_forward(L.plan, &in, &L.out, nullptr, s);
     case L_MAXPOOL: return launch_maxpool(&in, &L.out, L.size, L.stride, L.padding, s);
     case L_UPSAMPLE: return launch_upsample(&in, &L.out, L.stride, L.scale, s);
-    case L_SHORTCUT: return launch_shortcut(&in, &net->layers[L.from].out, &L.out, L.alpha, L.beta, L.activation, s);
+    case L_SHORTCUT:
+        if (L.fused_into_prev) return DNB_OK;   // done by the convolution before it
+        return launch_shortcut(&in, &net->layers[L.from].out, &L.out, L.alpha, L.beta, L.activation, s);
     case L_ROUTE: {
         std::vector<const dnb_tensor *> ins;
         for (int id : L.inputs) ins.push_back(&net->layers[id].out);
@@ -459,6 +491,8 @@ extern "C" int dnb_network_layer_output(dnb_network *net, int i, float *host_out
 {
     if (!net || !host_out || i < 0 || i >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "layer_output: bad argument");
     Layer &L = net->layers[i];
+    if (!L.out.data)
+        DNB_FAIL(DNB_EUNSUPPORTED, "layer %d is fused into the shortcut layer %d and has no output of its own (DNB_FUSE_SHORTCUT=0 keeps it)", i, i + 1);
     const size_t elems = (size_t)net->batch * L.out_c * L.out_h * L.out_w;
     DNB_CUDA(cudaDeviceSynchronize());  // the forward may have run on any stream
     if (L.out.layout == DNB_NCHW) {

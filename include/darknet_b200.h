@@ -130,6 +130,16 @@ int dnb_conv_plan_set_params(dnb_conv_plan *plan, const float *weights, const fl
 int dnb_conv_forward(dnb_conv_plan *plan, const dnb_tensor *x, const dnb_tensor *y,
                      const dnb_tensor *y2, void *stream);
 
+/* A convolution and the [shortcut] layer that follows it in one launch:
+ *   y = act2(alpha * act(conv(x)) + beta * add)
+ * i.e. forward_convolutional_layer_gpu followed by forward_shortcut_layer_gpu
+ * (src/shortcut_layer.c:77-82: copy_gpu + shortcut_gpu + activate_array_gpu) without
+ * the intermediate tensor.  Tensor-core plans only; x, add and y channels-last in the
+ * plan's storage type, add with the extents of y (other shapes: dnb_shortcut_forward).
+ * The network object uses it wherever nothing else reads the convolution's own output. */
+int dnb_conv_shortcut_forward(dnb_conv_plan *plan, const dnb_tensor *x, const dnb_tensor *add,
+                              const dnb_tensor *y, float alpha, float beta, int activation2, void *stream);
+
 /* Integer accumulators of an xnor plan, before scale/batchnorm/activation:
  * acc[b][n][oh][ow] (NCHW int32) = sum over in-bounds taps of sign(w)*sign(x).
  * What binarize + im2col + gemm produce in the reference

@@ -381,3 +381,31 @@ def test_conv_rejects_mismatched_tensors():
     gt, gd = empty_nchw(1, 16, 8, 8)
     with pytest.raises(dn.DarknetB200Error):
         plan.forward(bd, gd)   # bf16 input to a TF32 plan
+
+
+@pytest.mark.parametrize("mode,tol", [(dn.MODE_TF32, TOL_TF32), (dn.MODE_BF16, TOL_BF16)])
+@pytest.mark.parametrize("act2", ["linear", "leaky"])
+@pytest.mark.parametrize("shape", [dict(b=2, c=64, h=13, w=13, n=64, size=3), dict(b=3, c=32, h=19, w=19, n=320, size=1),
+                                   dict(b=1, c=16, h=9, w=10, n=24, size=3)])
+def test_conv_with_fused_shortcut(mode, tol, act2, shape):
+    import ctypes as C
+    case = conv_case(600, **shape)
+    x, w = case["x"], case["w"]
+    b, c, h, wd = x.shape
+    n = w.shape[0]
+    add = rng(601).standard_normal((b, n, h, wd), dtype=np.float32)
+    store = torch.bfloat16 if mode == dn.MODE_BF16 else torch.float32
+    if mode == dn.MODE_BF16:
+        add = bf16_round(add)
+    want = orc.shortcut_forward(oracle_conv(case), add, 1.0, 1.0, act2)
+    plan = dn.ConvPlan(b, c, h, wd, n, w.shape[2], 1, case["pad"], 1, True, case["act"], False, mode)
+    plan.set_params(w, case["biases"], case["scales"], case["mean"], case["var"])
+    xt, xd = dev_nhwc(x, store)
+    at, ad = dev_nhwc(add, store)
+    yt, yd = empty_nhwc(b, n, h, wd, store)
+    dn.check(dn.lib().dnb_conv_shortcut_forward(plan.handle, C.byref(xd), C.byref(ad), C.byref(yd), 1.0, 1.0, dn.ACTIVATIONS[act2],
+                                                C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    plan.check_status()
+    assert rel_to_max(host_from_nhwc(yt, n), want) < tol
+    assert padding_is_zero(yt, n)

@@ -36,7 +36,11 @@ def build(cfg, params, tmp_path, mode):
 
 @pytest.mark.parametrize("name", ["tiny64", "tiny96_b2", "yolov3_64", "resnet50_32", "resnet50_64_b2", "darknet19_64"])
 @pytest.mark.parametrize("mode", [dn.MODE_FP32, dn.MODE_TF32, dn.MODE_BF16])
-def test_network_matches_oracle_and_golden(name, mode, tmp_path, golden):
+@pytest.mark.parametrize("fuse", [0, 1])
+def test_network_matches_oracle_and_golden(name, mode, fuse, tmp_path, golden, monkeypatch):
+    # fuse=0: every layer separate, every layer's output checked; fuse=1 (the default): convolutions absorb the
+    # shortcut layer after them, their own outputs do not exist and are skipped
+    monkeypatch.setenv("DNB_FUSE_SHORTCUT", str(fuse))
     cfg, pseed, iseed, dist = CASES[name]
     params = synth.seeded_params(cfg, pseed)
     x = synth.seeded_input(cfg, iseed, dist)
@@ -46,8 +50,14 @@ def test_network_matches_oracle_and_golden(name, mode, tmp_path, golden):
     assert net.n == len(want)
     kinds = [k for k, _ in synth.parse_cfg(cfg)[1:]]
     worst = 0.0
+    skipped = 0
     for i, w in enumerate(want):
-        got = net.layer_output(i)
+        try:
+            got = net.layer_output(i)
+        except dn.DarknetB200Error as e:
+            assert fuse and e.status == dn.EUNSUPPORTED and kinds[i] == "convolutional" and kinds[i + 1] == "shortcut"
+            skipped += 1
+            continue
         assert got.shape == w.shape or got.size == w.size
         err = rel_to_max(got, w)
         worst = max(worst, err)
@@ -61,7 +71,11 @@ def test_network_matches_oracle_and_golden(name, mode, tmp_path, golden):
     for i, k in enumerate(kinds):
         if k == "yolo":
             assert rel_to_max(net.yolo_output(i), want[i]) < TOL[mode]
-    print(f"{name} mode {mode}: worst per-layer rel error {worst:.3g}")
+    if fuse and mode != dn.MODE_FP32 and "shortcut" in kinds:
+        assert skipped > 0, "no convolution was fused with its shortcut"
+    if not fuse:
+        assert skipped == 0
+    print(f"{name} mode {mode} fuse {fuse}: worst per-layer rel error {worst:.3g}, {skipped} fused layers")
 
 
 def test_network_device_forward_equals_predict(tmp_path):
