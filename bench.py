@@ -38,6 +38,15 @@ import numpy as np  # noqa: E402
 
 UNIT = "images/s"
 
+# DRAM traffic of the tensor-core convolution kernel from ncu (dram__bytes_read.sum + dram__bytes_write.sum), as
+# (bytes per image, bytes per launch set independent of the batch); see profiles/conv_tc_dram_traffic_*.md and
+# profiles/conv_tc_conv*_b64_tf32.md for the captures.  Scaled by the images one step processes.
+NCU_DRAM_TRAFFIC = {
+    ("yolov3", "tf32", 608): (547_463_136.0, 247_579_648.0),
+    ("conv3x3", "tf32", 224): (489.0e6 / 64, 0.0),
+    ("conv1x1", "tf32", 224): (491.0e6 / 64, 0.0),
+}
+
 
 def workload_cfg(name: str, batch: int, size: int) -> tuple[str, str, str]:
     """(cfg text, metric name, description) of a benchmark workload.  `yolov3` is the headline; the others
@@ -309,7 +318,9 @@ def run_b200(args):
     big3 = np.array([bool(tc[i]) and sections[i][1].get("size") == "3" and shapes[i].c >= 64 for i in range(net.n)])
     big3_tflops = float(flops[big3].sum() / (mean_ms[big3].sum() / 1000.0) / 1e12) if big3.any() else None
     roofline = {"kernel": "conv_tc_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": None,
+                "frac": achieved / peak,
+                "traffic": (lambda t: None if t is None else t[0] * per_gpu + t[1])(NCU_DRAM_TRAFFIC.get((args.workload, args.mode, args.size))),
+                "traffic_unit": "bytes per step per GPU (ncu dram read+write of all launches of this kernel)",
                 "launches_per_step": int(tc.sum()), "avg_launch_ms": tc_ms / max(int(tc.sum()), 1),
                 "share_of_step": tc_ms / float(mean_ms.sum()),
                 "peak_source": f"{peaks['source']}: cuBLAS bf16 {'burst' if alone else 'sustained'} {bf16_peak} TFLOP/s"

@@ -40,6 +40,8 @@ struct alignas(64) TcArgs {
     int tiles_w, tiles_h, tiles_b;
     int total_tiles;      // n_tiles * tiles_w * tiles_h * tiles_b
     int stages;           // depth of the shared-memory ring
+    int tmem_cols;        // TMEM columns the CTA allocates: a power of two >= 2*bn (two accumulators)
+    int ctas_per_sm;      // 2 for narrow tiles (TMEM and shared memory are sized so that two CTAs share an SM), else 1
     int a_bytes, b_bytes; // shared-memory bytes of one stage's activation / weight tile (1024-multiples)
     int store_row_bytes;  // bytes of one staged output row (128, 64 or 32) = swizzle span of tmy
     int n_pad;            // length of the scale / shift vectors

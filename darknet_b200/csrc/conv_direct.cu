@@ -146,7 +146,8 @@ conv_direct_kernel(DirectArgs a)
 // First-layer specialisation: 3 input channels, 3x3, stride 1, pad 1 (the RGB stems of YOLOv3,
 // YOLOv3-tiny and Darknet-19).  Everything is compile-time, so the 36 input values of a thread's two
 // neighbouring output pixels are loaded up front (independent loads in flight instead of one
-// load-use chain per tap) and every broadcast weight load feeds two FMAs.  256 pixels per block.
+// load-use chain per tap) and every broadcast weight load feeds two FMAs.  256 pixels per block, results
+// stored straight from registers.
 constexpr int SPIX = 2;                       // output pixels per thread, adjacent in x
 constexpr int STHREADS = 128;
 
@@ -155,8 +156,6 @@ __global__ void __launch_bounds__(STHREADS)
 conv_stem3x3_kernel(DirectArgs a)
 {
     __shared__ __align__(16) float w_s[27][FB];
-    __shared__ __align__(16) float out_s[STHREADS * SPIX][FB + 4];
-    __shared__ long long pix_s[STHREADS * SPIX];   // flat output pixel of every slot, -1 when outside the tensor
 
     const ConvGeom g = a.g;
     const int f0 = blockIdx.y * FB;
@@ -173,11 +172,6 @@ conv_stem3x3_kernel(DirectArgs a)
         const unsigned t = pair / pairs_per_row;
         oh = (int)(t % g.out_h);
         b = (int)(t / g.out_h);
-    }
-    {
-        const long long p0 = ((long long)b * g.out_h + oh) * g.out_w + ow;
-        pix_s[2 * threadIdx.x] = live ? p0 : -1;
-        pix_s[2 * threadIdx.x + 1] = (live && ow + 1 < g.out_w) ? p0 + 1 : -1;
     }
     const TX *xb = reinterpret_cast<const TX *>(a.x) + b * a.xs_b;
     float xv[3][3][4];
@@ -213,52 +207,65 @@ conv_stem3x3_kernel(DirectArgs a)
                     acc0[4 * v + 3] = fmaf(x0, w4.w, acc0[4 * v + 3]); acc1[4 * v + 3] = fmaf(x1, w4.w, acc1[4 * v + 3]);
                 }
             }
+    // Epilogue straight from registers: every thread owns whole pixels, so a pixel's 32 channels leave as
+    // eight 16-byte stores into one 128-byte line (no shared-memory staging, no index arithmetic).
     const int nvalid = min(FB, g.n - f0);
+    const int act = a.ep.activation, rnd = a.ep.round_tf32;
 #pragma unroll
     for (int j = 0; j < FB; ++j) {
         float v0 = 0.f, v1 = 0.f;
         if (j < nvalid) {
             const float sc = __ldg(a.ep.scale + f0 + j), sh = __ldg(a.ep.shift + f0 + j);
-            v0 = activate_fast(acc0[j] * sc + sh, a.ep.activation);
-            v1 = activate_fast(acc1[j] * sc + sh, a.ep.activation);
-            if (a.ep.round_tf32) { v0 = round_tf32(v0); v1 = round_tf32(v1); }
+            v0 = activate_fast(acc0[j] * sc + sh, act);
+            v1 = activate_fast(acc1[j] * sc + sh, act);
+            if (rnd) { v0 = round_tf32(v0); v1 = round_tf32(v1); }
         }
-        out_s[2 * threadIdx.x][j] = v0;
-        out_s[2 * threadIdx.x + 1][j] = v1;
+        acc0[j] = v0;
+        acc1[j] = v1;
     }
-    __syncthreads();
-
-    // stores: slot s of the block = pair (s / 2), pixel (s % 2).  Each thread published the flat pixel index
-    // of its two slots (or -1) in shared memory, so the store loop needs no divisions.
-    const bool last = f0 + FB >= g.n;
-    const int cols = last ? min(FB, (a.y_nhwc ? a.y_cpitch : g.n) - f0) : nvalid;
+    if (!live) return;
+    const bool second = ow + 1 < g.out_w;
+    const size_t pix = ((size_t)b * g.out_h + oh) * g.out_w + ow;
     if (a.y_nhwc) {
-        constexpr int EPV = 16 / sizeof(TY);
-        const int pieces = (cols + EPV - 1) / EPV;    // cpitch and FB are multiples of 8: whole pieces
-        const int total = STHREADS * SPIX * pieces;
-        for (int i = threadIdx.x; i < total; i += STHREADS) {
-            const int slot = i / pieces, q = i - slot * pieces;
-            const long long pix = pix_s[slot];
-            if (pix < 0) continue;
-            TY *dst = reinterpret_cast<TY *>(a.y_nhwc) + (size_t)pix * a.y_cpitch + f0 + q * EPV;
-            const float *src = &out_s[slot][q * EPV];
-            if (sizeof(TY) == 4) {
-                *reinterpret_cast<float4 *>(dst) = *reinterpret_cast<const float4 *>(src);
-            } else {
-                __align__(16) __nv_bfloat16 h[8];
+        // channels [f0, f0 + cols): the last slab also writes the zero padding up to cpitch
+        const int cols = (f0 + FB >= g.n) ? min(FB, a.y_cpitch - f0) : nvalid;
+        TY *d0 = reinterpret_cast<TY *>(a.y_nhwc) + pix * a.y_cpitch + f0;
+        TY *d1 = d0 + a.y_cpitch;
+        if (sizeof(TY) == 4) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) h[e] = __float2bfloat16_rn(src[e]);
-                *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<uint4 *>(h);
-            }
+            for (int q = 0; q < FB / 4; ++q)
+                if (4 * q < cols) {      // cpitch is a multiple of 8: whole pieces
+                    reinterpret_cast<float4 *>(d0)[q] = make_float4(acc0[4 * q], acc0[4 * q + 1], acc0[4 * q + 2], acc0[4 * q + 3]);
+                    if (second) reinterpret_cast<float4 *>(d1)[q] = make_float4(acc1[4 * q], acc1[4 * q + 1], acc1[4 * q + 2], acc1[4 * q + 3]);
+                }
+        } else {
+#pragma unroll
+            for (int q = 0; q < FB / 8; ++q)
+                if (8 * q < cols) {
+                    uint4 p0, p1;
+                    __nv_bfloat162 h;
+                    h = __floats2bfloat162_rn(acc0[8 * q], acc0[8 * q + 1]); p0.x = *reinterpret_cast<uint32_t *>(&h);
+                    h = __floats2bfloat162_rn(acc0[8 * q + 2], acc0[8 * q + 3]); p0.y = *reinterpret_cast<uint32_t *>(&h);
+                    h = __floats2bfloat162_rn(acc0[8 * q + 4], acc0[8 * q + 5]); p0.z = *reinterpret_cast<uint32_t *>(&h);
+                    h = __floats2bfloat162_rn(acc0[8 * q + 6], acc0[8 * q + 7]); p0.w = *reinterpret_cast<uint32_t *>(&h);
+                    h = __floats2bfloat162_rn(acc1[8 * q], acc1[8 * q + 1]); p1.x = *reinterpret_cast<uint32_t *>(&h);
+                    h = __floats2bfloat162_rn(acc1[8 * q + 2], acc1[8 * q + 3]); p1.y = *reinterpret_cast<uint32_t *>(&h);
+                    h = __floats2bfloat162_rn(acc1[8 * q + 4], acc1[8 * q + 5]); p1.z = *reinterpret_cast<uint32_t *>(&h);
+                    h = __floats2bfloat162_rn(acc1[8 * q + 6], acc1[8 * q + 7]); p1.w = *reinterpret_cast<uint32_t *>(&h);
+                    reinterpret_cast<uint4 *>(d0)[q] = p0;
+                    if (second) reinterpret_cast<uint4 *>(d1)[q] = p1;
+                }
         }
     }
-    if (a.y_nchw && live) {
+    if (a.y_nchw) {
         const size_t plane = (size_t)g.out_h * g.out_w;
         float *dst = a.y_nchw + ((size_t)b * g.n + f0) * plane + (size_t)oh * g.out_w + ow;
-        for (int j = 0; j < nvalid; ++j) {
-            dst[j * plane] = out_s[2 * threadIdx.x][j];
-            if (ow + 1 < g.out_w) dst[j * plane + 1] = out_s[2 * threadIdx.x + 1][j];
-        }
+#pragma unroll
+        for (int j = 0; j < FB; ++j)
+            if (j < nvalid) {
+                dst[j * plane] = acc0[j];
+                if (second) dst[j * plane + 1] = acc1[j];
+            }
     }
 }
 

@@ -236,10 +236,24 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
         if ((v == 128 || v == 64 || v == 32) && v >= min_srb && v < srb) srb = v;
     }
     const int min_stages = getenv("DNB_TC_MIN_STAGES") ? atoi(getenv("DNB_TC_MIN_STAGES")) : 4;
+    // two accumulators of bn columns; TMEM is allocated in powers of two >= 32 columns
+    a.tmem_cols = 32;
+    while (a.tmem_cols < 2 * a.bn) a.tmem_cols *= 2;
+    // Narrow tiles (bn <= 128) leave TMEM and, with a short ring, shared memory for a second CTA on the SM:
+    // twice the warps hide the per-tile hand-offs that dominate layers with few K iterations.
+    a.ctas_per_sm = 1;
     int stages = 0;
-    for (;; srb /= 2) {
-        stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.n_tot, residual != nullptr)) / (a.a_bytes + a.b_bytes));
-        if (stages >= min_stages || srb == min_srb) break;
+    const bool allow2 = getenv("DNB_TC_CTAS") ? atoi(getenv("DNB_TC_CTAS")) >= 2 : true;
+    if (allow2 && a.tmem_cols <= 256) {
+        const long budget = (228L * 1024) / 2 - 2048;   // per CTA when two share the SM (1 KB each is reserved by the system)
+        const int s2 = (int)((budget - (long)conv_tc_fixed_smem(srb, a.n_tot, residual != nullptr)) / (a.a_bytes + a.b_bytes));
+        if (s2 >= 2) { a.ctas_per_sm = 2; stages = s2 > 4 ? 4 : s2; }
+    }
+    if (a.ctas_per_sm == 1) {
+        for (;; srb /= 2) {
+            stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.n_tot, residual != nullptr)) / (a.a_bytes + a.b_bytes));
+            if (stages >= min_stages || srb == min_srb) break;
+        }
     }
     if (stages > 8) stages = 8;
     if (const char *e = getenv("DNB_TC_STAGES")) {

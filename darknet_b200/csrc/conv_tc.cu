@@ -226,7 +226,7 @@ __device__ __forceinline__ float act_apply(float x, int runtime_act)
 // NHWC output (bf16 for BF16 plans, f32 with TF32 products otherwise).
 // One staged row is CPC * sizeof(output element) bytes = the swizzle span of the store map.
 template <int ACT, int CPC, bool OUT_BF16>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS)
 conv_tc_kernel(const __grid_constant__ TcArgs a)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -257,8 +257,9 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 1) {  // TMEM: all 512 columns (two accumulators of 256), whole warp
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(512u) : "memory");
+    const uint32_t tmem_cols = (uint32_t)a.tmem_cols, acc_stride = tmem_cols / 2;
+    if (warp == 1) {  // TMEM: two accumulators of tmem_cols/2 columns each (512 in all for 256-filter tiles), whole warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // per-filter epilogue vectors, once per CTA (zero beyond the layer's filters)
@@ -343,7 +344,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             ok = mbar_wait_thread(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1, abort_flag, status, WAIT_ACC_EMPTY);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + acc * 256;
+            const uint32_t d_tmem = tmem_base + acc * acc_stride;
             for (int ki = 0; ki < k_iters; ++ki) {
                 ok = mbar_wait_thread(full0 + 8 * stage, phase, abort_flag, status, WAIT_FULL);
                 if (!ok) break;
@@ -405,7 +406,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             epilogue_bar();                 // all four warps agree on the abort flag from here
             if (*abort_flag) break;
             tc_fence_after();
-            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * acc_stride;
             // One staged chunk of CPC columns per iteration: CPC/16 TMEM loads in flight, one wait, the
             // arithmetic, the staged row, the store.  The loop is deliberately NOT unrolled: its body has to
             // stay resident in the instruction cache next to the MMA warp's loop.
@@ -530,7 +531,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
 }
 
@@ -559,7 +560,8 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
     const bool obf = a.is_bf16 != 0;
     const int cpc = a.store_row_bytes / (obf ? 2 : 4);
     if (cpc != 16 && cpc != 32 && cpc != 64) DNB_FAIL(DNB_EINVAL, "conv_tc: staged row of %d bytes", a.store_row_bytes);
-    const int grid = a.total_tiles < sm_count() ? a.total_tiles : sm_count();
+    const int slots = sm_count() * a.ctas_per_sm;
+    const int grid = a.total_tiles < slots ? a.total_tiles : slots;
     const int max_smem = conv_tc_max_smem();
     // one instantiation per (activation, columns per staged chunk, output type); the opt-in for large
     // dynamic shared memory is per kernel symbol and cheap, so it is set on every launch
