@@ -170,6 +170,24 @@ class Network:
         assert x.size == self.batch * self.inputs
         return self.predict_ptr(x.ctypes.data)
 
+    def submit(self, x) -> None:
+        """First half of a pipelined network_predict: enqueue upload, forward and result
+        copies of one step.  x (numpy or CPU torch tensor, ideally pinned) must stay
+        untouched until the step is collected; at most two steps may be in flight."""
+        if hasattr(x, "data_ptr"):
+            assert x.device.type == "cpu" and x.is_contiguous() and x.numel() == self.batch * self.inputs
+            ptr = x.data_ptr()
+        else:
+            assert x.dtype == np.float32 and x.flags.c_contiguous and x.size == self.batch * self.inputs
+            ptr = x.ctypes.data
+        check(lib().dnb_network_submit(self.handle, C.c_void_p(ptr)))
+
+    def collect(self) -> np.ndarray:
+        """Second half: wait for the oldest submitted step; returns its output as predict does."""
+        out = C.POINTER(C.c_float)()
+        check(lib().dnb_network_collect(self.handle, C.byref(out)))
+        return np.ctypeslib.as_array(out, shape=(self.batch, self.outputs))
+
     def forward(self, x_dev, stream=None):
         """Device-resident forward: x_dev is a CUDA float32 tensor [batch, c, h, w]."""
         assert x_dev.is_cuda and x_dev.is_contiguous() and x_dev.numel() == self.batch * self.inputs

@@ -103,6 +103,7 @@ struct dnb_conv_plan {
     uint32_t *x_bits;        // packed input of an xnor plan
     size_t x_bits_bytes;
     int *status;             // device status word of the tensor-core kernel
+    bool status_shared;      // the word belongs to a network object (one word for all its plans)
     // tensor-core launch block, rebuilt when the input pointer changes
     dnb::TcArgs tc;
     const void *tc_x_ptr;

@@ -76,7 +76,8 @@ extern "C" void dnb_conv_plan_destroy(dnb_conv_plan *p)
 {
     if (!p) return;
     cudaFree(p->scale); cudaFree(p->shift); cudaFree(p->w_tc); cudaFree(p->w_direct); cudaFree(p->w_bits);
-    cudaFree(p->w_mean); cudaFree(p->x_nhwc_scratch); cudaFree(p->x_bits); cudaFree(p->status);
+    cudaFree(p->w_mean); cudaFree(p->x_nhwc_scratch); cudaFree(p->x_bits);
+    if (!p->status_shared) cudaFree(p->status);
     delete p;
 }
 
@@ -246,8 +247,10 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     const bool allow2 = getenv("DNB_TC_CTAS") ? atoi(getenv("DNB_TC_CTAS")) >= 2 : true;
     if (allow2 && a.tmem_cols <= 256) {
         const long budget = (228L * 1024) / 2 - 2048;   // per CTA when two share the SM (1 KB each is reserved by the system)
-        const int s2 = (int)((budget - (long)conv_tc_fixed_smem(srb, a.n_tot, residual != nullptr)) / (a.a_bytes + a.b_bytes));
-        if (s2 >= 2) { a.ctas_per_sm = 2; stages = s2 > 4 ? 4 : s2; }
+        for (int srb2 = srb; srb2 >= min_srb; srb2 /= 2) {   // narrower staged rows if that is what makes two CTAs fit
+            const int s2 = (int)((budget - (long)conv_tc_fixed_smem(srb2, a.n_tot, residual != nullptr)) / (a.a_bytes + a.b_bytes));
+            if (s2 >= 2) { a.ctas_per_sm = 2; stages = s2 > 4 ? 4 : s2; srb = srb2; break; }
+        }
     }
     if (a.ctas_per_sm == 1) {
         for (;; srb /= 2) {

@@ -38,7 +38,10 @@ struct Layer {
     std::vector<int> inputs;
     // yolo
     int anchors = 0, classes = 0;
-    float *host_out = nullptr;     // pinned
+    float *host_out = nullptr;     // pinned; the slot of the step collected last
+    float *host_slot[2] = {nullptr, nullptr};   // pinned result buffers of the two steps that may be in flight
+    cudaEvent_t done = nullptr;    // compute stream: the layer's output is complete
+    cudaEvent_t copied = nullptr;  // copy stream: the device-to-host copy of that output is complete
     // softmax
     int groups = 1;
     float temperature = 1.f;
@@ -120,6 +123,14 @@ struct dnb_network {
     float *export_dev = nullptr;     // scratch for dnb_network_layer_output
     size_t export_elems = 0;
     cudaStream_t stream = nullptr;
+    cudaStream_t copy_stream = nullptr;   // device-to-host copies of finished [yolo] outputs, overlapping later layers
+    cudaStream_t h2d_stream = nullptr;    // host-to-device copy of the next step's images
+    float *input_slot[2] = {nullptr, nullptr};     // device images of the two steps that may be in flight ([0] is input_dev)
+    float *out_host_slot[2] = {nullptr, nullptr};  // pinned output-layer results ([0] is out_host)
+    cudaEvent_t in_ready[2] = {nullptr, nullptr}, fwd_done[2] = {nullptr, nullptr}, copy_done[2] = {nullptr, nullptr};
+    unsigned long long submitted = 0, collected = 0;
+    int *status_dev = nullptr;            // one time-out status word shared by every convolution plan
+    int *status_host = nullptr;           // pinned copy read after each predict
     int device = 0;
     bool weights_loaded = false;
     std::vector<cudaEvent_t> events;
@@ -257,7 +268,8 @@ static int build_network(const char *text, int mode, int batch_override, dnb_net
             L.out = dnb_tensor{nullptr, DNB_NCHW, DNB_F32, net->batch, L.out_c, L.out_h, L.out_w, 0};
             const size_t bytes = tensor_elems(&L.out) * sizeof(float);
             DNB_CUDA(cudaMalloc(&L.out.data, bytes));
-            DNB_CUDA(cudaMallocHost((void **)&L.host_out, bytes));
+            DNB_CUDA(cudaMallocHost((void **)&L.host_slot[0], bytes));
+            L.host_out = L.host_slot[0];
         } else {
             DNB_TRY(alloc_activation(net, &L.out, L.out_c, L.out_h, L.out_w));
         }
@@ -306,6 +318,26 @@ static int build_network(const char *text, int mode, int batch_override, dnb_net
         DNB_TRY(alloc_activation(net, t, net->c, net->h, net->w));
     }
     DNB_CUDA(cudaStreamCreateWithFlags(&net->stream, cudaStreamNonBlocking));
+    DNB_CUDA(cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking));
+    DNB_CUDA(cudaStreamCreateWithFlags(&net->h2d_stream, cudaStreamNonBlocking));
+    net->input_slot[0] = net->input_dev;
+    net->out_host_slot[0] = net->out_host;
+    for (int k = 0; k < 2; ++k) {
+        DNB_CUDA(cudaEventCreateWithFlags(&net->in_ready[k], cudaEventDisableTiming));
+        DNB_CUDA(cudaEventCreateWithFlags(&net->fwd_done[k], cudaEventDisableTiming));
+        DNB_CUDA(cudaEventCreateWithFlags(&net->copy_done[k], cudaEventDisableTiming));
+    }
+    for (Layer &L : net->layers)
+        if (L.kind == L_YOLO) {
+            DNB_CUDA(cudaEventCreateWithFlags(&L.done, cudaEventDisableTiming));
+            DNB_CUDA(cudaEventCreateWithFlags(&L.copied, cudaEventDisableTiming));
+        }
+    DNB_CUDA(cudaMalloc((void **)&net->status_dev, sizeof(int)));
+    DNB_CUDA(cudaMemset(net->status_dev, 0, sizeof(int)));
+    DNB_CUDA(cudaMallocHost((void **)&net->status_host, sizeof(int)));
+    *net->status_host = 0;
+    for (Layer &L : net->layers)
+        if (L.plan) { L.plan->status = net->status_dev; L.plan->status_shared = true; }
     guard.n = nullptr;
     *out = net;
     return DNB_OK;
@@ -335,12 +367,25 @@ extern "C" void dnb_free_network(dnb_network *net)
     for (Layer &L : net->layers) {
         if (L.plan) dnb_conv_plan_destroy(L.plan);
         cudaFree(L.out.data);
-        if (L.host_out) cudaFreeHost(L.host_out);
+        for (float *hp : L.host_slot) if (hp) cudaFreeHost(hp);
+        if (L.copied) cudaEventDestroy(L.copied);
     }
     cudaFree(net->input_dev); cudaFree(net->input_nhwc.data); cudaFree(net->out_dev_nchw); cudaFree(net->export_dev);
     if (net->out_host) cudaFreeHost(net->out_host);
+    if (net->status_host) cudaFreeHost(net->status_host);
+    cudaFree(net->status_dev);
     for (cudaEvent_t e : net->events) cudaEventDestroy(e);
+    for (Layer &L : net->layers) if (L.done) cudaEventDestroy(L.done);
     if (net->stream) cudaStreamDestroy(net->stream);
+    if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
+    if (net->h2d_stream) cudaStreamDestroy(net->h2d_stream);
+    cudaFree(net->input_slot[1]);
+    if (net->out_host_slot[1]) cudaFreeHost(net->out_host_slot[1]);
+    for (int k = 0; k < 2; ++k) {
+        if (net->in_ready[k]) cudaEventDestroy(net->in_ready[k]);
+        if (net->fwd_done[k]) cudaEventDestroy(net->fwd_done[k]);
+        if (net->copy_done[k]) cudaEventDestroy(net->copy_done[k]);
+    }
     delete net;
 }
 
@@ -440,27 +485,88 @@ extern "C" int dnb_network_forward(dnb_network *net, const float *device_input, 
 
 extern "C" int dnb_conv_plan_check_status(dnb_conv_plan *p);
 
+// The second set of buffers exists only once two steps are in flight.
+static int ensure_second_slot(dnb_network *net)
+{
+    if (net->input_slot[1]) return DNB_OK;
+    DNB_CUDA(cudaMalloc((void **)&net->input_slot[1], (size_t)net->batch * net->inputs * sizeof(float)));
+    DNB_CUDA(cudaMallocHost((void **)&net->out_host_slot[1], (size_t)net->batch * net->outputs * sizeof(float)));
+    for (Layer &L : net->layers)
+        if (L.kind == L_YOLO && !L.host_slot[1]) DNB_CUDA(cudaMallocHost((void **)&L.host_slot[1], tensor_elems(&L.out) * sizeof(float)));
+    return DNB_OK;
+}
+
+// Enqueues one step: images to the device on the upload stream, forward_network_gpu's loop
+// (src/network.c:772-785) on the compute stream, and each [yolo] layer's pull to the host
+// (src/yolo_layer.c:360) on the copy stream while the following layers compute.  Up to two steps may be
+// in flight, so the copies of one step overlap the layers of the next.
+extern "C" int dnb_network_submit(dnb_network *net, const float *input)
+{
+    if (!net || !input) DNB_FAIL(DNB_EINVAL, "network_submit: null argument");
+    if (!net->weights_loaded) DNB_FAIL(DNB_EINVAL, "network_submit: load_weights has not been called");
+    if (net->submitted - net->collected >= 2) DNB_FAIL(DNB_EINVAL, "network_submit: two steps are already in flight; collect one first");
+    const int slot = (int)(net->submitted & 1);
+    if (slot == 1) DNB_TRY(ensure_second_slot(net));
+    cudaStream_t s = net->stream, cs = net->copy_stream, hs = net->h2d_stream;
+    float *in_dev = net->input_slot[slot];
+    // the slot's buffers are free: the step that used them last has been collected
+    DNB_CUDA(cudaMemcpyAsync(in_dev, input, (size_t)net->batch * net->inputs * sizeof(float), cudaMemcpyHostToDevice, hs));
+    DNB_CUDA(cudaEventRecord(net->in_ready[slot], hs));
+    DNB_CUDA(cudaStreamWaitEvent(s, net->in_ready[slot], 0));
+    DNB_TRY(prepare_input(net, in_dev, s));
+    for (int i = 0; i < (int)net->layers.size(); ++i) {
+        Layer &L = net->layers[i];
+        if (L.kind == L_YOLO && net->submitted > 0) DNB_CUDA(cudaStreamWaitEvent(s, L.copied, 0));   // the previous step's pull has read L.out
+        DNB_TRY(forward_layer(net, i, in_dev, s));
+        if (L.kind == L_YOLO) {
+            DNB_CUDA(cudaEventRecord(L.done, s));
+            DNB_CUDA(cudaStreamWaitEvent(cs, L.done, 0));
+            DNB_CUDA(cudaMemcpyAsync(L.host_slot[slot], L.out.data, tensor_elems(&L.out) * sizeof(float), cudaMemcpyDeviceToHost, cs));
+            DNB_CUDA(cudaEventRecord(L.copied, cs));
+        }
+    }
+    Layer &last = net->layers.back();
+    if (last.kind != L_YOLO) {   // the output layer is pulled last (src/network.c:786)
+        dnb_tensor o{net->out_dev_nchw, DNB_NCHW, DNB_F32, net->batch, last.out_c, last.out_h, last.out_w, 0};
+        DNB_TRY(launch_convert(&last.out, &o, 0, 0, 0, s));
+        DNB_CUDA(cudaMemcpyAsync(net->out_host_slot[slot], net->out_dev_nchw, (size_t)net->batch * net->outputs * sizeof(float), cudaMemcpyDeviceToHost, s));
+    }
+    DNB_CUDA(cudaMemcpyAsync(net->status_host, net->status_dev, sizeof(int), cudaMemcpyDeviceToHost, s));
+    DNB_CUDA(cudaEventRecord(net->fwd_done[slot], s));
+    DNB_CUDA(cudaEventRecord(net->copy_done[slot], cs));
+    ++net->submitted;
+    return DNB_OK;
+}
+
+// Waits for the oldest step in flight and hands out its results.
+extern "C" int dnb_network_collect(dnb_network *net, float **output)
+{
+    if (!net || !output) DNB_FAIL(DNB_EINVAL, "network_collect: null argument");
+    if (net->submitted == net->collected) DNB_FAIL(DNB_EINVAL, "network_collect: nothing has been submitted");
+    const int slot = (int)(net->collected & 1);
+    ++net->collected;
+    DNB_CUDA(cudaEventSynchronize(net->fwd_done[slot]));
+    DNB_CUDA(cudaEventSynchronize(net->copy_done[slot]));
+    for (Layer &L : net->layers) if (L.kind == L_YOLO) L.host_out = L.host_slot[slot];
+    if (*net->status_host) {
+        const int code = *net->status_host;
+        *net->status_host = 0;
+        cudaMemsetAsync(net->status_dev, 0, sizeof(int), net->stream);
+        DNB_FAIL(DNB_ETIMEOUT, "network_predict: a device-side wait expired in a convolution (code %d: 101 ring slot free, 102 operands "
+                 "landed, 103 accumulator free, 104 accumulator ready, 105 residual tile); the outputs are incomplete", code);
+    }
+    Layer &last = net->layers.back();
+    *output = last.kind == L_YOLO ? last.host_out : net->out_host_slot[slot];
+    return DNB_OK;
+}
+
+// network_predict (src/network.c:497-508): one step, start to finish.
 extern "C" int dnb_network_predict(dnb_network *net, const float *input, float **output)
 {
     if (!net || !input || !output) DNB_FAIL(DNB_EINVAL, "network_predict: null argument");
-    cudaStream_t s = net->stream;
-    DNB_CUDA(cudaMemcpyAsync(net->input_dev, input, (size_t)net->batch * net->inputs * sizeof(float), cudaMemcpyHostToDevice, s));
-    DNB_TRY(dnb_network_forward(net, net->input_dev, s));
-    // yolo layers pull their own output (src/yolo_layer.c:360); the output layer is pulled last (src/network.c:786)
-    for (Layer &L : net->layers)
-        if (L.kind == L_YOLO)
-            DNB_CUDA(cudaMemcpyAsync(L.host_out, L.out.data, tensor_elems(&L.out) * sizeof(float), cudaMemcpyDeviceToHost, s));
-    Layer &last = net->layers.back();
-    if (last.kind != L_YOLO) {
-        dnb_tensor o{net->out_dev_nchw, DNB_NCHW, DNB_F32, net->batch, last.out_c, last.out_h, last.out_w, 0};
-        DNB_TRY(launch_convert(&last.out, &o, 0, 0, 0, s));
-        DNB_CUDA(cudaMemcpyAsync(net->out_host, net->out_dev_nchw, (size_t)net->batch * net->outputs * sizeof(float), cudaMemcpyDeviceToHost, s));
-    }
-    DNB_CUDA(cudaStreamSynchronize(s));
-    for (Layer &L : net->layers)
-        if (L.plan) DNB_TRY(dnb_conv_plan_check_status(L.plan));
-    *output = last.kind == L_YOLO ? last.host_out : net->out_host;
-    return DNB_OK;
+    if (net->submitted != net->collected) DNB_FAIL(DNB_EINVAL, "network_predict: a submitted step has not been collected");
+    DNB_TRY(dnb_network_submit(net, input));
+    return dnb_network_collect(net, output);
 }
 
 extern "C" int dnb_network_num_layers(const dnb_network *net) { return net ? (int)net->layers.size() : 0; }

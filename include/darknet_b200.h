@@ -258,6 +258,19 @@ void dnb_free_network(dnb_network *net);
  * by the network, batch*outputs floats, valid until the next call. */
 int dnb_network_predict(dnb_network *net, const float *input, float **output);
 
+/* network_predict split in two so that a caller streaming batches (the loop of
+ * validate_detector, examples/detector.c:420-520, or predict_classifier's) hides
+ * the host copies: dnb_network_submit enqueues upload, forward and the result
+ * copies of one step and returns; dnb_network_collect waits for the OLDEST
+ * submitted step and hands out its results as dnb_network_predict does.  At most
+ * two steps may be in flight (a third submit returns DNB_EINVAL); the results of
+ * a collected step (and dnb_network_yolo_output's pointers) stay valid until the
+ * step after the next one is submitted.  `input` should be pinned host memory
+ * and must stay untouched until the step is collected.  No counterpart in the
+ * reference, whose network_predict blocks on every pull (src/cuda.c:160-165). */
+int dnb_network_submit(dnb_network *net, const float *input);
+int dnb_network_collect(dnb_network *net, float **output);
+
 /* The device-resident part alone: input already on the device (NCHW f32,
  * batch*inputs floats), no host copies, asynchronous on `stream` (NULL = the
  * legacy default stream). */

@@ -94,6 +94,42 @@ def test_network_device_forward_equals_predict(tmp_path):
     assert net.launches >= net.n and net.flops > 0
 
 
+@pytest.mark.parametrize("name", ["tiny64", "resnet50_32"])
+def test_network_submit_collect_equals_predict(name, tmp_path):
+    """Two steps in flight give, step for step, the bytes the blocking call gives (yolo heads and
+    the output layer), and the in-flight limit is enforced."""
+    cfg, pseed, iseed, dist = CASES[name]
+    params = synth.seeded_params(cfg, pseed)
+    net = build(cfg, params, tmp_path, dn.MODE_TF32)
+    xs = [torch.from_numpy(synth.seeded_input(cfg, iseed + k, dist)).pin_memory() for k in range(5)]
+    yolos = [i for i in range(net.n) if net.layer_type(i) == "yolo"]
+    want = []
+    for x in xs:
+        out = net.predict(x).copy()
+        want.append((out, [net.yolo_output(i).copy() for i in yolos]))
+    got = []
+    net.submit(xs[0])
+    for k in range(1, len(xs)):
+        net.submit(xs[k])
+        if k == 1:
+            with pytest.raises(dn.DarknetB200Error) as e:
+                net.submit(xs[k])          # a third step in flight
+            assert e.value.status == dn.EINVAL
+            with pytest.raises(dn.DarknetB200Error):
+                net.predict(xs[k])         # the blocking call refuses while steps are in flight
+        out = net.collect().copy()
+        got.append((out, [net.yolo_output(i).copy() for i in yolos]))
+    out = net.collect().copy()
+    got.append((out, [net.yolo_output(i).copy() for i in yolos]))
+    with pytest.raises(dn.DarknetB200Error):
+        net.collect()                      # nothing left
+    for (wo, wy), (go, gy) in zip(want, got):
+        assert np.array_equal(wo, go)
+        for a, b in zip(wy, gy):
+            assert np.array_equal(a, b)
+    assert not np.array_equal(want[0][0], want[1][0])
+
+
 def test_network_batch_override_and_errors(tmp_path):
     cfg = synth.yolov3_tiny_cfg(batch=1, size=64)
     params = synth.seeded_params(cfg, 1)
