@@ -525,14 +525,19 @@ extern "C" int dnb_network_submit(dnb_network *net, const float *input)
             DNB_CUDA(cudaEventRecord(L.copied, cs));
         }
     }
+    // Every device-to-host copy goes through the copy stream: a copy enqueued on the compute stream would
+    // queue behind the large [yolo] pulls on the copy engine and hold back the next step's layers.
     Layer &last = net->layers.back();
     if (last.kind != L_YOLO) {   // the output layer is pulled last (src/network.c:786)
         dnb_tensor o{net->out_dev_nchw, DNB_NCHW, DNB_F32, net->batch, last.out_c, last.out_h, last.out_w, 0};
+        if (net->submitted > 0) DNB_CUDA(cudaStreamWaitEvent(s, net->copy_done[slot ^ 1], 0));   // the previous step's pull has read out_dev_nchw
         DNB_TRY(launch_convert(&last.out, &o, 0, 0, 0, s));
-        DNB_CUDA(cudaMemcpyAsync(net->out_host_slot[slot], net->out_dev_nchw, (size_t)net->batch * net->outputs * sizeof(float), cudaMemcpyDeviceToHost, s));
     }
-    DNB_CUDA(cudaMemcpyAsync(net->status_host, net->status_dev, sizeof(int), cudaMemcpyDeviceToHost, s));
     DNB_CUDA(cudaEventRecord(net->fwd_done[slot], s));
+    DNB_CUDA(cudaStreamWaitEvent(cs, net->fwd_done[slot], 0));
+    if (last.kind != L_YOLO)
+        DNB_CUDA(cudaMemcpyAsync(net->out_host_slot[slot], net->out_dev_nchw, (size_t)net->batch * net->outputs * sizeof(float), cudaMemcpyDeviceToHost, cs));
+    DNB_CUDA(cudaMemcpyAsync(net->status_host, net->status_dev, sizeof(int), cudaMemcpyDeviceToHost, cs));
     DNB_CUDA(cudaEventRecord(net->copy_done[slot], cs));
     ++net->submitted;
     return DNB_OK;
@@ -545,8 +550,7 @@ extern "C" int dnb_network_collect(dnb_network *net, float **output)
     if (net->submitted == net->collected) DNB_FAIL(DNB_EINVAL, "network_collect: nothing has been submitted");
     const int slot = (int)(net->collected & 1);
     ++net->collected;
-    DNB_CUDA(cudaEventSynchronize(net->fwd_done[slot]));
-    DNB_CUDA(cudaEventSynchronize(net->copy_done[slot]));
+    DNB_CUDA(cudaEventSynchronize(net->copy_done[slot]));   // follows fwd_done[slot] and every copy of the step
     for (Layer &L : net->layers) if (L.kind == L_YOLO) L.host_out = L.host_slot[slot];
     if (*net->status_host) {
         const int code = *net->status_host;
