@@ -41,6 +41,7 @@ struct alignas(64) TcArgs {
     int total_tiles;      // n_tiles * tiles_w * tiles_h * tiles_b
     int stages;           // depth of the shared-memory ring
     int tmem_cols;        // TMEM columns the CTA allocates: a power of two >= 2*bn (two accumulators)
+    int stage_bufs;       // staging buffers of the epilogue: 2, or 4 with a fused residual (tiles land in them first)
     int ctas_per_sm;      // 2 for narrow tiles (TMEM and shared memory are sized so that two CTAs share an SM), else 1
     int a_bytes, b_bytes; // shared-memory bytes of one stage's activation / weight tile (1024-multiples)
     int store_row_bytes;  // bytes of one staged output row (128, 64 or 32) = swizzle span of tmy
@@ -55,7 +56,7 @@ struct alignas(64) TcArgs {
 };
 int launch_conv_tc(const TcArgs &a, cudaStream_t s);
 size_t conv_tc_smem_bytes(const TcArgs &a);
-size_t conv_tc_fixed_smem(int store_row_bytes, int n_tot, int with_residual);
+size_t conv_tc_fixed_smem(int store_row_bytes, int bn, int stage_bufs);
 int conv_tc_max_smem();
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link).

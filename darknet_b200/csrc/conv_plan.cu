@@ -243,19 +243,25 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     // Narrow tiles (bn <= 128) leave TMEM and, with a short ring, shared memory for a second CTA on the SM:
     // twice the warps hide the per-tile hand-offs that dominate layers with few K iterations.
     a.ctas_per_sm = 1;
+    a.stage_bufs = residual ? 4 : 2;
     int stages = 0;
     const bool allow2 = getenv("DNB_TC_CTAS") ? atoi(getenv("DNB_TC_CTAS")) >= 2 : true;
     if (allow2 && a.tmem_cols <= 256) {
         const long budget = (228L * 1024) / 2 - 2048;   // per CTA when two share the SM (1 KB each is reserved by the system)
         for (int srb2 = srb; srb2 >= min_srb; srb2 /= 2) {   // narrower staged rows if that is what makes two CTAs fit
-            const int s2 = (int)((budget - (long)conv_tc_fixed_smem(srb2, a.n_tot, residual != nullptr)) / (a.a_bytes + a.b_bytes));
+            const int s2 = (int)((budget - (long)conv_tc_fixed_smem(srb2, a.bn, a.stage_bufs)) / (a.a_bytes + a.b_bytes));
             if (s2 >= 2) { a.ctas_per_sm = 2; stages = s2 > 4 ? 4 : s2; srb = srb2; break; }
         }
     }
     if (a.ctas_per_sm == 1) {
+        // The depth of the ring is what hides the operand loads' latency: four slots before wide staged rows.
+        // The exception is a fused residual behind a short K loop, where the epilogue (one round of barrier,
+        // residual wait and store per staged chunk) would outlast the tile's MMAs: fewer, wider chunks then.
+        const int k_iters = g.size * g.size * a.c_blocks;
+        const int want = (residual && k_iters < 64 && min_stages > 3) ? 3 : min_stages;
         for (;; srb /= 2) {
-            stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.n_tot, residual != nullptr)) / (a.a_bytes + a.b_bytes));
-            if (stages >= min_stages || srb == min_srb) break;
+            stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.bn, a.stage_bufs)) / (a.a_bytes + a.b_bytes));
+            if (stages >= want || srb == min_srb) break;
         }
     }
     if (stages > 8) stages = 8;
@@ -466,7 +472,7 @@ extern "C" int dnb_conv_plan_check_status(dnb_conv_plan *p)
     DNB_CUDA(cudaMemcpy(&v, p->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (v) {
         cudaMemset(p->status, 0, sizeof(int));
-        DNB_FAIL(DNB_ETIMEOUT, "conv: a device-side wait expired (code %d: 101 ring slot free, 102 operands landed, 103 accumulator free, 104 accumulator ready)", v);
+        DNB_FAIL(DNB_ETIMEOUT, "conv: a device-side wait expired (code %d: 101 ring slot free, 102 operands landed, 103 accumulator free, 104 accumulator ready, 105 residual tile, 106 shared memory window not 1024-byte aligned)", v);
     }
     return DNB_OK;
 }

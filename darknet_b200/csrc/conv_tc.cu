@@ -37,6 +37,7 @@ namespace dnb {
 
 constexpr int TC_THREADS = 192;
 constexpr int MAX_STAGES = 8;
+constexpr int MAX_RES_BUFS = 4;   // staging buffers with a fused residual; tiles are requested two chunks ahead
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about one second
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -193,6 +194,7 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t sr
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read2() { asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 // barrier among the 128 epilogue threads only (barrier 0 is __syncthreads)
@@ -204,12 +206,12 @@ struct TcShared {
     uint64_t empty[MAX_STAGES];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
-    uint64_t res_full[2];      // residual tile landed in its staging buffer
+    uint64_t res_full[MAX_RES_BUFS];   // residual tile landed in its staging buffer
     uint32_t tmem_base;
     int abort_flag;
 };
 
-enum { WAIT_EMPTY = 101, WAIT_FULL = 102, WAIT_ACC_EMPTY = 103, WAIT_ACC_FULL = 104, WAIT_RESIDUAL = 105 };
+enum { WAIT_EMPTY = 101, WAIT_FULL = 102, WAIT_ACC_EMPTY = 103, WAIT_ACC_FULL = 104, WAIT_RESIDUAL = 105, BAD_SMEM_BASE = 106 };
 enum { ACT_GENERIC = -1 };
 
 
@@ -229,16 +231,23 @@ template <int ACT, int CPC, bool OUT_BF16>
 __global__ void __launch_bounds__(TC_THREADS)
 conv_tc_kernel(const __grid_constant__ TcArgs a)
 {
-    extern __shared__ uint8_t smem_raw[];
-    // operand ring, 1024-byte aligned (the 128-byte swizzle pattern repeats every 1024 bytes)
-    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // operand ring, 1024-byte aligned (the 128-byte swizzle pattern repeats every 1024 bytes).  The kernel
+    // has no static shared memory, so the dynamic window starts aligned; no slack is budgeted for rounding
+    // up, and a launch that finds it otherwise reports that and does nothing.
+    const uint32_t ring = smem_u32(smem_raw);
+    if (ring & 1023u) {
+        if (threadIdx.x == 0) atomicCAS(a.status, 0, BAD_SMEM_BASE);
+        return;
+    }
     const uint32_t stage_bytes = a.a_bytes + a.b_bytes;
     uint8_t *after_ring = smem_raw + (ring - smem_u32(smem_raw)) + (size_t)a.stages * stage_bytes;
-    uint8_t *stage_out = after_ring;                                  // 2 x 128 rows x store_row_bytes
-    uint8_t *stage_res = after_ring + 2 * 128 * (CPC * (OUT_BF16 ? 2 : 4));   // 2 more buffers when a residual is fused
-    float *s_scale = reinterpret_cast<float *>(stage_res + (a.ep.residual ? 2 * 128 * (CPC * (OUT_BF16 ? 2 : 4)) : 0));
-    float *s_shift = s_scale + a.n_tot + 64;
-    TcShared *sh = reinterpret_cast<TcShared *>(s_shift + a.n_tot + 64);
+    // staging buffers of 128 rows x store_row_bytes: two for plain stores; four when a residual is fused, each
+    // then receiving a residual tile first and the finished output rows, in place, afterwards
+    uint8_t *stage_out = after_ring;
+    float *s_scale = reinterpret_cast<float *>(stage_out + (size_t)a.stage_bufs * 128 * (CPC * (OUT_BF16 ? 2 : 4)));
+    float *s_shift = s_scale + a.bn + 64;   // the current filter tile's vectors, padded by one widest chunk
+    TcShared *sh = reinterpret_cast<TcShared *>(s_shift + a.bn + 64);
     volatile int *abort_flag = &sh->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -251,8 +260,8 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&sh->acc_full[i]), 1);
             mbar_init(smem_u32(&sh->acc_empty[i]), 4);
-            mbar_init(smem_u32(&sh->res_full[i]), 1);
         }
+        for (int i = 0; i < MAX_RES_BUFS; ++i) mbar_init(smem_u32(&sh->res_full[i]), 1);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -261,11 +270,6 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     if (warp == 1) {  // TMEM: two accumulators of tmem_cols/2 columns each (512 in all for 256-filter tiles), whole warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    // per-filter epilogue vectors, once per CTA (zero beyond the layer's filters)
-    for (int i = threadIdx.x; i < a.n_tot + 64; i += TC_THREADS) {
-        s_scale[i] = i < a.n_pad ? __ldg(a.ep.scale + i) : 0.f;
-        s_shift[i] = i < a.n_pad ? __ldg(a.ep.shift + i) : 0.f;
     }
     tc_fence_before();
     __syncthreads();
@@ -375,6 +379,8 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         const int runtime_act = a.ep.activation, do_round = a.ep.round_tf32;
         const bool residual = a.ep.residual != nullptr;
         const CUtensorMap *rmap = &a.tmr;
+        const uint32_t buf_mask = residual ? 3u : 1u;   // staging buffers in rotation
+        constexpr int res_ahead = 2;
         const int act2 = a.ep.activation2;
         const float res_alpha = a.ep.alpha, res_beta = a.ep.beta;
         const CUtensorMap *ymap = &a.tmy;
@@ -386,7 +392,9 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         constexpr int q_mask = srb / 16 - 1;
         const int q_xor = (m >> (srb == 128 ? 0 : (srb == 64 ? 1 : 2))) & q_mask;   // 16-byte chunk swizzle of row m
         uint32_t chunk_count = 0;
-        int it = 0;
+        int it = 0, loaded_nt = -1;
+        const float *const ep_scale = a.ep.scale, *const ep_shift = a.ep.shift;
+        const int n_pad = a.n_pad;
         for (int tile = blockIdx.x; tile < total_tiles; tile += grid_stride, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
@@ -394,12 +402,26 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             const int ow0 = (pt % tiles_w) * wt, oh0 = ((pt / tiles_w) % tiles_h) * ht, b0 = (pt / ptiles_wh) * bt;
             const int ow = ow0 + wl, oh = oh0 + hl, b = b0 + bl;
             const bool pix_ok = ow < g.out_w && oh < g.out_h && b < g.batch;
+            if (nt != loaded_nt) {
+                // this filter tile's epilogue vectors (zero beyond the layer's filters).  Every thread is past the
+                // previous tile's last barrier, which follows the last read; the barrier below publishes the writes.
+                for (int i = threadIdx.x - 64; i < bn + 64; i += 128) {
+                    const int gi = nt * bn + i;
+                    const bool in = i < bn && gi < n_pad;
+                    s_scale[i] = in ? __ldg(ep_scale + gi) : 0.f;
+                    s_shift[i] = in ? __ldg(ep_shift + gi) : 0.f;
+                }
+                loaded_nt = nt;
+            }
             if (residual && store_thread) {
-                // residual tile of the first chunk: requested before the accumulator is even ready.  The buffer's
-                // previous readers (two chunks ago) are past the barriers of the chunk in between.
-                const uint32_t rb = chunk_count & 1, bar = smem_u32(&sh->res_full[rb]);
-                mbar_expect_tx(bar, 128u * srb);
-                tma_load_4d(smem_u32(stage_res + (size_t)rb * 128 * srb), rmap, bar, nt * bn, ow0, oh0, b0);
+                // residual tiles of the first two chunks: requested before the accumulator is even ready.  Their
+                // buffers were last read by the stores of four and three chunks ago; two newer stores may be pending.
+                tma_store_wait_read2();
+                for (int d = 0; d < res_ahead && d * CPC < bn; ++d) {
+                    const uint32_t rb = (chunk_count + d) & 3u, bar = smem_u32(&sh->res_full[rb]);
+                    mbar_expect_tx(bar, 128u * srb);
+                    tma_load_4d(smem_u32(stage_out + (size_t)rb * 128 * srb), rmap, bar, nt * bn + d * CPC, ow0, oh0, b0);
+                }
             }
 
             mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, abort_flag, status, WAIT_ACC_FULL, 32);
@@ -428,9 +450,9 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 uint4 res[RES_V];
                 if (residual) {
                     // this chunk's residual tile (TMA zero-fills pixels and channels outside the tensor)
-                    const uint32_t rb = chunk_count & 1;
-                    mbar_wait(smem_u32(&sh->res_full[rb]), (chunk_count >> 1) & 1, abort_flag, status, WAIT_RESIDUAL);
-                    const uint8_t *rrow = stage_res + (size_t)rb * 128 * srb + (size_t)m * srb;
+                    const uint32_t rb = chunk_count & 3u;
+                    mbar_wait(smem_u32(&sh->res_full[rb]), (chunk_count >> 2) & 1, abort_flag, status, WAIT_RESIDUAL);
+                    const uint8_t *rrow = stage_out + (size_t)rb * 128 * srb + (size_t)m * srb;
 #pragma unroll
                     for (int q = 0; q < RES_V; ++q) res[q] = *reinterpret_cast<const uint4 *>(rrow + ((q ^ q_xor) << 4));
                 }
@@ -438,8 +460,8 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 // scale / shift copies are zero beyond the layer's filters and padded by 64 entries
                 const int nl0 = nt * bn + c0;                 // first filter of this chunk
                 const int nvalid = min(bn - c0, g.n - nl0);   // columns of this chunk that are real filters
-                const float4 *sc4 = reinterpret_cast<const float4 *>(s_scale + nl0);
-                const float4 *sf4 = reinterpret_cast<const float4 *>(s_shift + nl0);
+                const float4 *sc4 = reinterpret_cast<const float4 *>(s_scale + c0);
+                const float4 *sf4 = reinterpret_cast<const float4 *>(s_shift + c0);
 #pragma unroll
                 for (int q = 0; q < CPC / 4; ++q) {
                     const float4 sc = sc4[q], sf = sf4[q];
@@ -466,15 +488,12 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                         r[j] = __float_as_uint(j < nvalid ? t : 0.f);
                     }
                 }
-                const uint32_t buf = chunk_count & 1;
-                if (store_thread && chunk_count >= 2) tma_store_wait_read1();   // the store that last read this buffer is done
-                epilogue_bar();
-                if (residual && store_thread && c0 + CPC < bn) {
-                    // next chunk's residual tile into the other buffer: every thread finished reading it one chunk ago
-                    const uint32_t nb = (chunk_count + 1) & 1, bar = smem_u32(&sh->res_full[nb]);
-                    mbar_expect_tx(bar, 128u * srb);
-                    tma_load_4d(smem_u32(stage_res + (size_t)nb * 128 * srb), rmap, bar, nt * bn + c0 + CPC, ow0, oh0, b0);
-                }
+                const uint32_t buf = chunk_count & buf_mask;
+                if (!residual) {
+                    if (store_thread && chunk_count >= 2) tma_store_wait_read1();   // the store that last read this buffer is done
+                    epilogue_bar();
+                }   // with a residual the buffer is this thread's to overwrite: its tile landed after that store, and
+                    // a thread reads and writes its own row only
                 uint8_t *row = stage_out + (size_t)buf * 128 * srb + (size_t)m * srb;
                 if (!out_bf16) {
 #pragma unroll
@@ -500,6 +519,13 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                     // the TMA unit clips the box at the tensor's extents: ragged tiles need no predicates
                     if (y_nhwc) tma_store_4d(ymap, smem_u32(stage_out + (size_t)buf * 128 * srb), nl0, ow0, oh0, b0);
                     tma_store_commit();
+                    if (residual && c0 + res_ahead * CPC < bn) {
+                        // the tile two chunks on goes into the buffer of two chunks ago, once that chunk's store has read it
+                        tma_store_wait_read2();
+                        const uint32_t nb = (chunk_count + res_ahead) & 3u, bar = smem_u32(&sh->res_full[nb]);
+                        mbar_expect_tx(bar, 128u * srb);
+                        tma_load_4d(smem_u32(stage_out + (size_t)nb * 128 * srb), rmap, bar, nt * bn + c0 + res_ahead * CPC, ow0, oh0, b0);
+                    }
                 }
                 if (y_nchw && pix_ok) {
                     // Darknet-layout copy: this thread's pixel, one filter plane per staged column, read
@@ -536,14 +562,14 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
 }
 
 // ------------------------------------------------------------------ host side
-size_t conv_tc_fixed_smem(int store_row_bytes, int n_tot, int with_residual)
+size_t conv_tc_fixed_smem(int store_row_bytes, int bn, int stage_bufs)
 {
-    return 1024 + (with_residual ? 4 : 2) * 128 * (size_t)store_row_bytes + 2 * sizeof(float) * ((size_t)n_tot + 64) + sizeof(TcShared) + 64;
+    return stage_bufs * 128 * (size_t)store_row_bytes + 2 * sizeof(float) * ((size_t)bn + 64) + sizeof(TcShared) + 16;
 }
 
 size_t conv_tc_smem_bytes(const TcArgs &a)
 {
-    return (size_t)a.stages * (a.a_bytes + a.b_bytes) + conv_tc_fixed_smem(a.store_row_bytes, a.n_tot, a.ep.residual != nullptr);
+    return (size_t)a.stages * (a.a_bytes + a.b_bytes) + conv_tc_fixed_smem(a.store_row_bytes, a.bn, a.stage_bufs);
 }
 
 int conv_tc_max_smem()

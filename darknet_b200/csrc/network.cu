@@ -557,7 +557,7 @@ extern "C" int dnb_network_collect(dnb_network *net, float **output)
         *net->status_host = 0;
         cudaMemsetAsync(net->status_dev, 0, sizeof(int), net->stream);
         DNB_FAIL(DNB_ETIMEOUT, "network_predict: a device-side wait expired in a convolution (code %d: 101 ring slot free, 102 operands "
-                 "landed, 103 accumulator free, 104 accumulator ready, 105 residual tile); the outputs are incomplete", code);
+                 "landed, 103 accumulator free, 104 accumulator ready, 105 residual tile, 106 shared memory window not 1024-byte aligned); the outputs are incomplete", code);
     }
     Layer &last = net->layers.back();
     *output = last.kind == L_YOLO ? last.host_out : net->out_host_slot[slot];
