@@ -23,6 +23,22 @@ struct DirectArgs {
 };
 int launch_conv_direct(const DirectArgs &a, cudaStream_t s);
 
+// ---- conv_stem_tc.cu : first layer (3x3, at most 3 input channels) on tcgen05, im2col rows built by the threads
+struct StemTcArgs {
+    const float *x;                      // f32 input, any layout through element strides
+    long long xs_b, xs_c, xs_h, xs_w;
+    const float *w;                      // weights [K][npg_pad], K = c*9 (the direct kernel's packing)
+    int npg_pad;
+    void *y;                             // channels-last output, pitch == n
+    int y_dtype, y_cpitch;
+    int n_pad, tmem_cols, tiles, npix;   // filled by the launcher
+    int *status;
+    ConvGeom g;
+    ConvEpilogue ep;
+};
+bool conv_stem_tc_covers(const ConvGeom &g);
+int launch_conv_stem_tc(StemTcArgs a, cudaStream_t s);
+
 // ---- conv_tc.cu : implicit GEMM on tcgen05 / TMEM, operands by TMA
 struct alignas(64) TcArgs {
     CUtensorMap tmx[4];   // activation maps: one per (row parity, column parity) lattice of a strided conv
@@ -91,6 +107,7 @@ struct dnb_conv_plan {
     int n_pad;               // filters rounded up to 16
     int c_pad;               // input channels rounded up to 8 (cpitch the kernel expects of NHWC input)
     bool params_set;
+    bool stem_tc;            // a direct plan whose channels-last f32-input launches use the tensor-core first-layer kernel
     // derived device tensors
     float *scale, *shift;    // [n_pad] folded batchnorm / bias
     void *w_tc;              // [taps][n_pad][c_pad] f32 (TF32-rounded) or bf16

@@ -67,6 +67,9 @@ extern "C" int dnb_conv_plan_create(const dnb_conv_desc *d, int mode, dnb_conv_p
     if (d->xnor) p->kernel = K_XNOR;
     else if (mode == DNB_MODE_FP32 || d->groups != 1 || d->c < 8) p->kernel = K_DIRECT;
     else p->kernel = mode == DNB_MODE_BF16 ? K_TC_BF16 : K_TC_TF32;
+    // RGB first layers of the TF32 / BF16 modes: tensor cores with thread-built im2col rows (DNB_STEM_TC=0 keeps the FP32 kernel)
+    const char *stem_env = getenv("DNB_STEM_TC");
+    p->stem_tc = p->kernel == K_DIRECT && mode != DNB_MODE_FP32 && !d->xnor && conv_stem_tc_covers(p->g) && !(stem_env && atoi(stem_env) == 0);
     cudaGetDevice(&p->device);
     *out = p;
     return DNB_OK;
@@ -81,7 +84,11 @@ extern "C" void dnb_conv_plan_destroy(dnb_conv_plan *p)
     delete p;
 }
 
-extern "C" const char *dnb_conv_plan_kernel(const dnb_conv_plan *p) { return p ? kKernelNames[p->kernel] : ""; }
+extern "C" const char *dnb_conv_plan_kernel(const dnb_conv_plan *p)
+{
+    if (!p) return "";
+    return p->stem_tc ? "stem_tc_tf32" : kKernelNames[p->kernel];
+}
 
 template <typename T>
 static int upload(T **dst, const std::vector<T> &src)
@@ -374,7 +381,22 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
     // f32 channels-last results of a TF32 network feed the next tensor-core layer: round them once here
     ep.round_tf32 = (p->mode == DNB_MODE_TF32 && y_nhwc && y_dtype == DNB_F32 && !y_nchw) ? 1 : 0;
 
-    if (p->kernel == K_DIRECT) {
+    if (p->kernel == K_DIRECT && p->stem_tc && x->dtype == DNB_F32 && y_nhwc && !y_nchw && y_cpitch == g.n) {
+        StemTcArgs a;
+        a.x = (const float *)x->data;
+        if (x->layout == DNB_NHWC) { a.xs_c = 1; a.xs_w = x->cpitch; a.xs_h = (long long)g.w * x->cpitch; a.xs_b = (long long)g.h * a.xs_h; }
+        else { a.xs_w = 1; a.xs_h = g.w; a.xs_c = (long long)g.h * g.w; a.xs_b = (long long)g.c * a.xs_c; }
+        a.w = p->w_direct; a.npg_pad = p->npg_pad;
+        a.y = y_nhwc; a.y_dtype = y_dtype; a.y_cpitch = y_cpitch;
+        if (!p->status) {
+            DNB_CUDA(cudaMalloc((void **)&p->status, sizeof(int)));
+            DNB_CUDA(cudaMemset(p->status, 0, sizeof(int)));
+        }
+        a.status = p->status;
+        a.g = g; a.ep = ep;
+        return launch_conv_stem_tc(a, s);
+    }
+    if (p->kernel == K_DIRECT) {   // also a first-layer plan asked for Darknet's layout or given bf16 input
         DirectArgs a;
         a.x = x->data; a.x_dtype = x->dtype;
         if (x->layout == DNB_NHWC) { a.xs_c = 1; a.xs_w = x->cpitch; a.xs_h = (long long)g.w * x->cpitch; a.xs_b = (long long)g.h * a.xs_h; }

@@ -1,0 +1,293 @@
+// First-layer convolution on the sm_100a tensor cores: 3x3 filters over at most 3 input channels
+// (the RGB stems of YOLOv3, YOLOv3-tiny and Darknet-19), K = c*9 <= 27 padded to 32.
+//
+// The K extent is one 128-byte row of TF32 values, far too short for the TMA-fed ring of the general
+// kernel (nine 32-byte-wide loads per tile).  Here the 128 threads of a CTA build the im2col rows
+// themselves: thread m gathers the 27 input values of output pixel m of the tile from the image as
+// the caller laid it out (NCHW or channels-last, through element strides; out-of-image taps read as
+// zero, which is the padding), rounds them to TF32 and writes its row into shared memory in the
+// 128-byte-swizzled K-major layout tcgen05.mma reads.  One thread then issues four K=8 MMAs against the
+// filter matrix, which sits in shared memory for the life of the CTA, into one of two TMEM accumulators;
+// the epilogue of tile i (TMEM -> registers -> folded batchnorm / bias, activation -> 16-byte stores of
+// the pixel's channels-last row) runs while the MMAs of tile i+1 are in flight.  Tiles are runs of 128
+// consecutive output pixels of the flattened [batch][out_h][out_w] index, so a CTA's stores are one
+// contiguous span.  Several CTAs share an SM and hide each other's load latency.
+//
+// Every mbarrier wait is bounded; on expiry the CTA records a code in the status word and leaves.
+//
+// Replaces forward_convolutional_layer_gpu (src/convolutional_kernels.cu:73-135 of the reference) for
+// size 3, groups 1, c <= 3, n a multiple of 16 up to 64, channels-last output; im2col row order
+// c*9 + kh*3 + kw as in src/im2col.c:15-39.
+#include "common.h"
+#include "conv.h"
+#include "device_utils.cuh"
+#include "tc_ptx.cuh"
+
+namespace dnb {
+
+constexpr int ST_THREADS = 128;
+constexpr int ST_A_BYTES = 128 * 128;   // one im2col tile: 128 rows of 32 TF32 values
+
+struct StemShared {
+    uint64_t acc_full[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+enum { ST_WAIT_ACC = 104, ST_BAD_SMEM_BASE = 106 };
+enum { ST_ACT_GENERIC = -1 };
+
+template <int ACT>
+__device__ __forceinline__ float stem_act(float x, int runtime_act)
+{
+    if (ACT == DNB_LINEAR) return x;
+    if (ACT == DNB_LEAKY) return fmaxf(x, 0.1f * x);
+    return activate_call(x, runtime_act);
+}
+
+// C: input channels (1..3); ACT: activation folded at compile time or ST_ACT_GENERIC; OUT_BF16: storage
+// type of the channels-last output.
+template <int C, int ACT, bool OUT_BF16>
+__global__ void __launch_bounds__(ST_THREADS, 8)
+conv_stem_tc_kernel(const __grid_constant__ StemTcArgs a)
+{
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (smem_u32(smem) & 1023u) {   // the swizzle pattern repeats every 1024 bytes
+        if (threadIdx.x == 0) atomicCAS(a.status, 0, ST_BAD_SMEM_BASE);
+        return;
+    }
+    constexpr int K = C * 9;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int n_pad = a.n_pad;
+    uint8_t *sA = smem;                           // 2 x 128 rows x 128 bytes
+    uint8_t *sB = smem + 2 * ST_A_BYTES;          // n_pad rows x 128 bytes
+    float *s_scale = reinterpret_cast<float *>(sB + (size_t)n_pad * 128);
+    float *s_shift = s_scale + n_pad;
+    StemShared *sh = reinterpret_cast<StemShared *>(s_shift + n_pad);
+    volatile int *abort_flag = &sh->abort_flag;
+    const ConvGeom g = a.g;
+
+    // filters: row f holds w[f][0..K) rounded to TF32, zero beyond K and beyond the layer's filters
+    for (int i = tid; i < n_pad * 8; i += ST_THREADS) {
+        const int f = i >> 3, q = i & 7;
+        uint32_t v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int k = 4 * q + e;
+            v[e] = (k < K && f < g.n) ? __float_as_uint(round_tf32(__ldg(a.w + (size_t)k * a.npg_pad + f))) : 0u;
+        }
+        *reinterpret_cast<uint4 *>(sB + f * 128 + ((q ^ (f & 7)) << 4)) = make_uint4(v[0], v[1], v[2], v[3]);
+    }
+    for (int i = tid; i < n_pad; i += ST_THREADS) {
+        s_scale[i] = i < g.n ? __ldg(a.ep.scale + i) : 0.f;
+        s_shift[i] = i < g.n ? __ldg(a.ep.shift + i) : 0.f;
+    }
+    if (tid == 0) {
+        mbar_init(smem_u32(&sh->acc_full[0]), 1);
+        mbar_init(smem_u32(&sh->acc_full[1]), 1);
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const uint32_t tmem_cols = (uint32_t)a.tmem_cols, acc_stride = tmem_cols / 2;
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_async_smem();   // the filter rows are read by the tensor cores
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+
+    // register copies: every asm statement below is a compiler memory barrier
+    const float *const x = a.x;
+    const long long xs_b = a.xs_b;
+    const int xs_c = (int)a.xs_c, xs_h = (int)a.xs_h, xs_w = (int)a.xs_w;
+    const int npix = a.npix, tiles = a.tiles, plane = g.out_h * g.out_w;
+    const int runtime_act = a.ep.activation, do_round = a.ep.round_tf32;
+    uint8_t *const y = reinterpret_cast<uint8_t *>(a.y);
+    const size_t y_row_bytes = (size_t)a.y_cpitch * (OUT_BF16 ? 2 : 4);
+    int *const status = a.status;
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n_pad >> 3) << 17) | ((128u >> 4) << 24);   // TF32 x TF32 -> f32, M 128, N n_pad
+    const uint64_t db = make_smem_desc(smem_u32(sB), 128);
+    const uint64_t da0 = make_smem_desc(smem_u32(sA), 128);
+    const uint32_t bar0 = smem_u32(&sh->acc_full[0]);
+    const uint32_t row_off = (uint32_t)tid * 128u, sw = (uint32_t)(tid & 7);
+
+    bool failed = false;
+    int prev_p = npix;   // output pixel this thread finishes in the next epilogue
+    int it = 0;
+    for (int tile = blockIdx.x;; tile += gridDim.x, ++it) {
+        const bool have = tile < tiles;   // uniform over the CTA
+        const int buf = it & 1;
+        const int p = tile * ST_THREADS + tid;
+        if (have) {
+            // ---- gather this thread's im2col row
+            float v[32];
+            const bool valid = p < npix;
+            const int b = p / plane, rem = p - b * plane;
+            const int oy = rem / g.out_w, ox = rem - oy * g.out_w;
+            const int iy0 = oy * g.stride - g.pad, ix0 = ox * g.stride - g.pad;
+            const float *xb = x + (size_t)b * xs_b;
+#pragma unroll
+            for (int c = 0; c < C; ++c)
+#pragma unroll
+                for (int kh = 0; kh < 3; ++kh)
+#pragma unroll
+                    for (int kw = 0; kw < 3; ++kw) {
+                        const int iy = iy0 + kh, ix = ix0 + kw;
+                        const bool in = valid && (unsigned)iy < (unsigned)g.h && (unsigned)ix < (unsigned)g.w;
+                        v[c * 9 + kh * 3 + kw] = in ? __ldg(xb + c * xs_c + iy * xs_h + ix * xs_w) : 0.f;
+                    }
+#pragma unroll
+            for (int k = K; k < 32; ++k) v[k] = 0.f;
+            uint8_t *row = sA + buf * ST_A_BYTES + row_off;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<uint4 *>(row + ((q ^ sw) << 4)) =
+                    make_uint4(__float_as_uint(round_tf32(v[4 * q])), __float_as_uint(round_tf32(v[4 * q + 1])),
+                               __float_as_uint(round_tf32(v[4 * q + 2])), __float_as_uint(round_tf32(v[4 * q + 3])));
+            fence_async_smem();   // rows visible to the tensor cores
+        }
+        tc_fence_before();        // this thread's TMEM loads of the previous epilogue precede the barrier
+        if (__syncthreads_or(failed)) break;
+        if (have && tid == 0) {
+            tc_fence_after();
+            const uint32_t d = tmem_base + buf * acc_stride;
+            const uint64_t da = da0 + (uint64_t)(buf * (ST_A_BYTES >> 4));
+            umma<false>(d, da, db, idesc, 0u);
+            umma<false>(d, da + 2, db + 2, idesc, 1u);
+            umma<false>(d, da + 4, db + 4, idesc, 1u);
+            umma<false>(d, da + 6, db + 6, idesc, 1u);
+            umma_commit(bar0 + 8 * buf);
+        }
+        __syncwarp();
+        if (it > 0) {
+            // ---- epilogue of the previous tile, overlapping the MMAs just issued
+            const int pb = (it - 1) & 1;
+            if (!mbar_wait(bar0 + 8 * pb, ((it - 1) >> 1) & 1, abort_flag, status, ST_WAIT_ACC)) {
+                failed = true;
+            } else {
+                tc_fence_after();
+                const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + pb * acc_stride;
+                const bool store = prev_p < npix;
+                uint8_t *dst = y + (size_t)prev_p * y_row_bytes;
+#pragma unroll 1
+                for (int c0 = 0; c0 < n_pad; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(t_row + c0, r);
+                    tmem_ld_wait();
+                    float o[16];
+                    const float4 *sc4 = reinterpret_cast<const float4 *>(s_scale + c0);
+                    const float4 *sf4 = reinterpret_cast<const float4 *>(s_shift + c0);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 sc = sc4[q], sf = sf4[q];
+                        const float scv[4] = {sc.x, sc.y, sc.z, sc.w}, sfv[4] = {sf.x, sf.y, sf.z, sf.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int j = 4 * q + e;
+                            float t = stem_act<ACT>(fmaf(__uint_as_float(r[j]), scv[e], sfv[e]), runtime_act);
+                            if (do_round) t = round_tf32(t);
+                            o[j] = c0 + j < g.n ? t : 0.f;
+                        }
+                    }
+                    if (store) {
+                        if (!OUT_BF16) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                reinterpret_cast<float4 *>(dst + (size_t)c0 * 4)[q] = make_float4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < 2; ++q) {
+                                uint4 pk;
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(o[8 * q], o[8 * q + 1]);
+                                __nv_bfloat162 h1 = __floats2bfloat162_rn(o[8 * q + 2], o[8 * q + 3]);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(o[8 * q + 4], o[8 * q + 5]);
+                                __nv_bfloat162 h3 = __floats2bfloat162_rn(o[8 * q + 6], o[8 * q + 7]);
+                                pk.x = *reinterpret_cast<uint32_t *>(&h0); pk.y = *reinterpret_cast<uint32_t *>(&h1);
+                                pk.z = *reinterpret_cast<uint32_t *>(&h2); pk.w = *reinterpret_cast<uint32_t *>(&h3);
+                                reinterpret_cast<uint4 *>(dst + (size_t)c0 * 2)[q] = pk;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        if (!have) break;
+        prev_p = p;
+    }
+
+    // ---- teardown (also the abort path)
+    if (*abort_flag) {   // give MMAs that may still read shared memory time to retire
+        const long long t0 = clock64();
+        while (clock64() - t0 < 4000000LL) { }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+bool conv_stem_tc_covers(const ConvGeom &g)
+{
+    return g.size == 3 && g.groups == 1 && g.c >= 1 && g.c <= 3 && g.n % 16 == 0 && g.n <= 64 && g.stride >= 1 && g.stride <= 2;
+}
+
+template <int C, int ACT, bool OBF>
+static int launch_one(const StemTcArgs &a, size_t smem, int grid_limit_per_sm, cudaStream_t s)
+{
+    auto kern = conv_stem_tc_kernel<C, ACT, OBF>;
+    DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // all of the SM's configurable memory as shared memory, so that several CTAs are resident
+    DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    int per_sm = (int)((228 * 1024) / (smem + 1024));   // each resident CTA also reserves 1 KB
+    if (per_sm > 2048 / ST_THREADS) per_sm = 2048 / ST_THREADS;
+    if (per_sm > 65536 / (64 * ST_THREADS)) per_sm = 65536 / (64 * ST_THREADS);   // the kernel is held to 64 registers
+    if (per_sm < 1) DNB_FAIL(DNB_ECUDA, "first-layer kernel: %zu bytes of shared memory do not fit", smem);
+    if (per_sm > grid_limit_per_sm) per_sm = grid_limit_per_sm;
+    long long grid = (long long)sm_count() * per_sm;
+    if (grid > a.tiles) grid = a.tiles;
+    kern<<<(unsigned)grid, ST_THREADS, smem, s>>>(a);
+    DNB_LAUNCH_CHECK("conv_stem_tc");
+    return DNB_OK;
+}
+
+template <int C, bool OBF>
+static int launch_act(const StemTcArgs &a, size_t smem, int lim, cudaStream_t s)
+{
+    if (a.ep.activation == DNB_LEAKY) return launch_one<C, DNB_LEAKY, OBF>(a, smem, lim, s);
+    if (a.ep.activation == DNB_LINEAR) return launch_one<C, DNB_LINEAR, OBF>(a, smem, lim, s);
+    return launch_one<C, ST_ACT_GENERIC, OBF>(a, smem, lim, s);
+}
+
+int launch_conv_stem_tc(StemTcArgs a, cudaStream_t s)
+{
+    const ConvGeom &g = a.g;
+    if (!conv_stem_tc_covers(g)) DNB_FAIL(DNB_EUNSUPPORTED, "first-layer kernel: geometry outside its coverage");
+    const long long npix = (long long)g.batch * g.out_h * g.out_w;
+    if (npix + ST_THREADS >= (1LL << 31)) DNB_FAIL(DNB_EUNSUPPORTED, "first-layer kernel: %lld output pixels", npix);
+    if (a.xs_c >= (1LL << 31) / 4 || a.xs_h >= (1LL << 31) / 4) DNB_FAIL(DNB_EUNSUPPORTED, "first-layer kernel: image too large for 32-bit offsets");
+    a.npix = (int)npix;
+    a.tiles = (int)((npix + ST_THREADS - 1) / ST_THREADS);
+    a.n_pad = round_up(g.n, 16);
+    a.tmem_cols = 32;
+    while (a.tmem_cols < 2 * a.n_pad) a.tmem_cols *= 2;
+    size_t smem = 2 * ST_A_BYTES + (size_t)a.n_pad * 128 + 2 * sizeof(float) * a.n_pad + sizeof(StemShared) + 16;
+    // TMEM holds 512 columns per SM: never more CTAs on an SM than can all hold their accumulators at once.
+    // The grid is sized for that, and the shared-memory request is padded so that one more would not fit.
+    const int lim = 512 / a.tmem_cols;
+    const size_t sm_bytes = 228 * 1024, reserved = 1024;   // per SM, and per resident CTA
+    if ((smem + reserved) * (lim + 1) <= sm_bytes) smem = sm_bytes / (lim + 1) - reserved + 16;
+    const bool obf = a.y_dtype == DNB_BF16;
+    switch (g.c) {
+    case 1: return obf ? launch_act<1, true>(a, smem, lim, s) : launch_act<1, false>(a, smem, lim, s);
+    case 2: return obf ? launch_act<2, true>(a, smem, lim, s) : launch_act<2, false>(a, smem, lim, s);
+    default: return obf ? launch_act<3, true>(a, smem, lim, s) : launch_act<3, false>(a, smem, lim, s);
+    }
+}
+
+}  // namespace dnb

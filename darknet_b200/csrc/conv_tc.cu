@@ -32,173 +32,13 @@
 #include "common.h"
 #include "conv.h"
 #include "device_utils.cuh"
+#include "tc_ptx.cuh"
 
 namespace dnb {
 
 constexpr int TC_THREADS = 192;
 constexpr int MAX_STAGES = 8;
 constexpr int MAX_RES_BUFS = 4;   // staging buffers with a fused residual; tiles are requested two chunks ahead
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about one second
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    return done;
-}
-
-// Bounded wait by ONE polling lane per warp; the result is broadcast to the warp.  Returns false when
-// the wait expired or another role aborted.  Polling goes through shared memory, which the tensor
-// cores read their operands from: one lane per warp polls, with a hardware suspend hint, and waiters
-// that are not latency-critical back off with nanosleep between polls.
-__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns)
-{
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
-    return done;
-}
-
-// Bounded wait for a loop that a single thread runs (the TMA and MMA roles): no warp traffic at all.
-__device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
-{
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    int spins = 0;
-    while (!mbar_try_wait_hint(bar, parity, 1000u)) {
-        if ((++spins & 0x3f) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                atomicCAS(status, 0, code);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
-                                          unsigned backoff_ns = 0)
-{
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) {
-        if (!mbar_try_wait(bar, parity)) {
-            const long long t0 = clock64();
-            int spins = 0;
-            while (!mbar_try_wait_hint(bar, parity, 2000u)) {
-                if (backoff_ns) __nanosleep(backoff_ns);
-                if ((++spins & 0x3f) == 0) {
-                    if (*abort_flag) { ok = 0; break; }
-                    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                        *abort_flag = 1;
-                        atomicCAS(status, 0, code);
-                        ok = 0;
-                        break;
-                    }
-                }
-            }
-        }
-    }
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    return ok != 0;
-}
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-
-// Shared-memory matrix descriptor, K-major operand whose rows are `row_bytes`
-// long and equal to the swizzle span; 8-row groups are 8*row_bytes apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int row_bytes)
-{
-    const uint64_t layout = row_bytes == 128 ? 2 : (row_bytes == 64 ? 4 : 6);  // SWIZZLE_128B / 64B / 32B
-    uint64_t d = (uint64_t)((addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)1 << 16;                                  // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)((8 * row_bytes) >> 4) << 32;             // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                                  // descriptor version for sm_100
-    d |= layout << 61;
-    return d;
-}
-
-// The operand kind is a template parameter on purpose: with a run-time `if` the compiler predicates BOTH
-// tcgen05.mma instructions, and the predicated-off one still occupies the tensor pipe's issue path.
-template <bool IS_BF16>
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
-{
-    if (IS_BF16) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-    } else {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-    }
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// TMA store of one staged output chunk (shared -> global), bulk-group completion.
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2, int c3)
-{
-    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_read2() { asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// barrier among the 128 epilogue threads only (barrier 0 is __syncthreads)
-__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // ------------------------------------------------------------------ kernel
 struct TcShared {

@@ -259,6 +259,37 @@ def test_conv_direct_fp32(name, layouts):
     assert rel_to_max(got, oracle_conv(case)) < 1e-5
 
 
+STEM_CASES = {
+    "rgb_n32": dict(b=3, c=3, h=37, w=29, n=32, size=3, dist="uniform"),
+    "rgb_n16": dict(b=2, c=3, h=32, w=32, n=16, size=3, dist="uniform"),
+    "rgb_n64_s2": dict(b=2, c=3, h=31, w=45, n=64, size=3, stride=2, dist="uniform"),
+    "rgb_n48_nopad_linear": dict(b=1, c=3, h=20, w=20, n=48, size=3, pad=0, bn=False, act="linear"),
+    "gray_n32_logistic": dict(b=2, c=1, h=24, w=24, n=32, size=3, act="logistic"),
+    "two_channels": dict(b=1, c=2, h=16, w=130, n=32, size=3),
+    "many_tiles": dict(b=4, c=3, h=160, w=160, n=32, size=3, dist="uniform"),
+}
+
+
+@pytest.mark.parametrize("name", list(STEM_CASES))
+@pytest.mark.parametrize("mode", [dn.MODE_TF32, dn.MODE_BF16])
+def test_conv_stem_tensor_core(name, mode):
+    """First-layer kernel (im2col rows built by the threads, TF32 products): f32 input in Darknet's
+    layout or channels-last, channels-last output in the mode's storage type.  Asked for Darknet's
+    layout on the output side, the same plan falls back to the FP32 kernel."""
+    case = conv_case(150, **STEM_CASES[name])
+    want = oracle_conv(case)
+    tol = TOL_TF32 if mode == dn.MODE_TF32 else TOL_BF16
+    plan, got, _ = run_conv(case, mode, "nchw", "nhwc")
+    assert plan.kernel == "stem_tc_tf32"
+    err = rel_to_max(got, want)
+    assert err < tol, f"{name}: rel error {err:.3g}"
+    if mode == dn.MODE_TF32:
+        _, got2, _ = run_conv(case, mode, "nhwc", "nhwc")     # channels-last f32 input through the same strides
+        assert np.array_equal(got, got2)
+        _, got3, _ = run_conv(case, mode, "nchw", "nchw")     # fallback: exact FP32 arithmetic
+        assert rel_to_max(got3, want) < 1e-5
+
+
 TC_CASES = {
     "1x1_c32_onetile": dict(b=1, c=32, h=8, w=16, n=16, size=1, bn=False, act="linear"),
     "1x1_c64": dict(b=2, c=64, h=9, w=9, n=40, size=1),
