@@ -24,7 +24,9 @@ struct DirectArgs {
 int launch_conv_direct(const DirectArgs &a, cudaStream_t s);
 
 // ---- conv_stem_tc.cu : first layer (3x3, at most 3 input channels) on tcgen05, im2col rows built by the threads
-struct StemTcArgs {
+struct alignas(64) StemTcArgs {
+    CUtensorMap tmy;                     // channels-last output as [pixel][channel], 32-row boxes
+    int tma_store;                       // rows leave through tmy (else plain stores)
     const float *x;                      // f32 input, any layout through element strides
     long long xs_b, xs_c, xs_h, xs_w;
     const float *w;                      // weights [K][npg_pad], K = c*9 (the direct kernel's packing)

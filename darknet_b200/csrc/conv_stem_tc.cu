@@ -7,11 +7,13 @@
 // the caller laid it out (NCHW or channels-last, through element strides; out-of-image taps read as
 // zero, which is the padding), rounds them to TF32 and writes its row into shared memory in the
 // 128-byte-swizzled K-major layout tcgen05.mma reads.  One thread then issues four K=8 MMAs against the
-// filter matrix, which sits in shared memory for the life of the CTA, into one of two TMEM accumulators;
-// the epilogue of tile i (TMEM -> registers -> folded batchnorm / bias, activation -> 16-byte stores of
-// the pixel's channels-last row) runs while the MMAs of tile i+1 are in flight.  Tiles are runs of 128
-// consecutive output pixels of the flattened [batch][out_h][out_w] index, so a CTA's stores are one
-// contiguous span.  Several CTAs share an SM and hide each other's load latency.
+// filter matrix, which sits in shared memory for the life of the CTA,
+// into a TMEM accumulator.  A thread requests the inputs of tile i+1 before it runs the epilogue of tile i
+// (TMEM -> registers -> folded batchnorm / bias, activation), so the loads' latency is covered.  The
+// finished rows are staged where the tile's im2col rows were and leave through one TMA store per warp
+// (32 rows; plain 16-byte stores when a row is wider than 128 bytes).  Tiles are runs of 128 consecutive
+// output pixels of the flattened [batch][out_h][out_w] index, so a tile's output is one contiguous span.
+// Several CTAs share an SM and fill each other's barrier and MMA waits.
 //
 // Every mbarrier wait is bounded; on expiry the CTA records a code in the status word and leaves.
 //
@@ -29,7 +31,7 @@ constexpr int ST_THREADS = 128;
 constexpr int ST_A_BYTES = 128 * 128;   // one im2col tile: 128 rows of 32 TF32 values
 
 struct StemShared {
-    uint64_t acc_full[2];
+    uint64_t acc_full;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -48,7 +50,7 @@ __device__ __forceinline__ float stem_act(float x, int runtime_act)
 // C: input channels (1..3); ACT: activation folded at compile time or ST_ACT_GENERIC; OUT_BF16: storage
 // type of the channels-last output.
 template <int C, int ACT, bool OUT_BF16>
-__global__ void __launch_bounds__(ST_THREADS, 8)
+__global__ void __launch_bounds__(ST_THREADS, 5)
 conv_stem_tc_kernel(const __grid_constant__ StemTcArgs a)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -83,12 +85,11 @@ conv_stem_tc_kernel(const __grid_constant__ StemTcArgs a)
         s_shift[i] = i < g.n ? __ldg(a.ep.shift + i) : 0.f;
     }
     if (tid == 0) {
-        mbar_init(smem_u32(&sh->acc_full[0]), 1);
-        mbar_init(smem_u32(&sh->acc_full[1]), 1);
+        mbar_init(smem_u32(&sh->acc_full), 1);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    const uint32_t tmem_cols = (uint32_t)a.tmem_cols, acc_stride = tmem_cols / 2;
+    const uint32_t tmem_cols = (uint32_t)a.tmem_cols;
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -111,19 +112,26 @@ conv_stem_tc_kernel(const __grid_constant__ StemTcArgs a)
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n_pad >> 3) << 17) | ((128u >> 4) << 24);   // TF32 x TF32 -> f32, M 128, N n_pad
     const uint64_t db = make_smem_desc(smem_u32(sB), 128);
     const uint64_t da0 = make_smem_desc(smem_u32(sA), 128);
-    const uint32_t bar0 = smem_u32(&sh->acc_full[0]);
+    const uint32_t bar0 = smem_u32(&sh->acc_full);
     const uint32_t row_off = (uint32_t)tid * 128u, sw = (uint32_t)(tid & 7);
 
+    // staged output rows for the TMA store: row m of the tile at m * row_bytes, 16-byte pieces swizzled as the map says
+    const bool tma = a.tma_store != 0;
+    const uint32_t out_row_bytes = (uint32_t)a.y_cpitch * (OUT_BF16 ? 2u : 4u);
+    const uint32_t q_xor = out_row_bytes == 128 ? (uint32_t)(tid & 7) : (out_row_bytes == 64 ? (uint32_t)((tid >> 1) & 3) : (uint32_t)((tid >> 2) & 1));
+    const CUtensorMap *ymap = &a.tmy;
+    const int lane = tid & 31;
+
     bool failed = false;
-    int prev_p = npix;   // output pixel this thread finishes in the next epilogue
+    int prev_tile = 0;
     int it = 0;
     for (int tile = blockIdx.x;; tile += gridDim.x, ++it) {
         const bool have = tile < tiles;   // uniform over the CTA
         const int buf = it & 1;
-        const int p = tile * ST_THREADS + tid;
+        // ---- this thread's 27 input values of the next tile: requested first, used after the epilogue below
+        float v[K];
         if (have) {
-            // ---- gather this thread's im2col row
-            float v[32];
+            const int p = tile * ST_THREADS + tid;
             const bool valid = p < npix;
             const int b = p / plane, rem = p - b * plane;
             const int oy = rem / g.out_w, ox = rem - oy * g.out_w;
@@ -139,39 +147,20 @@ conv_stem_tc_kernel(const __grid_constant__ StemTcArgs a)
                         const bool in = valid && (unsigned)iy < (unsigned)g.h && (unsigned)ix < (unsigned)g.w;
                         v[c * 9 + kh * 3 + kw] = in ? __ldg(xb + c * xs_c + iy * xs_h + ix * xs_w) : 0.f;
                     }
-#pragma unroll
-            for (int k = K; k < 32; ++k) v[k] = 0.f;
-            uint8_t *row = sA + buf * ST_A_BYTES + row_off;
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<uint4 *>(row + ((q ^ sw) << 4)) =
-                    make_uint4(__float_as_uint(round_tf32(v[4 * q])), __float_as_uint(round_tf32(v[4 * q + 1])),
-                               __float_as_uint(round_tf32(v[4 * q + 2])), __float_as_uint(round_tf32(v[4 * q + 3])));
-            fence_async_smem();   // rows visible to the tensor cores
         }
-        tc_fence_before();        // this thread's TMEM loads of the previous epilogue precede the barrier
-        if (__syncthreads_or(failed)) break;
-        if (have && tid == 0) {
-            tc_fence_after();
-            const uint32_t d = tmem_base + buf * acc_stride;
-            const uint64_t da = da0 + (uint64_t)(buf * (ST_A_BYTES >> 4));
-            umma<false>(d, da, db, idesc, 0u);
-            umma<false>(d, da + 2, db + 2, idesc, 1u);
-            umma<false>(d, da + 4, db + 4, idesc, 1u);
-            umma<false>(d, da + 6, db + 6, idesc, 1u);
-            umma_commit(bar0 + 8 * buf);
-        }
-        __syncwarp();
         if (it > 0) {
-            // ---- epilogue of the previous tile, overlapping the MMAs just issued
+            // ---- epilogue of the previous tile (its MMAs were issued at the end of the previous iteration)
             const int pb = (it - 1) & 1;
-            if (!mbar_wait(bar0 + 8 * pb, ((it - 1) >> 1) & 1, abort_flag, status, ST_WAIT_ACC)) {
+            if (!mbar_wait(bar0, (uint32_t)((it - 1) & 1), abort_flag, status, ST_WAIT_ACC)) {
                 failed = true;
             } else {
                 tc_fence_after();
-                const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + pb * acc_stride;
+                const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+                const int prev_p = prev_tile * ST_THREADS + tid;
                 const bool store = prev_p < npix;
                 uint8_t *dst = y + (size_t)prev_p * y_row_bytes;
+                // the finished rows go where the tile's im2col rows were: its MMAs have retired
+                uint8_t *srow = sA + pb * ST_A_BYTES + (uint32_t)tid * out_row_bytes;
 #pragma unroll 1
                 for (int c0 = 0; c0 < n_pad; c0 += 16) {
                     uint32_t r[16];
@@ -192,31 +181,72 @@ conv_stem_tc_kernel(const __grid_constant__ StemTcArgs a)
                             o[j] = c0 + j < g.n ? t : 0.f;
                         }
                     }
-                    if (store) {
-                        if (!OUT_BF16) {
+                    if (!OUT_BF16) {
 #pragma unroll
-                            for (int q = 0; q < 4; ++q)
-                                reinterpret_cast<float4 *>(dst + (size_t)c0 * 4)[q] = make_float4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
-                        } else {
-#pragma unroll
-                            for (int q = 0; q < 2; ++q) {
-                                uint4 pk;
-                                __nv_bfloat162 h0 = __floats2bfloat162_rn(o[8 * q], o[8 * q + 1]);
-                                __nv_bfloat162 h1 = __floats2bfloat162_rn(o[8 * q + 2], o[8 * q + 3]);
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(o[8 * q + 4], o[8 * q + 5]);
-                                __nv_bfloat162 h3 = __floats2bfloat162_rn(o[8 * q + 6], o[8 * q + 7]);
-                                pk.x = *reinterpret_cast<uint32_t *>(&h0); pk.y = *reinterpret_cast<uint32_t *>(&h1);
-                                pk.z = *reinterpret_cast<uint32_t *>(&h2); pk.w = *reinterpret_cast<uint32_t *>(&h3);
-                                reinterpret_cast<uint4 *>(dst + (size_t)c0 * 2)[q] = pk;
-                            }
+                        for (int q = 0; q < 4; ++q) {
+                            const uint4 pk = make_uint4(__float_as_uint(o[4 * q]), __float_as_uint(o[4 * q + 1]), __float_as_uint(o[4 * q + 2]), __float_as_uint(o[4 * q + 3]));
+                            if (tma) *reinterpret_cast<uint4 *>(srow + ((((uint32_t)(c0 >> 2) + q) ^ q_xor) << 4)) = pk;
+                            else if (store) reinterpret_cast<uint4 *>(dst + (size_t)c0 * 4)[q] = pk;
                         }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            uint4 pk;
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(o[8 * q], o[8 * q + 1]);
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(o[8 * q + 2], o[8 * q + 3]);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(o[8 * q + 4], o[8 * q + 5]);
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(o[8 * q + 6], o[8 * q + 7]);
+                            pk.x = *reinterpret_cast<uint32_t *>(&h0); pk.y = *reinterpret_cast<uint32_t *>(&h1);
+                            pk.z = *reinterpret_cast<uint32_t *>(&h2); pk.w = *reinterpret_cast<uint32_t *>(&h3);
+                            if (tma) *reinterpret_cast<uint4 *>(srow + ((((uint32_t)(c0 >> 3) + q) ^ q_xor) << 4)) = pk;
+                            else if (store) reinterpret_cast<uint4 *>(dst + (size_t)c0 * 2)[q] = pk;
+                        }
+                    }
+                }
+                if (tma) {
+                    // each warp stores its own 32 rows: no CTA-wide barrier between the rows and the store
+                    fence_async_smem();
+                    __syncwarp();
+                    const int row0 = prev_tile * ST_THREADS + warp * 32;
+                    if (lane == 0 && row0 < npix) {   // the TMA unit clips the box at the last pixel
+                        tma_store_2d(ymap, smem_u32(sA + pb * ST_A_BYTES) + (uint32_t)(warp * 32) * out_row_bytes, 0, row0);
+                        tma_store_commit();
                     }
                 }
             }
         }
+        if (have) {
+            // ---- im2col row into A[buf]; the buffer last held the staged rows of two tiles ago
+            if (tma) {
+                if (lane == 0) tma_store_wait_read1();   // all but the store just issued have read their rows
+                __syncwarp();
+            }
+            uint8_t *row = sA + buf * ST_A_BYTES + row_off;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                uint32_t w4[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) w4[e] = 4 * q + e < K ? __float_as_uint(round_tf32(v[4 * q + e < K ? 4 * q + e : 0])) : 0u;
+                *reinterpret_cast<uint4 *>(row + ((q ^ sw) << 4)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+            fence_async_smem();   // rows visible to the tensor cores
+        }
+        tc_fence_before();        // this thread's TMEM loads precede the barrier, the next MMAs follow it
+        if (__syncthreads_or(failed)) break;
         if (!have) break;
-        prev_p = p;
+        if (tid == 0) {
+            tc_fence_after();
+            const uint64_t da = da0 + (uint64_t)(buf * (ST_A_BYTES >> 4));
+            umma<false>(tmem_base, da, db, idesc, 0u);
+            umma<false>(tmem_base, da + 2, db + 2, idesc, 1u);
+            umma<false>(tmem_base, da + 4, db + 4, idesc, 1u);
+            umma<false>(tmem_base, da + 6, db + 6, idesc, 1u);
+            umma_commit(bar0);
+        }
+        __syncwarp();
+        prev_tile = tile;
     }
+    if (tma && lane == 0) tma_store_wait_all();
 
     // ---- teardown (also the abort path)
     if (*abort_flag) {   // give MMAs that may still read shared memory time to retire
@@ -246,7 +276,7 @@ static int launch_one(const StemTcArgs &a, size_t smem, int grid_limit_per_sm, c
     DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     int per_sm = (int)((228 * 1024) / (smem + 1024));   // each resident CTA also reserves 1 KB
     if (per_sm > 2048 / ST_THREADS) per_sm = 2048 / ST_THREADS;
-    if (per_sm > 65536 / (64 * ST_THREADS)) per_sm = 65536 / (64 * ST_THREADS);   // the kernel is held to 64 registers
+    if (per_sm > 5) per_sm = 5;   // the kernel's register budget (__launch_bounds__)
     if (per_sm < 1) DNB_FAIL(DNB_ECUDA, "first-layer kernel: %zu bytes of shared memory do not fit", smem);
     if (per_sm > grid_limit_per_sm) per_sm = grid_limit_per_sm;
     long long grid = (long long)sm_count() * per_sm;
@@ -275,7 +305,7 @@ int launch_conv_stem_tc(StemTcArgs a, cudaStream_t s)
     a.tiles = (int)((npix + ST_THREADS - 1) / ST_THREADS);
     a.n_pad = round_up(g.n, 16);
     a.tmem_cols = 32;
-    while (a.tmem_cols < 2 * a.n_pad) a.tmem_cols *= 2;
+    while (a.tmem_cols < a.n_pad) a.tmem_cols *= 2;
     size_t smem = 2 * ST_A_BYTES + (size_t)a.n_pad * 128 + 2 * sizeof(float) * a.n_pad + sizeof(StemShared) + 16;
     // TMEM holds 512 columns per SM: never more CTAs on an SM than can all hold their accumulators at once.
     // The grid is sized for that, and the shared-memory request is padded so that one more would not fit.
@@ -283,6 +313,16 @@ int launch_conv_stem_tc(StemTcArgs a, cudaStream_t s)
     const size_t sm_bytes = 228 * 1024, reserved = 1024;   // per SM, and per resident CTA
     if ((smem + reserved) * (lim + 1) <= sm_bytes) smem = sm_bytes / (lim + 1) - reserved + 16;
     const bool obf = a.y_dtype == DNB_BF16;
+    // rows of 32, 64 or 128 bytes leave through TMA stores from swizzled staging rows; wider ones by plain stores
+    const int row_bytes = a.y_cpitch * (obf ? 2 : 4);
+    a.tma_store = (a.y_cpitch == g.n && (row_bytes == 32 || row_bytes == 64 || row_bytes == 128)) ? 1 : 0;
+    if (const char *e = getenv("DNB_STEM_TMA")) a.tma_store = a.tma_store && atoi(e) != 0;
+    if (a.tma_store) {
+        const uint64_t dims[2] = {(uint64_t)a.y_cpitch, (uint64_t)npix};
+        const uint64_t strides[1] = {(uint64_t)row_bytes};
+        const uint32_t box[2] = {(uint32_t)a.y_cpitch, 32u};
+        DNB_TRY(encode_tensor_map(&a.tmy, obf, 2, a.y, dims, strides, box, row_bytes));
+    }
     switch (g.c) {
     case 1: return obf ? launch_act<1, true>(a, smem, lim, s) : launch_act<1, false>(a, smem, lim, s);
     case 2: return obf ? launch_act<2, true>(a, smem, lim, s) : launch_act<2, false>(a, smem, lim, s);
