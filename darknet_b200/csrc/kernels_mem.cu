@@ -385,28 +385,58 @@ __global__ void nchw_to_nhwc_kernel(const float *__restrict__ x, T *__restrict__
     }
 }
 
+// Channels-last to Darknet's layout: a tile of 128 pixels x 32 channels per block.  Loads are 16-byte
+// (8-byte for bf16) pieces of a pixel's channels, four pixels per warp instruction; stores are 128-byte
+// runs of one channel plane.  The 129-float row pitch keeps both shared-memory phases conflict-free.
 template <typename T>
-__global__ void nhwc_to_nchw_kernel(const T *__restrict__ x, float *__restrict__ y, int C, int HW, int Cp, int yolo_entries)
+__global__ void __launch_bounds__(256)
+nhwc_to_nchw_kernel(const T *__restrict__ x, float *__restrict__ y, int C, int HW, int Cp, int yolo_entries)
 {
-    __shared__ float tile[32][33];
+    __shared__ float tile[32][129];
     const int b = blockIdx.z;
-    const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+    const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 128;
     const T *src = x + (size_t)b * HW * Cp;
     float *dst = y + (size_t)b * C * HW;
-    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
-        int p = p0 + j, c = c0 + threadIdx.x;
-        tile[j][threadIdx.x] = (p < HW && c < C) ? to_float<T>(src[(size_t)p * Cp + c]) : 0.f;
+    const int t = threadIdx.x;
+    {
+        const int pl = t >> 3, q = t & 7, c = c0 + 4 * q;
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+            const int pp = pl + 32 * pass, p = p0 + pp;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (p < HW && c < Cp) {   // the pitch is a multiple of 8: a 4-channel piece is inside it or outside
+                if (sizeof(T) == 4) {
+                    const float4 f = __ldg(reinterpret_cast<const float4 *>(src + (size_t)p * Cp + c));
+                    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+                } else {
+                    const uint2 u = __ldg(reinterpret_cast<const uint2 *>(src + (size_t)p * Cp + c));
+                    v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xffff0000u);
+                    v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xffff0000u);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) tile[4 * q + e][pp] = v[e];
+        }
     }
     __syncthreads();
-    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
-        int c = c0 + j, p = p0 + threadIdx.x;
-        if (c < C && p < HW) {
-            float v = tile[threadIdx.x][j];
-            if (yolo_entries > 0) {
-                int e = c % yolo_entries;
-                if (e < 2 || e >= 4) v = 1.f / (1.f + expf(-v));
+    const int lane = t & 31, w = t >> 5;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int j = w + 8 * k, c = c0 + j;
+        if (c >= C) continue;
+        bool logistic = false;
+        if (yolo_entries > 0) {
+            const int e = c % yolo_entries;
+            logistic = e < 2 || e >= 4;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int pp = lane + 32 * e, p = p0 + pp;
+            if (p < HW) {
+                float v = tile[j][pp];
+                if (logistic) v = 1.f / (1.f + expf(-v));
+                dst[(size_t)c * HW + p] = v;
             }
-            dst[(size_t)c * HW + p] = v;
         }
     }
 }
@@ -444,9 +474,9 @@ int launch_convert(const dnb_tensor *x, const dnb_tensor *y, int rnd, int yolo_a
         else nchw_to_nhwc_kernel<__nv_bfloat16><<<grid, block, 0, s>>>((const float *)x->data, (__nv_bfloat16 *)y->data, x->c, HW, y->cpitch, 0);
     } else if (x->layout == DNB_NHWC && y->layout == DNB_NCHW) {
         if (y->dtype != DNB_F32) DNB_FAIL(DNB_EINVAL, "convert: NCHW tensors must be f32");
-        dim3 grid((HW + 31) / 32, (x->c + 31) / 32, x->n);
-        if (x->dtype == DNB_F32) nhwc_to_nchw_kernel<float><<<grid, block, 0, s>>>((const float *)x->data, (float *)y->data, x->c, HW, x->cpitch, entries);
-        else nhwc_to_nchw_kernel<__nv_bfloat16><<<grid, block, 0, s>>>((const __nv_bfloat16 *)x->data, (float *)y->data, x->c, HW, x->cpitch, entries);
+        dim3 grid((HW + 127) / 128, (x->c + 31) / 32, x->n);
+        if (x->dtype == DNB_F32) nhwc_to_nchw_kernel<float><<<grid, 256, 0, s>>>((const float *)x->data, (float *)y->data, x->c, HW, x->cpitch, entries);
+        else nhwc_to_nchw_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16 *)x->data, (float *)y->data, x->c, HW, x->cpitch, entries);
     } else if (x->layout == DNB_NCHW) {
         if (x->dtype != DNB_F32 || y->dtype != DNB_F32) DNB_FAIL(DNB_EINVAL, "convert: NCHW tensors must be f32");
         size_t total = tensor_elems(x);
