@@ -42,9 +42,9 @@ UNIT = "images/s"
 # (bytes per image, bytes per launch set independent of the batch); see profiles/conv_tc_dram_traffic_*.md and
 # profiles/conv_tc_conv*_b64_tf32.md for the captures.  Scaled by the images one step processes.
 NCU_DRAM_TRAFFIC = {
-    ("yolov3", "tf32", 608): (547_463_136.0, 247_579_648.0),
-    ("conv3x3", "tf32", 224): (489.0e6 / 64, 0.0),
-    ("conv1x1", "tf32", 224): (491.0e6 / 64, 0.0),
+    ("yolov3", "tf32", 608): (544_815_392.0, 247_579_648.0),
+    ("conv3x3", "tf32", 224): (485.0e6 / 64, 0.0),
+    ("conv1x1", "tf32", 224): (490.0e6 / 64, 0.0),
 }
 
 
@@ -93,14 +93,28 @@ def load_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons during the timed region."""
+    """SM clock, power and throttle reasons sampled during the timed region: every 20 ms through NVML
+    (read-only queries), or every 200 ms through nvidia-smi when NVML cannot be loaded."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, gpu_index: int):
         self.proc = None
-        self.lines: list[str] = []
-        self.gpu = gpu_index
+        self.rows: list[tuple] = []     # (sm_mhz, max_mhz, watts, {reasons})
+        self.stop_flag = False
+        self.nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.t = threading.Thread(target=self._poll, daemon=True)
+            self.t.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
                                           "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -109,33 +123,57 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        n = self.nvml
+        bits = {"hw_slowdown": getattr(n, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(n, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(n, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(n, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+        while not self.stop_flag:
+            try:
+                mhz = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                watts = n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                mask = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.rows.append((mhz, self.max_mhz, watts, {k for k, b in bits.items() if mask & b}))
+            except Exception:
+                pass
+            time.sleep(0.02)
+
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            r = line.strip().split(", ")
+            if len(r) >= 9:
+                try:
+                    self.rows.append((float(r[1]), float(r[2]), float(r[3]),
+                                      {k for k, v in zip(self.NAMES, r[5:9]) if v.strip().lower().startswith("active")}))
+                except ValueError:
+                    pass
 
     def mark(self):
-        return len(self.lines)
+        return len(self.rows)
 
     def stop(self, start: int = 0):
-        if not self.proc:
+        self.stop_flag = True
+        if self.nvml is None and not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=3)
-        except Exception:
-            self.proc.kill()
-        rows = [r.split(", ") for r in self.lines[start:] if r.count(",") >= 8] or [r.split(", ") for r in self.lines if r.count(",") >= 8]
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=3)
+            except Exception:
+                self.proc.kill()
+        else:
+            self.t.join(timeout=1)
+        rows = self.rows[start:] or self.rows
         if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        sm = sorted(float(r[1]) for r in rows)
+        sm = sorted(r[0] for r in rows)
         reasons = set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in rows:
-            for name, v in zip(names, r[5:9]):
-                if v.strip().lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons),
-                "power_w_max": max(float(r[3]) for r in rows), "samples": len(rows)}
+            reasons |= r[3]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": rows[0][1], "reasons": sorted(reasons),
+                "power_w_max": max(r[2] for r in rows), "samples": len(rows),
+                "source": "NVML, 20 ms" if self.nvml is not None else "nvidia-smi, 200 ms"}
 
 
 def write_net_files(d: str, cfg: str, seed: int = 0):

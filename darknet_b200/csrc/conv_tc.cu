@@ -13,20 +13,29 @@
 //   zero-filled by the TMA unit, which is the convolution's padding.  A strided
 //   convolution reads from stride*stride lattices of the input (one tensor map
 //   per row/column parity), so every load is still a dense box.
-// * Accumulators live in TMEM (fp32); two accumulator buffers of 256 columns let
-//   the epilogue of tile i overlap the MMAs of tile i+1.
-// * Warp roles in a 192-thread CTA: warp 0 issues TMA, warp 1 issues tcgen05.mma
-//   and owns the TMEM allocation, warps 2-5 drain TMEM and apply the fused
-//   epilogue (folded batchnorm or bias, activation, stores in NHWC and/or NCHW).
-// * Persistent: one CTA per SM walks tiles blockIdx.x, +gridDim.x, ...; tiles
-//   that share a pixel box are adjacent so the box is fetched from HBM once and
-//   re-read from L2 by the neighbouring CTAs.  No cluster, no multicast.
+// * Accumulators live in TMEM (fp32); two accumulator buffers of bn columns let the
+//   epilogue of tile i overlap the MMAs of tile i+1.
+// * Warp roles in a 192-thread CTA: warp 0 issues TMA (one thread), warp 1 issues
+//   tcgen05.mma (one thread) and owns the TMEM allocation, warps 2-5 drain TMEM
+//   and apply the fused epilogue: folded batchnorm or bias, activation, optionally
+//   the residual add of a following shortcut layer (its tile arrives by TMA in the
+//   staging buffer the finished rows then overwrite), TF32 rounding, TMA store of
+//   the channels-last rows and/or plain stores of Darknet's NCHW layout.
+// * Persistent: one CTA per SM (two when the filter tile is at most 128 wide) walks
+//   tiles blockIdx.x, +gridDim.x, ...; tiles that share a pixel box are adjacent so
+//   the box is fetched from HBM once and re-read from L2 by the neighbouring CTAs.
+//   No cluster, no multicast.
+// * The depth of the operand ring decides how much load latency is hidden (2 / 3 / 4
+//   slots: 0.45 / 0.35 / 0.32 ms on a 76x76 256-filter layer), so shared memory is
+//   budgeted to the byte: no alignment slack, only the current filter tile's
+//   scale/shift vectors, staging rows as narrow as four ring slots require.
 // * Every mbarrier wait is bounded: when it expires the CTA records a code in
 //   the status word, raises a shared abort flag that all roles poll, drains,
 //   frees its TMEM and returns.  The kernel never traps.
 //
 // Replaces forward_convolutional_layer_gpu (src/convolutional_kernels.cu:73-135
-// of the reference) for groups == 1 and c >= 8.
+// of the reference) for groups == 1 and c >= 8, and with it the shortcut layer that follows
+// (forward_shortcut_layer_gpu, src/shortcut_layer.c:75-80; src/blas_kernels.cu:711-745) when the caller asks for the fusion.
 #include <cuda.h>
 
 #include "common.h"
