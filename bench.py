@@ -72,7 +72,8 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-gpu"])
+    ap.add_argument("--ref-gpu-batch", type=int, default=8, help="images per network_predict call of the reference's own CUDA build (0: skip that row)")
     ap.add_argument("--mode", default="tf32", choices=["tf32", "bf16"])
     ap.add_argument("--batch", type=int, default=64, help="images per GPU per step")
     ap.add_argument("--size", type=int, default=0, help="input width = height (default: 608 yolov3, 416 tiny, 224 classifiers)")
@@ -253,6 +254,40 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_gpu(args):
+    """The unmodified reference's own CUDA path (im2col + cuBLAS + separate bias / batchnorm / activation
+    kernels, its .cu files recompiled for sm_100a; oracle/_ref/libdarknet_ref_gpu.so) through its
+    network_predict, host buffers in and out, on GPU 0.  A same-box row beside the CPU baseline; the
+    reference allocates training buffers too, so it runs a smaller batch (its GEMMs are per image anyway)."""
+    from darknet_b200 import synth
+    from oracle import network as orc
+    if not orc.ReferenceGpu.available():
+        print(json.dumps({"impl": "reference-gpu", "unavailable": "oracle/_ref/libdarknet_ref_gpu.so was not built (make -C oracle refgpu)"}), flush=True)
+        return
+    batch = max(1, args.ref_gpu_batch)
+    cfg, metric, desc = workload_cfg(args.workload, batch, args.size)
+    d = tempfile.mkdtemp(prefix="dnb_refgpu_")
+    write_net_files(d, cfg)
+    ref = orc.ReferenceGpu()
+    net = ref.load(os.path.join(d, "net.cfg"), os.path.join(d, "net.weights"))
+    x = synth.seeded_input(cfg, 0, "normal" if args.workload.startswith("conv") else "uniform")
+    ref.time_predict(net, x, max(args.warmup, 1))
+    sec = ref.time_predict(net, x, args.steps) / args.steps
+    # the same `network` after b200_attach: Darknet's loop, buffers and layout, this library's kernels per layer
+    import darknet_b200 as dn
+    attached = ref.attach(net, dn.MODE_TF32)
+    att = None
+    if attached > 0:
+        ref.time_predict(net, x, max(args.warmup, 1))
+        asec = ref.time_predict(net, x, args.steps) / args.steps
+        att = {"value": batch / asec, "unit": UNIT, "ms_per_step": asec * 1000.0, "layers_repointed": attached,
+               "note": "forward_gpu pointers of the unmodified network re-pointed by b200_attach (TF32 plans, NCHW fp32 tensors at every layer boundary)"}
+    print(json.dumps({"impl": "reference-gpu", "metric": metric, "value": batch / sec, "unit": UNIT, "ms_per_step": sec * 1000.0, "attached": att,
+                      "steps": args.steps, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"{desc}, batch {batch}, the reference's CUDA build recompiled for sm_100a "
+                                             "(im2col + cuBLAS sgemm per image), network_predict with host buffers"}}), flush=True)
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -400,6 +435,18 @@ def run_b200(args):
         cpu = {"value": args.cpu_sample / sec, "unit": UNIT, "cores": ref.cores, "kind": ref.kind,
                "sample": f"{args.cpu_sample} image(s) of {desc}, second of two network_predict calls on the host cores ({sec:.1f} s)"}
 
+    # the reference's own GPU path on the same box, in a child process (it exits on any error and holds tens of GB)
+    ref_gpu = None
+    if world == 1 and args.ref_gpu_batch > 0 and not args.workload.startswith("conv"):
+        try:
+            p = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-gpu", "--workload", args.workload,
+                                "--size", str(args.size), "--ref-gpu-batch", str(args.ref_gpu_batch), "--steps", "3", "--warmup", "1"],
+                               capture_output=True, text=True, timeout=600)
+            rows = [ln for ln in p.stdout.splitlines() if ln.startswith("{")]
+            ref_gpu = json.loads(rows[-1]) if rows else {"unavailable": f"child exited {p.returncode}: {p.stderr[-200:]}"}
+        except Exception as e:   # noqa: BLE001
+            ref_gpu = {"unavailable": repr(e)[:200]}
+
     line = {"metric": metric, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": args.mode, "data": "synthetic",
@@ -411,7 +458,7 @@ def run_b200(args):
                     "ms_per_step": e2e_ms_step, "timer": "host wall clock around K submit/collect steps, two in flight",
                     "blocking_predict": {"value": total_images / (sync_ms_step / 1000.0), "ms_per_step": sync_ms_step}},
             "gpu_launches": net.launches * args.steps,
-            "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
+            "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "reference_gpu": ref_gpu}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -423,6 +470,8 @@ def main():
         args.size = {"yolov3": 608, "yolov3-tiny": 416}.get(args.workload, 224)
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
     else:
         run_b200(args)
 

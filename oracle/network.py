@@ -265,3 +265,28 @@ class Reference:
             shape = (batch, oc, oh, ow) if oc * oh * ow == outputs and outputs > 0 else (batch, outputs)
             outs.append(buf.reshape(shape))
         return outs
+
+
+class ReferenceGpu(Reference):
+    """ctypes view of oracle/_ref/libdarknet_ref_gpu.so: the unmodified reference's own CUDA build
+    (-DGPU: im2col + cuBLAS + separate bias / batchnorm / activation kernels), recompiled for sm_100a,
+    linked with the attach shim (darknet_b200/shim/b200_attach.c).  Needs a GPU at load time.  The
+    reference exits the process on any error, so callers that must survive one run it in a child."""
+
+    path = os.path.join(HERE, "_ref", "libdarknet_ref_gpu.so")
+
+    def __init__(self):
+        super().__init__()
+        self.L.ref_attach_b200.argtypes = [C.c_void_p, C.c_int]
+        self.L.ref_detach_b200.argtypes = [C.c_void_p]
+
+    def attach(self, net, mode: int) -> int:
+        """b200_attach: re-point forward_gpu of the covered layers at libdarknet_b200."""
+        return self.L.ref_attach_b200(net, mode)
+
+    def detach(self, net) -> None:
+        self.L.ref_detach_b200(net)
+
+    def time_predict(self, net, x: np.ndarray, reps: int) -> float:
+        x = np.ascontiguousarray(x, np.float32)
+        return float(self.L.ref_time_predict(net, _p(x), reps))

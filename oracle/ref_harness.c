@@ -1,5 +1,6 @@
 /*
- * Thin C harness around the UNMODIFIED reference (pjreddie/darknet, CPU build).
+ * Thin C harness around the UNMODIFIED reference (pjreddie/darknet): the CPU build, and with -DGPU
+ * the reference's own CUDA build (im2col + cuBLAS, recompiled for sm_100a) plus the attach shim.
  *
  * TEST INFRASTRUCTURE ONLY.  Compiled against the reference's own public
  * header (include/darknet.h) and linked with objects built from the
@@ -40,8 +41,26 @@ void ref_layer_info(void *h, int i, int *info)
     info[4] = l->outputs;   info[5] = l->batch; info[6] = l->n;     info[7] = l->size;
 }
 
-/* Pointer to layer i's host output buffer, outputs*batch floats. */
-float *ref_layer_output(void *h, int i) { return ((network *)h)->layers[i].output; }
+/* Pointer to layer i's host output buffer, outputs*batch floats.  In the GPU build the device copy
+ * is pulled first (cuda_pull_array, src/cuda.c:160-165). */
+float *ref_layer_output(void *h, int i)
+{
+    layer *l = &((network *)h)->layers[i];
+#ifdef GPU
+    if (l->output_gpu && l->output) cuda_pull_array(l->output_gpu, l->output, (size_t)l->outputs * l->batch);
+#endif
+    return l->output;
+}
+
+#ifdef GPU
+#include "b200_attach.h"
+/* The drop-in under test: re-point the network's forward_gpu pointers at libdarknet_b200. */
+int ref_attach_b200(void *h, int mode) { return b200_attach((network *)h, mode); }
+void ref_detach_b200(void *h) { b200_detach((network *)h); }
+int ref_is_gpu_build(void) { return 1; }
+#else
+int ref_is_gpu_build(void) { return 0; }
+#endif
 
 /* network_predict (src/network.c:497-508): returns the last layer's output. */
 float *ref_network_predict(void *h, float *input) { return network_predict((network *)h, input); }
