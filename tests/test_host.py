@@ -39,6 +39,27 @@ def test_library_exports_every_declared_symbol():
     assert L.dnb_cpitch(255) == 256 and L.dnb_cpitch(3) == 8
 
 
+def test_attach_shim_exports_its_header():
+    """include/b200_attach.h is implemented by darknet_b200/shim/b200_attach.c, which is compiled inside a
+    Darknet GPU tree; where the reference's CUDA build was made here, its library carries both symbols."""
+    import ctypes
+    text = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "b200_attach.h")).read(), flags=re.S)
+    names = set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text))
+    assert names == {"b200_attach", "b200_detach"}
+    src = open(os.path.join(ROOT, "darknet_b200", "shim", "b200_attach.c")).read()
+    for n in names:
+        assert re.search(r"^(int|void) %s\(" % n, src, flags=re.M), n
+    lib = os.path.join(ROOT, "oracle", "_ref", "libdarknet_ref_gpu.so")
+    if not os.path.exists(lib):
+        pytest.skip("the reference's CUDA build was not made here (make -C oracle refgpu)")
+    try:
+        L = ctypes.CDLL(lib)
+    except OSError as e:
+        pytest.skip(f"cannot load the reference's CUDA build here: {e}")
+    for n in names:
+        assert hasattr(L, n)
+
+
 def test_plan_validation_needs_no_device():
     L = dn.lib()
     h = C.c_void_p()
