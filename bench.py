@@ -303,7 +303,9 @@ def run_b200(args):
     dn.check(dn.lib().dnb_set_device(local))
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    from darknet_b200.shard import max_over_ranks, shard_batch
+    from darknet_b200.shard import bind_near_gpu, max_over_ranks, shard_batch
+    # several ranks share the host: each keeps its threads and its pinned buffers in the memory next to its GPU
+    near_cpus = bind_near_gpu(local) if world > 1 and not os.environ.get("DNB_NO_NUMA_BIND") else []
     # weak: every rank forwards --batch images; strong: --batch images are cut into contiguous slices
     per_gpu = args.batch if args.scaling == "weak" else max(1, shard_batch(args.batch, world, rank)[1])
     mode = dn.MODE_TF32 if args.mode == "tf32" else dn.MODE_BF16
@@ -452,6 +454,7 @@ def run_b200(args):
             "dtype": args.mode, "data": "synthetic",
             "config": {"workload": f"{desc}, batch {per_gpu} per GPU ({total_images} images per step over {world} GPU)",
                        "global_batch": total_images, "parallelism": f"dp{world} (image sharding, replicated weights, no collective)",
+                       "host_binding": f"rank 0 bound to {len(near_cpus)} CPUs next to its GPU" if near_cpus else "none",
                        "l2": f"inputs larger than L2: every step streams {act_gb:.1f} GB of layer outputs through HBM, no flush needed",
                        "tflops_algorithmic": float(flops.sum()) * world / (ms_step / 1000.0) / 1e12},
             "e2e": {"value": total_images / (e2e_ms_step / 1000.0), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -59,6 +59,7 @@ struct alignas(64) TcArgs {
     int total_tiles;      // n_tiles * tiles_w * tiles_h * tiles_b
     int stages;           // depth of the shared-memory ring
     int tmem_cols;        // TMEM columns the CTA allocates: a power of two >= 2*bn (two accumulators)
+    int debug;            // timing experiments only (DNB_TC_DEBUG): 1 no residual loads, 2 no output stores, 4 no wait before a residual request
     int stage_bufs;       // staging buffers of the epilogue: 2, or 4 with a fused residual (tiles land in them first)
     int ctas_per_sm;      // 2 for narrow tiles (TMEM and shared memory are sized so that two CTAs share an SM), else 1
     int a_bytes, b_bytes; // shared-memory bytes of one stage's activation / weight tile (1024-multiples)

@@ -251,6 +251,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     // twice the warps hide the per-tile hand-offs that dominate layers with few K iterations.
     a.ctas_per_sm = 1;
     a.stage_bufs = residual ? 4 : 2;
+    a.debug = getenv("DNB_TC_DEBUG") ? atoi(getenv("DNB_TC_DEBUG")) : 0;
     int stages = 0;
     const bool allow2 = getenv("DNB_TC_CTAS") ? atoi(getenv("DNB_TC_CTAS")) >= 2 : true;
     if (allow2 && a.tmem_cols <= 256) {
@@ -265,7 +266,8 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
         // The exception is a fused residual behind a short K loop, where the epilogue (one round of barrier,
         // residual wait and store per staged chunk) would outlast the tile's MMAs: fewer, wider chunks then.
         const int k_iters = g.size * g.size * a.c_blocks;
-        const int want = (residual && k_iters < 64 && min_stages > 3) ? 3 : min_stages;
+        const bool short_k_rule = getenv("DNB_TC_SHORTK") ? atoi(getenv("DNB_TC_SHORTK")) != 0 : true;
+        const int want = (residual && k_iters < 64 && min_stages > 3 && short_k_rule) ? 3 : min_stages;
         for (;; srb /= 2) {
             stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.bn, a.stage_bufs)) / (a.a_bytes + a.b_bytes));
             if (stages >= want || srb == min_srb) break;

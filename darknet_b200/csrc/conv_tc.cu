@@ -61,7 +61,7 @@ struct TcShared {
 };
 
 enum { WAIT_EMPTY = 101, WAIT_FULL = 102, WAIT_ACC_EMPTY = 103, WAIT_ACC_FULL = 104, WAIT_RESIDUAL = 105, BAD_SMEM_BASE = 106 };
-enum { ACT_GENERIC = -1 };
+enum { ACT_GENERIC = -1, ACT2_NONE = -2 };   // ACT2_NONE: no fused residual
 
 
 template <int ACT>
@@ -73,10 +73,13 @@ __device__ __forceinline__ float act_apply(float x, int runtime_act)
 }
 
 // ACT: activation folded at compile time (DNB_LINEAR, DNB_LEAKY) or ACT_GENERIC (runtime switch).
+// ACT2: ACT2_NONE, or the activation of the fused shortcut layer (same three choices).  The epilogue's chunk
+// body is unrolled over CPC columns and shares the instruction cache with the TMA and MMA loops: every
+// per-element run-time choice that can be a template parameter is one, or the warps stall on instruction fetch.
 // CPC: output columns per staged chunk (16, 32 or 64); OUT_BF16: storage type of the operands and of the
 // NHWC output (bf16 for BF16 plans, f32 with TF32 products otherwise).
 // One staged row is CPC * sizeof(output element) bytes = the swizzle span of the store map.
-template <int ACT, int CPC, bool OUT_BF16>
+template <int ACT, int CPC, bool OUT_BF16, int ACT2>
 __global__ void __launch_bounds__(TC_THREADS)
 conv_tc_kernel(const __grid_constant__ TcArgs a)
 {
@@ -226,10 +229,10 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         void *const y_nhwc = a.y_nhwc;
         float *const y_nchw = a.y_nchw;
         const int runtime_act = a.ep.activation, do_round = a.ep.round_tf32;
-        const bool residual = a.ep.residual != nullptr;
+        constexpr bool residual = ACT2 != ACT2_NONE;
         const CUtensorMap *rmap = &a.tmr;
         const uint32_t buf_mask = residual ? 3u : 1u;   // staging buffers in rotation
-        constexpr int res_ahead = 2;
+        constexpr int res_ahead = 3;   // residual tiles requested ahead of the chunk being finished (of four buffers)
         const int act2 = a.ep.activation2;
         const float res_alpha = a.ep.alpha, res_beta = a.ep.beta;
         const CUtensorMap *ymap = &a.tmy;
@@ -237,11 +240,29 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         const bool store_thread = threadIdx.x == 64;
         constexpr bool out_bf16 = OUT_BF16;
         constexpr int srb = CPC * (OUT_BF16 ? 2 : 4);            // bytes of one staged row = swizzle span
-        constexpr int cols_per_chunk = CPC;
         constexpr int q_mask = srb / 16 - 1;
         const int q_xor = (m >> (srb == 128 ? 0 : (srb == 64 ? 1 : 2))) & q_mask;   // 16-byte chunk swizzle of row m
         uint32_t chunk_count = 0;
         int it = 0, loaded_nt = -1;
+        // Residual tiles are requested as one stream of chunks that runs res_ahead chunks in front of the epilogue
+        // and does not stop at tile boundaries: what bounds a layer with a fused residual is how many bytes of it
+        // are in flight, so the requests must not drain while the epilogue waits for the next accumulator.
+        uint32_t pf_count = 0;                 // chunks requested so far (buffer = count & 3)
+        int pf_tile = blockIdx.x, pf_c0 = 0;   // the next chunk to request
+        const int dbg = a.debug;
+        auto request_residual = [&]() {
+            if (pf_tile >= total_tiles || (dbg & 1)) return;
+            const int nt = pf_tile % n_tiles, pt = pf_tile / n_tiles;
+            const int ow0 = (pt % tiles_w) * wt, oh0 = ((pt / tiles_w) % tiles_h) * ht, b0 = (pt / ptiles_wh) * bt;
+            const uint32_t rb = pf_count & 3u, bar = smem_u32(&sh->res_full[rb]);
+            mbar_expect_tx(bar, 128u * srb);
+            tma_load_4d(smem_u32(stage_out + (size_t)rb * 128 * srb), rmap, bar, nt * bn + pf_c0, ow0, oh0, b0);
+            ++pf_count;
+            pf_c0 += CPC;
+            if (pf_c0 >= bn) { pf_c0 = 0; pf_tile += grid_stride; }
+        };
+        if (residual && store_thread)
+            for (int d = 0; d < res_ahead; ++d) request_residual();
         const float *const ep_scale = a.ep.scale, *const ep_shift = a.ep.shift;
         const int n_pad = a.n_pad;
         for (int tile = blockIdx.x; tile < total_tiles; tile += grid_stride, ++it) {
@@ -262,17 +283,6 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 }
                 loaded_nt = nt;
             }
-            if (residual && store_thread) {
-                // residual tiles of the first two chunks: requested before the accumulator is even ready.  Their
-                // buffers were last read by the stores of four and three chunks ago; two newer stores may be pending.
-                tma_store_wait_read2();
-                for (int d = 0; d < res_ahead && d * CPC < bn; ++d) {
-                    const uint32_t rb = (chunk_count + d) & 3u, bar = smem_u32(&sh->res_full[rb]);
-                    mbar_expect_tx(bar, 128u * srb);
-                    tma_load_4d(smem_u32(stage_out + (size_t)rb * 128 * srb), rmap, bar, nt * bn + d * CPC, ow0, oh0, b0);
-                }
-            }
-
             mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, abort_flag, status, WAIT_ACC_FULL, 32);
             epilogue_bar();                 // all four warps agree on the abort flag from here
             if (*abort_flag) break;
@@ -300,7 +310,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 if (residual) {
                     // this chunk's residual tile (TMA zero-fills pixels and channels outside the tensor)
                     const uint32_t rb = chunk_count & 3u;
-                    mbar_wait(smem_u32(&sh->res_full[rb]), (chunk_count >> 2) & 1, abort_flag, status, WAIT_RESIDUAL);
+                    if (!(dbg & 1)) mbar_wait(smem_u32(&sh->res_full[rb]), (chunk_count >> 2) & 1, abort_flag, status, WAIT_RESIDUAL);
                     const uint8_t *rrow = stage_out + (size_t)rb * 128 * srb + (size_t)m * srb;
 #pragma unroll
                     for (int q = 0; q < RES_V; ++q) res[q] = *reinterpret_cast<const uint4 *>(rrow + ((q ^ q_xor) << 4));
@@ -331,9 +341,9 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                                     rv = __uint_as_float((j & 1) ? (wd & 0xffff0000u) : (wd << 16));
                                 }
                             }
-                            t = activate_fast(res_alpha * t + res_beta * rv, act2);
+                            t = act_apply<ACT2>(res_alpha * t + res_beta * rv, act2);
                         }
-                        if (do_round) t = round_tf32(t);
+                        if (!OUT_BF16 && do_round) t = round_tf32(t);
                         r[j] = __float_as_uint(j < nvalid ? t : 0.f);
                     }
                 }
@@ -366,14 +376,13 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 epilogue_bar();
                 if (store_thread) {
                     // the TMA unit clips the box at the tensor's extents: ragged tiles need no predicates
-                    if (y_nhwc) tma_store_4d(ymap, smem_u32(stage_out + (size_t)buf * 128 * srb), nl0, ow0, oh0, b0);
+                    if (y_nhwc && !(dbg & 2)) tma_store_4d(ymap, smem_u32(stage_out + (size_t)buf * 128 * srb), nl0, ow0, oh0, b0);
                     tma_store_commit();
-                    if (residual && c0 + res_ahead * CPC < bn) {
-                        // the tile two chunks on goes into the buffer of two chunks ago, once that chunk's store has read it
-                        tma_store_wait_read2();
-                        const uint32_t nb = (chunk_count + res_ahead) & 3u, bar = smem_u32(&sh->res_full[nb]);
-                        mbar_expect_tx(bar, 128u * srb);
-                        tma_load_4d(smem_u32(stage_out + (size_t)nb * 128 * srb), rmap, bar, nt * bn + c0 + res_ahead * CPC, ow0, oh0, b0);
+                    if (residual) {
+                        // the tile three chunks on goes into the buffer of the previous chunk, once that chunk's
+                        // store has read it (only the store just issued may still be pending)
+                        if (!(dbg & 4)) tma_store_wait_read1();
+                        request_residual();
                     }
                 }
                 if (y_nchw && pix_ok) {
@@ -440,24 +449,33 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
     const int max_smem = conv_tc_max_smem();
     // one instantiation per (activation, columns per staged chunk, output type); the opt-in for large
     // dynamic shared memory is per kernel symbol and cheap, so it is set on every launch
-#define DNB_TC_LAUNCH(ACT, CPC, OBF)                                                                                       \
-    do {                                                                                                                   \
-        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<ACT, CPC, OBF>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)); \
-        conv_tc_kernel<ACT, CPC, OBF><<<grid, TC_THREADS, smem, s>>>(a);                                                  \
+#define DNB_TC_LAUNCH(ACT, CPC, OBF, ACT2)                                                                                       \
+    do {                                                                                                                         \
+        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<ACT, CPC, OBF, ACT2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)); \
+        conv_tc_kernel<ACT, CPC, OBF, ACT2><<<grid, TC_THREADS, smem, s>>>(a);                                                  \
     } while (0)
-#define DNB_TC_LAUNCH_ACT(ACT)                                        \
-    do {                                                              \
-        if (!obf && cpc == 32) DNB_TC_LAUNCH(ACT, 32, false);         \
-        else if (!obf && cpc == 16) DNB_TC_LAUNCH(ACT, 16, false);    \
-        else if (obf && cpc == 64) DNB_TC_LAUNCH(ACT, 64, true);      \
-        else if (obf && cpc == 32) DNB_TC_LAUNCH(ACT, 32, true);      \
-        else if (obf && cpc == 16) DNB_TC_LAUNCH(ACT, 16, true);      \
+#define DNB_TC_LAUNCH_ACT(ACT, ACT2)                                        \
+    do {                                                                    \
+        if (!obf && cpc == 32) DNB_TC_LAUNCH(ACT, 32, false, ACT2);         \
+        else if (!obf && cpc == 16) DNB_TC_LAUNCH(ACT, 16, false, ACT2);    \
+        else if (obf && cpc == 64) DNB_TC_LAUNCH(ACT, 64, true, ACT2);      \
+        else if (obf && cpc == 32) DNB_TC_LAUNCH(ACT, 32, true, ACT2);      \
+        else if (obf && cpc == 16) DNB_TC_LAUNCH(ACT, 16, true, ACT2);      \
         else DNB_FAIL(DNB_EINVAL, "conv_tc: no kernel for %d columns per chunk", cpc); \
     } while (0)
-    switch (a.ep.activation) {
-    case DNB_LINEAR: DNB_TC_LAUNCH_ACT(DNB_LINEAR); break;
-    case DNB_LEAKY: DNB_TC_LAUNCH_ACT(DNB_LEAKY); break;
-    default: DNB_TC_LAUNCH_ACT(ACT_GENERIC); break;
+    if (!a.ep.residual) {
+        switch (a.ep.activation) {
+        case DNB_LINEAR: DNB_TC_LAUNCH_ACT(DNB_LINEAR, ACT2_NONE); break;
+        case DNB_LEAKY: DNB_TC_LAUNCH_ACT(DNB_LEAKY, ACT2_NONE); break;
+        default: DNB_TC_LAUNCH_ACT(ACT_GENERIC, ACT2_NONE); break;
+        }
+    } else {
+        // fused shortcut: the two pairs the reference's cfgs use (yolov3: leaky conv, linear shortcut; resnet:
+        // linear conv, leaky shortcut) are compile-time, every other pair takes the run-time switches
+        if (a.stage_bufs != 4) DNB_FAIL(DNB_EINVAL, "conv_tc: a fused residual needs four staging buffers");
+        if (a.ep.activation == DNB_LEAKY && a.ep.activation2 == DNB_LINEAR) DNB_TC_LAUNCH_ACT(DNB_LEAKY, DNB_LINEAR);
+        else if (a.ep.activation == DNB_LINEAR && a.ep.activation2 == DNB_LEAKY) DNB_TC_LAUNCH_ACT(DNB_LINEAR, DNB_LEAKY);
+        else DNB_TC_LAUNCH_ACT(ACT_GENERIC, ACT_GENERIC);
     }
 #undef DNB_TC_LAUNCH_ACT
 #undef DNB_TC_LAUNCH

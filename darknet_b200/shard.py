@@ -50,3 +50,40 @@ def gather_outputs(local: np.ndarray, total: int):
     out = np.concatenate([p for p in parts if p is not None and len(p)], axis=0)
     assert out.shape[0] == total
     return out
+
+
+def cpus_near_gpu(gpu_index: int, affinity_words=None, ncpu: int | None = None) -> list[int]:
+    """Host CPUs of the NUMA node the GPU hangs off, from NVML's read-only affinity query
+    (`affinity_words`: the 64-bit mask words, passed in by tests).  Empty when NVML is not usable."""
+    import os
+    ncpu = ncpu or os.cpu_count() or 1
+    if affinity_words is None:
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            affinity_words = list(pynvml.nvmlDeviceGetCpuAffinity(h, (ncpu + 63) // 64))
+        except Exception:
+            return []
+    cpus = [64 * w + b for w, word in enumerate(affinity_words) for b in range(64) if (int(word) >> b) & 1]
+    return [c for c in cpus if c < ncpu]
+
+
+def bind_near_gpu(gpu_index: int) -> list[int]:
+    """One process per GPU: run this rank on the CPUs next to its GPU, so that the pinned host buffers it
+    allocates afterwards (first touch) sit in that node's memory and its PCIe copies do not cross the
+    socket interconnect.  Returns the CPUs chosen ([] = left as it was).  Only CPUs the process may
+    already use are kept."""
+    import os
+    if not hasattr(os, "sched_setaffinity"):
+        return []
+    near = set(cpus_near_gpu(gpu_index))
+    allowed = os.sched_getaffinity(0)
+    chosen = sorted(near & allowed)
+    if not chosen or len(chosen) == len(allowed):
+        return []
+    try:
+        os.sched_setaffinity(0, chosen)
+    except OSError:
+        return []
+    return chosen

@@ -68,3 +68,13 @@ def test_two_ranks_shard_and_gather():
         assert p.exitcode == 0
     assert same, "sharded forward differs from the unsharded one"
     assert slowest == 11.0
+
+
+def test_cpus_near_gpu_decodes_the_affinity_mask():
+    from darknet_b200.shard import cpus_near_gpu
+    # CPUs 0-3 and 64-65 of a 128-CPU host
+    assert cpus_near_gpu(0, affinity_words=[0b1111, 0b11], ncpu=128) == [0, 1, 2, 3, 64, 65]
+    # CPUs beyond the host's count are dropped
+    assert cpus_near_gpu(0, affinity_words=[0b1111, 0b11], ncpu=3) == [0, 1, 2]
+    # without NVML (no GPU here) the query degrades to "unknown"
+    assert isinstance(cpus_near_gpu(0), list)
