@@ -58,8 +58,13 @@ struct alignas(64) TcArgs {
     int tiles_w, tiles_h, tiles_b;
     int total_tiles;      // n_tiles * tiles_w * tiles_h * tiles_b
     int stages;           // depth of the shared-memory ring
+    // Halo mode (3x3, stride 1, tiles of 8 x 16 pixels): ONE activation box of (8+2) x (16+2) pixels per channel
+    // block serves all nine taps (the MMA's A descriptor starts at row kh*10 + kw of the box, its 8-row groups are
+    // 10 rows apart), so activations cross L2 -> shared memory once instead of nine times.  Activations and
+    // weights then travel in two rings: a_stages boxes of a_slot bytes, b_stages weight tiles of b_bytes.
+    int halo, a_stages, b_stages, a_slot, a_box_bytes, a_pitch;
     int tmem_cols;        // TMEM columns the CTA allocates: a power of two >= 2*bn (two accumulators)
-    int debug;            // timing experiments only (DNB_TC_DEBUG): 1 no residual loads, 2 no output stores, 4 no wait before a residual request
+    int debug;            // timing experiments only (DNB_TC_DEBUG): 1 no residual loads, 2 no output stores, 4 no wait before a residual request, 8 empty epilogue, 16 no MMAs
     int stage_bufs;       // staging buffers of the epilogue: 2, or 4 with a fused residual (tiles land in them first)
     int ctas_per_sm;      // 2 for narrow tiles (TMEM and shared memory are sized so that two CTAs share an SM), else 1
     int a_bytes, b_bytes; // shared-memory bytes of one stage's activation / weight tile (1024-multiples)

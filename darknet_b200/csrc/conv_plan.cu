@@ -199,6 +199,22 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     a.c_blocks = (p->c_pad + a.bk - 1) / a.bk;
     a.taps = g.size * g.size;
     pick_pixel_tile(g, &a.wt, &a.ht, &a.bt);
+    // Halo mode (experimental, off unless DNB_TC_HALO is 1 or 2): one activation box per channel block serves all
+    // nine taps of a 3x3 stride-1 layer, which cuts the bytes that cross L2 -> shared memory by 2.3x on the
+    // 32- and 64-channel layers of large maps.  Measured on YOLOv3-608 batch 64 it does not pay yet: the 8 x 16
+    // tile, the two rings it needs and the smaller share of shared memory left for each slow the 304x304 and
+    // 152x152 layers by 25-35 % (an isolated 32 -> 64 layer without a residual gains 11 %).  1: where the
+    // heuristic below allows; 2: wherever the geometry allows (the tests use this).
+    a.halo = 0;
+    {
+        const char *e = getenv("DNB_TC_HALO");
+        const int knob = e ? atoi(e) : 0;
+        if (knob != 0 && g.size == 3 && g.stride == 1 && g.pad == 1 && a.row_bytes == 128 && g.out_w >= 8 && g.out_h >= 16) {
+            const double work_h = (double)round_up(g.out_w, 8) * round_up(g.out_h, 16) * g.batch;
+            const double work_0 = (double)round_up(g.out_w, a.wt) * round_up(g.out_h, a.ht) * round_up(g.batch, a.bt);
+            if (knob == 2 || (a.c_blocks <= 2 && work_h <= 1.08 * work_0)) { a.halo = 1; a.wt = 8; a.ht = 16; a.bt = 1; }
+        }
+    }
     a.tiles_w = (g.out_w + a.wt - 1) / a.wt;
     a.tiles_h = (g.out_h + a.ht - 1) / a.ht;
     a.tiles_b = (g.batch + a.bt - 1) / a.bt;
@@ -254,11 +270,38 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     a.debug = getenv("DNB_TC_DEBUG") ? atoi(getenv("DNB_TC_DEBUG")) : 0;
     int stages = 0;
     const bool allow2 = getenv("DNB_TC_CTAS") ? atoi(getenv("DNB_TC_CTAS")) >= 2 : true;
+    a.a_stages = a.b_stages = a.a_slot = a.a_box_bytes = a.a_pitch = 0;
+    if (a.halo) {
+        // two rings: activation boxes (one per channel block) and weight tiles (nine per box).  A weight tile is
+        // consumed in a quarter of the time an ordinary ring slot is, so that ring wants to be deep: one CTA per
+        // SM unless two still leave six weight slots each.
+        a.a_pitch = a.wt + 2;
+        a.a_box_bytes = (a.wt + 2) * (a.ht + 2) * a.row_bytes;
+        a.a_slot = round_up(a.a_box_bytes, 1024);
+        auto fit = [&](long budget, int srb_try, int a_want, int b_min) {
+            const long left = budget - (long)conv_tc_fixed_smem(srb_try, a.bn, a.stage_bufs) - (long)a_want * a.a_slot;
+            const int b = left > 0 ? (int)(left / a.b_bytes) : 0;
+            if (b < b_min) return false;
+            a.a_stages = a_want; a.b_stages = b > 12 ? 12 : b; srb = srb_try;
+            return true;
+        };
+        bool done = false;
+        if (allow2 && a.tmem_cols <= 256) {
+            const long budget = (228L * 1024) / 2 - 2048;
+            for (int srb2 = srb; srb2 >= min_srb && !done; srb2 /= 2) done = fit(budget, srb2, 2, 6);
+            if (done) a.ctas_per_sm = 2;
+        }
+        for (int srb2 = srb; srb2 >= min_srb && !done; srb2 /= 2) done = fit(max_smem, srb2, 3, 6) || fit(max_smem, srb2, 2, 4);
+        if (!done) a.halo = 0;   // the tile shape stays 8 x 16: still a valid tiling for the ordinary rings below
+        stages = 2;
+    }
+    if (!a.halo) {
     if (allow2 && a.tmem_cols <= 256) {
+        const int max2 = getenv("DNB_TC_MAX2") ? atoi(getenv("DNB_TC_MAX2")) : 4;   // ring slots per CTA when two share the SM
         const long budget = (228L * 1024) / 2 - 2048;   // per CTA when two share the SM (1 KB each is reserved by the system)
         for (int srb2 = srb; srb2 >= min_srb; srb2 /= 2) {   // narrower staged rows if that is what makes two CTAs fit
             const int s2 = (int)((budget - (long)conv_tc_fixed_smem(srb2, a.bn, a.stage_bufs)) / (a.a_bytes + a.b_bytes));
-            if (s2 >= 2) { a.ctas_per_sm = 2; stages = s2 > 4 ? 4 : s2; srb = srb2; break; }
+            if (s2 >= 2) { a.ctas_per_sm = 2; stages = s2 > max2 ? max2 : s2; srb = srb2; break; }
         }
     }
     if (a.ctas_per_sm == 1) {
@@ -272,6 +315,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
             stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.bn, a.stage_bufs)) / (a.a_bytes + a.b_bytes));
             if (stages >= want || srb == min_srb) break;
         }
+    }
     }
     if (stages > 8) stages = 8;
     if (const char *e = getenv("DNB_TC_STAGES")) {
@@ -298,6 +342,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
             uint64_t dims[4] = {(uint64_t)p->c_pad, (uint64_t)(wl > 0 ? wl : 1), (uint64_t)(hl > 0 ? hl : 1), (uint64_t)g.batch};
             uint64_t strides[3] = {pix_bytes * s, pix_bytes * g.w * s, pix_bytes * g.w * g.h};
             uint32_t box[4] = {(uint32_t)a.bk, (uint32_t)a.wt, (uint32_t)a.ht, (uint32_t)a.bt};
+            if (a.halo) { box[1] = (uint32_t)(a.wt + 2); box[2] = (uint32_t)(a.ht + 2); }
             char *base = (char *)x->data + ((size_t)ph * g.w + pw) * pix_bytes;
             if (hl <= 0 || wl <= 0) base = (char *)x->data;  // lattice empty: never addressed in-bounds
             DNB_TRY(encode_tensor_map(&a.tmx[ph * s + pw], bf16, 4, base, dims, strides, box, a.row_bytes));

@@ -47,12 +47,15 @@ namespace dnb {
 
 constexpr int TC_THREADS = 192;
 constexpr int MAX_STAGES = 8;
+constexpr int MAX_B_STAGES = 12;   // weight-tile ring of the halo mode
 constexpr int MAX_RES_BUFS = 4;   // staging buffers with a fused residual; tiles are requested two chunks ahead
 
 // ------------------------------------------------------------------ kernel
 struct TcShared {
-    uint64_t full[MAX_STAGES];
+    uint64_t full[MAX_STAGES];     // operand ring (halo mode: the ring of activation boxes)
     uint64_t empty[MAX_STAGES];
+    uint64_t full_b[MAX_B_STAGES]; // halo mode: the ring of weight tiles
+    uint64_t empty_b[MAX_B_STAGES];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint64_t res_full[MAX_RES_BUFS];   // residual tile landed in its staging buffer
@@ -93,7 +96,8 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         return;
     }
     const uint32_t stage_bytes = a.a_bytes + a.b_bytes;
-    uint8_t *after_ring = smem_raw + (ring - smem_u32(smem_raw)) + (size_t)a.stages * stage_bytes;
+    const size_t ring_bytes = a.halo ? (size_t)a.a_stages * a.a_slot + (size_t)a.b_stages * a.b_bytes : (size_t)a.stages * stage_bytes;
+    uint8_t *after_ring = smem_raw + (ring - smem_u32(smem_raw)) + ring_bytes;
     // staging buffers of 128 rows x store_row_bytes: two for plain stores; four when a residual is fused, each
     // then receiving a residual tile first and the finished output rows, in place, afterwards
     uint8_t *stage_out = after_ring;
@@ -105,9 +109,13 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < a.stages; ++s) {
+        for (int s = 0; s < MAX_STAGES; ++s) {
             mbar_init(smem_u32(&sh->full[s]), 1);
             mbar_init(smem_u32(&sh->empty[s]), 1);
+        }
+        for (int s = 0; s < MAX_B_STAGES; ++s) {
+            mbar_init(smem_u32(&sh->full_b[s]), 1);
+            mbar_init(smem_u32(&sh->empty_b[s]), 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&sh->acc_full[i]), 1);
@@ -149,6 +157,34 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
+        if (a.halo) {
+            // one activation box per channel block, then the nine weight tiles that multiply it
+            const int a_stages = a.a_stages, b_stages = a.b_stages;
+            const uint32_t a_slot = a.a_slot, a_tx = a.a_box_bytes, b_slot = a.b_bytes, b_tx = (uint32_t)bn * row_bytes;
+            const uint32_t ring_b = ring + a_stages * a_slot;
+            const uint32_t fullb0 = smem_u32(&sh->full_b[0]), emptyb0 = smem_u32(&sh->empty_b[0]);
+            int sb = 0;
+            uint32_t phase_b = 0;
+            for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok; tile += grid_stride) {
+                const int nt = tile % n_tiles, pt = tile / n_tiles;
+                const int ow0 = (pt % tiles_w) * wt, oh0 = ((pt / tiles_w) % tiles_h) * ht, b0 = (pt / ptiles_wh) * bt;
+                const int n0 = nt * bn;
+                for (int cb = 0; cb < c_blocks && ok; ++cb) {
+                    ok = mbar_wait_thread(empty0 + 8 * stage, phase ^ 1, abort_flag, status, WAIT_EMPTY);
+                    if (!ok) break;
+                    mbar_expect_tx(full0 + 8 * stage, a_tx);
+                    tma_load_4d(ring + stage * a_slot, maps, full0 + 8 * stage, cb * bk, ow0 - cpad, oh0 - cpad, b0);
+                    if (++stage == a_stages) { stage = 0; phase ^= 1; }
+                    for (int tap = 0; tap < taps; ++tap) {
+                        ok = mbar_wait_thread(emptyb0 + 8 * sb, phase_b ^ 1, abort_flag, status, WAIT_EMPTY);
+                        if (!ok) break;
+                        mbar_expect_tx(fullb0 + 8 * sb, b_tx);
+                        tma_load_3d(ring_b + sb * b_slot, wmap, fullb0 + 8 * sb, cb * bk, n0, tap);
+                        if (++sb == b_stages) { sb = 0; phase_b ^= 1; }
+                    }
+                }
+            }
+        } else
         for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok; tile += grid_stride) {
             const int nt = tile % n_tiles, pt = tile / n_tiles;
             const int ow0 = (pt % tiles_w) * wt;
@@ -189,11 +225,58 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         const uint64_t slot_step = stage_bytes >> 4;   // descriptor address field counts 16-byte units
         const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
         int *status = a.status;
+        const int dbg_mma = a.debug;
         int stage = 0;
         uint32_t phase = 0;
         uint64_t da = da0, db = db0;
         int it = 0;
         bool ok = true;
+        if (a.halo) {
+            const int a_stages = a.a_stages, b_stages = a.b_stages, pitch = a.a_pitch, ksize = a.g.size;
+            const uint32_t fullb0 = smem_u32(&sh->full_b[0]), emptyb0 = smem_u32(&sh->empty_b[0]);
+            // A descriptor of a box: rows of 128 bytes, 8-row groups one box row (pitch pixels) apart
+            uint64_t dbox0 = make_smem_desc(ring, 128);
+            dbox0 = (dbox0 & ~((uint64_t)0x3FFF << 32)) | ((uint64_t)(pitch * 8) << 32);
+            const uint64_t dw0 = make_smem_desc(ring + a_stages * a.a_slot, 128);
+            const uint64_t a_step = (uint64_t)(a.a_slot >> 4), b_step = (uint64_t)(a.b_bytes >> 4);
+            int sb = 0;
+            uint32_t phase_b = 0;
+            for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok; tile += grid_stride, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                ok = mbar_wait_thread(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1, abort_flag, status, WAIT_ACC_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * acc_stride;
+                uint32_t accumulate = 0u;
+                for (int cb = 0; cb < c_blocks && ok; ++cb) {
+                    ok = mbar_wait_thread(full0 + 8 * stage, phase, abort_flag, status, WAIT_FULL);
+                    if (!ok) break;
+                    const uint64_t dbox = dbox0 + stage * a_step;
+                    int kh = 0, kw = 0;
+                    for (int tap = 0; tap < taps; ++tap) {
+                        ok = mbar_wait_thread(fullb0 + 8 * sb, phase_b, abort_flag, status, WAIT_FULL);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint64_t da = dbox + (uint64_t)((kh * pitch + kw) * 8);   // 128-byte rows in 16-byte units
+                        const uint64_t db = dw0 + sb * b_step;
+                        if (!(dbg_mma & 16)) {
+                            umma<is_bf16>(d_tmem, da, db, idesc, accumulate);
+                            umma<is_bf16>(d_tmem, da + 2, db + 2, idesc, 1u);
+                            umma<is_bf16>(d_tmem, da + 4, db + 4, idesc, 1u);
+                            umma<is_bf16>(d_tmem, da + 6, db + 6, idesc, 1u);
+                        }
+                        accumulate = 1u;
+                        umma_commit(emptyb0 + 8 * sb);   // the weight tile is free when these MMAs retire
+                        if (++sb == b_stages) { sb = 0; phase_b ^= 1; }
+                        if (++kw == ksize) { kw = 0; ++kh; }
+                    }
+                    if (ok) umma_commit(empty0 + 8 * stage);   // and the box when all nine taps have read it
+                    if (++stage == a_stages) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(smem_u32(&sh->acc_full[acc]));
+            }
+        } else
         for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok; tile += grid_stride, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
@@ -205,7 +288,8 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 ok = mbar_wait_thread(full0 + 8 * stage, phase, abort_flag, status, WAIT_FULL);
                 if (!ok) break;
                 tc_fence_after();
-                if (k_steps == 4) {
+                if (dbg_mma & 16) {
+                } else if (k_steps == 4) {
                     umma<is_bf16>(d_tmem, da, db, idesc, ki != 0);
                     umma<is_bf16>(d_tmem, da + 2, db + 2, idesc, 1u);
                     umma<is_bf16>(d_tmem, da + 4, db + 4, idesc, 1u);
@@ -293,7 +377,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             // stay resident in the instruction cache next to the MMA warp's loop.
             const size_t plane = (size_t)g.out_h * g.out_w;
 #pragma unroll 1
-            for (int c0 = 0; c0 < bn; c0 += CPC) {
+            for (int c0 = (dbg & 8) ? bn : 0; c0 < bn; c0 += CPC) {
                 uint32_t r[CPC];
                 constexpr int RES_V = CPC * (OUT_BF16 ? 2 : 4) / 16;      // 16-byte pieces of a staged row
 #pragma unroll
@@ -427,6 +511,7 @@ size_t conv_tc_fixed_smem(int store_row_bytes, int bn, int stage_bufs)
 
 size_t conv_tc_smem_bytes(const TcArgs &a)
 {
+    if (a.halo) return (size_t)a.a_stages * a.a_slot + (size_t)a.b_stages * a.b_bytes + conv_tc_fixed_smem(a.store_row_bytes, a.bn, a.stage_bufs);
     return (size_t)a.stages * (a.a_bytes + a.b_bytes) + conv_tc_fixed_smem(a.store_row_bytes, a.bn, a.stage_bufs);
 }
 

@@ -340,6 +340,37 @@ def test_conv_tc_bf16(name):
     assert rel_to_max(got3, want) < TOL_BF16
 
 
+HALO_CASES = {
+    "c32_n64": dict(b=2, c=32, h=32, w=24, n=64, size=3),
+    "c64_n128_two_blocks": dict(b=1, c=64, h=48, w=40, n=128, size=3),
+    "ragged_19x21": dict(b=3, c=32, h=21, w=19, n=32, size=3),
+    "c40_ragged_k": dict(b=1, c=40, h=16, w=8, n=16, size=3),
+    "c128_n256_forced": dict(b=1, c=128, h=32, w=16, n=256, size=3),
+    "n512_two_ntiles_forced": dict(b=1, c=64, h=16, w=16, n=512, size=3),
+}
+
+
+@pytest.mark.parametrize("name", list(HALO_CASES))
+@pytest.mark.parametrize("mode,tol", [(dn.MODE_TF32, TOL_TF32), (dn.MODE_BF16, TOL_BF16)])
+def test_conv_tc_halo_mode(name, mode, tol, monkeypatch):
+    """3x3 stride-1 layers in halo mode (one activation box per channel block serves all nine taps through
+    shifted A descriptors), forced on wherever the geometry allows, against the ordinary rings and the checker."""
+    case = conv_case(250, **HALO_CASES[name])
+    want = oracle_conv(case)
+    monkeypatch.setenv("DNB_TC_HALO", "2")
+    _, got, _ = run_conv(case, mode, "nhwc", "nhwc")
+    monkeypatch.setenv("DNB_TC_HALO", "0")
+    _, plain, _ = run_conv(case, mode, "nhwc", "nhwc")
+    err = rel_to_max(got, want)
+    assert err < tol, f"{name}: rel error {err:.3g}"
+    # same products in another summation order: a few results land on the neighbouring TF32 (bf16) value when rounded for storage
+    assert rel_to_max(got, plain) < (2e-3 if mode == dn.MODE_TF32 else 1e-2)
+    monkeypatch.setenv("DNB_TC_HALO", "2")
+    _, got_nchw, got_nhwc = run_conv(case, mode, "nchw", "nchw", both=True)
+    assert np.array_equal(got_nchw, got_nhwc)
+    assert rel_to_max(got_nchw, want) < tol
+
+
 def test_conv_tc_all_ones_counts_taps():
     # analytic known answer: ones everywhere -> in-image taps x channels, exact in TF32 and BF16
     C, H, W, N = 16, 9, 10, 16
