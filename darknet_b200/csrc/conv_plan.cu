@@ -310,7 +310,8 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
         // residual wait and store per staged chunk) would outlast the tile's MMAs: fewer, wider chunks then.
         const int k_iters = g.size * g.size * a.c_blocks;
         const bool short_k_rule = getenv("DNB_TC_SHORTK") ? atoi(getenv("DNB_TC_SHORTK")) != 0 : true;
-        const int want = (residual && k_iters < 64 && min_stages > 3 && short_k_rule) ? 3 : min_stages;
+        const int short_k = bf16 ? 32 : 64;   // measured: 76x76x128 -> 256 layers want the wide rows in both modes, 38x38x256 -> 512 only in TF32
+        const int want = (residual && k_iters < short_k && min_stages > 3 && short_k_rule) ? 3 : min_stages;
         for (;; srb /= 2) {
             stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.bn, a.stage_bufs)) / (a.a_bytes + a.b_bytes));
             if (stages >= want || srb == min_srb) break;
