@@ -136,17 +136,21 @@ conv_stem_tc_kernel(const __grid_constant__ StemTcArgs a)
             const int b = p / plane, rem = p - b * plane;
             const int oy = rem / g.out_w, ox = rem - oy * g.out_w;
             const int iy0 = oy * g.stride - g.pad, ix0 = ox * g.stride - g.pad;
-            const float *xb = x + (size_t)b * xs_b;
+            // three row and three column validity flags and one base pointer: a tap costs one predicated load
+            const bool rv0 = valid && (unsigned)iy0 < (unsigned)g.h, rv1 = valid && (unsigned)(iy0 + 1) < (unsigned)g.h,
+                       rv2 = valid && (unsigned)(iy0 + 2) < (unsigned)g.h;
+            const bool cv0 = (unsigned)ix0 < (unsigned)g.w, cv1 = (unsigned)(ix0 + 1) < (unsigned)g.w, cv2 = (unsigned)(ix0 + 2) < (unsigned)g.w;
+            const float *xp = x + (size_t)b * xs_b + (long long)iy0 * xs_h + (long long)ix0 * xs_w;   // dereferenced only where valid
 #pragma unroll
             for (int c = 0; c < C; ++c)
 #pragma unroll
-                for (int kh = 0; kh < 3; ++kh)
-#pragma unroll
-                    for (int kw = 0; kw < 3; ++kw) {
-                        const int iy = iy0 + kh, ix = ix0 + kw;
-                        const bool in = valid && (unsigned)iy < (unsigned)g.h && (unsigned)ix < (unsigned)g.w;
-                        v[c * 9 + kh * 3 + kw] = in ? __ldg(xb + c * xs_c + iy * xs_h + ix * xs_w) : 0.f;
-                    }
+                for (int kh = 0; kh < 3; ++kh) {
+                    const bool rv = kh == 0 ? rv0 : (kh == 1 ? rv1 : rv2);
+                    const float *rp = xp + c * xs_c + kh * xs_h;
+                    v[c * 9 + kh * 3 + 0] = (rv && cv0) ? __ldg(rp) : 0.f;
+                    v[c * 9 + kh * 3 + 1] = (rv && cv1) ? __ldg(rp + xs_w) : 0.f;
+                    v[c * 9 + kh * 3 + 2] = (rv && cv2) ? __ldg(rp + 2 * xs_w) : 0.f;
+                }
         }
         if (it > 0) {
             // ---- epilogue of the previous tile (its MMAs were issued at the end of the previous iteration)
@@ -178,7 +182,8 @@ conv_stem_tc_kernel(const __grid_constant__ StemTcArgs a)
                             const int j = 4 * q + e;
                             float t = stem_act<ACT>(fmaf(__uint_as_float(r[j]), scv[e], sfv[e]), runtime_act);
                             if (do_round) t = round_tf32(t);
-                            o[j] = c0 + j < g.n ? t : 0.f;
+                            // beyond the layer's filters scale and shift are zero: only an activation with f(0) != 0 needs the mask
+                            o[j] = (ACT == ST_ACT_GENERIC && c0 + j >= g.n) ? 0.f : t;
                         }
                     }
                     if (!OUT_BF16) {

@@ -53,13 +53,13 @@ __device__ __forceinline__ float activate_fast(float x, int a)
     return activate_call(x, a);
 }
 
-// Round an fp32 value to the nearest TF32 (10-bit mantissa) value, ties away
-// from zero, and return it as fp32 bits with the low 13 mantissa bits clear.
+// Round an fp32 value to the nearest TF32 (10-bit mantissa) value, ties away from zero, low 13 mantissa
+// bits clear: what cvt.rna.tf32.f32 computes for finite values, written as an integer add and a mask
+// because the conversion instruction issues at a fraction of the rate and the epilogues run it per element.
+// (Infinity stays infinity; a NaN may become infinity.)
 __device__ __forceinline__ float round_tf32(float x)
 {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
 }
 
 template <typename T> __device__ __forceinline__ float to_float(T v);
