@@ -428,7 +428,11 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                             t = act_apply<ACT2>(res_alpha * t + res_beta * rv, act2);
                         }
                         if (!OUT_BF16 && do_round) t = round_tf32(t);
-                        r[j] = __float_as_uint(j < nvalid ? t : 0.f);
+                        // columns beyond the layer's filters: scale, shift, weights and residual are all zero there, so
+                        // linear and leaky epilogues produce the zero by themselves; others need the mask
+                        constexpr bool self_zero = (ACT == DNB_LINEAR || ACT == DNB_LEAKY) &&
+                                                   (ACT2 == ACT2_NONE || ACT2 == DNB_LINEAR || ACT2 == DNB_LEAKY);
+                        r[j] = __float_as_uint((self_zero || j < nvalid) ? t : 0.f);
                     }
                 }
                 const uint32_t buf = chunk_count & buf_mask;
