@@ -296,27 +296,27 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
         stages = 2;
     }
     if (!a.halo) {
-    if (allow2 && a.tmem_cols <= 256) {
-        const int max2 = getenv("DNB_TC_MAX2") ? atoi(getenv("DNB_TC_MAX2")) : 4;   // ring slots per CTA when two share the SM
-        const long budget = (228L * 1024) / 2 - 2048;   // per CTA when two share the SM (1 KB each is reserved by the system)
-        for (int srb2 = srb; srb2 >= min_srb; srb2 /= 2) {   // narrower staged rows if that is what makes two CTAs fit
-            const int s2 = (int)((budget - (long)conv_tc_fixed_smem(srb2, a.bn, a.stage_bufs)) / (a.a_bytes + a.b_bytes));
-            if (s2 >= 2) { a.ctas_per_sm = 2; stages = s2 > max2 ? max2 : s2; srb = srb2; break; }
+        if (allow2 && a.tmem_cols <= 256) {
+            const int max2 = getenv("DNB_TC_MAX2") ? atoi(getenv("DNB_TC_MAX2")) : 4;   // ring slots per CTA when two share the SM
+            const long budget = (228L * 1024) / 2 - 2048;   // per CTA when two share the SM (1 KB each is reserved by the system)
+            for (int srb2 = srb; srb2 >= min_srb; srb2 /= 2) {   // narrower staged rows if that is what makes two CTAs fit
+                const int s2 = (int)((budget - (long)conv_tc_fixed_smem(srb2, a.bn, a.stage_bufs)) / (a.a_bytes + a.b_bytes));
+                if (s2 >= 2) { a.ctas_per_sm = 2; stages = s2 > max2 ? max2 : s2; srb = srb2; break; }
+            }
         }
-    }
-    if (a.ctas_per_sm == 1) {
-        // The depth of the ring is what hides the operand loads' latency: four slots before wide staged rows.
-        // The exception is a fused residual behind a short K loop, where the epilogue (one round of barrier,
-        // residual wait and store per staged chunk) would outlast the tile's MMAs: fewer, wider chunks then.
-        const int k_iters = g.size * g.size * a.c_blocks;
-        const bool short_k_rule = getenv("DNB_TC_SHORTK") ? atoi(getenv("DNB_TC_SHORTK")) != 0 : true;
-        const int short_k = bf16 ? 32 : 64;   // measured: 76x76x128 -> 256 layers want the wide rows in both modes, 38x38x256 -> 512 only in TF32
-        const int want = (residual && k_iters < short_k && min_stages > 3 && short_k_rule) ? 3 : min_stages;
-        for (;; srb /= 2) {
-            stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.bn, a.stage_bufs)) / (a.a_bytes + a.b_bytes));
-            if (stages >= want || srb == min_srb) break;
+        if (a.ctas_per_sm == 1) {
+            // The depth of the ring is what hides the operand loads' latency: four slots before wide staged rows.
+            // The exception is a fused residual behind a short K loop, where the epilogue (one round of barrier,
+            // residual wait and store per staged chunk) would outlast the tile's MMAs: fewer, wider chunks then.
+            const int k_iters = g.size * g.size * a.c_blocks;
+            const bool short_k_rule = getenv("DNB_TC_SHORTK") ? atoi(getenv("DNB_TC_SHORTK")) != 0 : true;
+            const int short_k = bf16 ? 32 : 64;   // measured: 76x76x128 -> 256 layers want the wide rows in both modes, 38x38x256 -> 512 only in TF32
+            const int want = (residual && k_iters < short_k && min_stages > 3 && short_k_rule) ? 3 : min_stages;
+            for (;; srb /= 2) {
+                stages = (int)((max_smem - (long)conv_tc_fixed_smem(srb, a.bn, a.stage_bufs)) / (a.a_bytes + a.b_bytes));
+                if (stages >= want || srb == min_srb) break;
+            }
         }
-    }
     }
     if (stages > 8) stages = 8;
     if (const char *e = getenv("DNB_TC_STAGES")) {
