@@ -75,6 +75,22 @@ def test_plan_validation_needs_no_device():
         dn.check(L.dnb_conv_plan_create(None, 0, C.byref(h)))
 
 
+def test_degenerate_geometry_is_refused():
+    """Empty batches, empty images, no filters, zero stride or size, negative padding, unknown activation:
+    refused with a message, nothing is launched (the reference would divide by zero or abort)."""
+    L = dn.lib()
+    h = C.c_void_p()
+    cases = [dn.ConvDesc(0, 8, 8, 8, 8, 1, 3, 1, 1, 0, 3, 0), dn.ConvDesc(1, 8, 8, 0, 8, 1, 3, 1, 1, 0, 3, 0),
+             dn.ConvDesc(1, 8, 8, 8, 0, 1, 3, 1, 1, 0, 3, 0), dn.ConvDesc(1, 8, 8, 8, 8, 1, 3, 0, 1, 0, 3, 0),
+             dn.ConvDesc(1, 8, 8, 8, 8, 1, 0, 1, 1, 0, 3, 0), dn.ConvDesc(1, 8, 8, 8, 8, 1, 3, 1, -1, 0, 3, 0),
+             dn.ConvDesc(1, 8, 8, 8, 8, 1, 3, 1, 1, 0, 99, 0)]
+    for d in cases:
+        assert L.dnb_conv_plan_create(C.byref(d), dn.MODE_TF32, C.byref(h)) == dn.EINVAL
+        assert len(L.dnb_last_error()) > 10
+    t = dn.Tensor(256, dn.NHWC, dn.F32, 0, 8, 4, 4, 8)      # empty batch
+    assert L.dnb_maxpool_forward(C.byref(t), C.byref(t), 2, 2, 1, None) == dn.EINVAL
+
+
 def test_tensor_validation():
     L = dn.lib()
     t = dn.Tensor(0, dn.NHWC, dn.F32, 1, 8, 4, 4, 8)
