@@ -477,6 +477,7 @@ extern "C" int dnb_network_forward(dnb_network *net, const float *device_input, 
 {
     if (!net || !device_input) DNB_FAIL(DNB_EINVAL, "network_forward: null argument");
     if (!net->weights_loaded) DNB_FAIL(DNB_EINVAL, "network_forward: load_weights has not been called");
+    if (net->submitted != net->collected) DNB_FAIL(DNB_EINVAL, "network_forward: a submitted step is still in flight (the layers' outputs are shared); collect it first");
     cudaStream_t s = (cudaStream_t)stream;  // NULL is the legacy default stream, as everywhere in CUDA
     DNB_TRY(prepare_input(net, device_input, s));
     for (int i = 0; i < (int)net->layers.size(); ++i) DNB_TRY(forward_layer(net, i, device_input, s));
@@ -601,6 +602,7 @@ extern "C" int dnb_network_layer_output(dnb_network *net, int i, float *host_out
 {
     if (!net || !host_out || i < 0 || i >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "layer_output: bad argument");
     Layer &L = net->layers[i];
+    if (net->submitted != net->collected) DNB_FAIL(DNB_EINVAL, "layer_output: a submitted step is still in flight; collect it first");
     if (!L.out.data)
         DNB_FAIL(DNB_EUNSUPPORTED, "layer %d is fused into the shortcut layer %d and has no output of its own (DNB_FUSE_SHORTCUT=0 keeps it)", i, i + 1);
     const size_t elems = (size_t)net->batch * L.out_c * L.out_h * L.out_w;
@@ -656,6 +658,7 @@ extern "C" int dnb_network_forward_timed(dnb_network *net, const float *device_i
 {
     if (!net || !device_input || slot < 0 || slot > 4096) DNB_FAIL(DNB_EINVAL, "network_forward_timed: bad argument");
     if (!net->weights_loaded) DNB_FAIL(DNB_EINVAL, "network_forward_timed: load_weights has not been called");
+    if (net->submitted != net->collected) DNB_FAIL(DNB_EINVAL, "network_forward_timed: a submitted step is still in flight; collect it first");
     const int n = (int)net->layers.size();
     while ((int)net->events.size() < (slot + 1) * (n + 1)) {
         cudaEvent_t e;
