@@ -270,7 +270,9 @@ def run_reference_gpu(args):
     write_net_files(d, cfg)
     ref = orc.ReferenceGpu()
     net = ref.load(os.path.join(d, "net.cfg"), os.path.join(d, "net.weights"))
-    x = synth.seeded_input(cfg, 0, "normal" if args.workload.startswith("conv") else "uniform")
+    import torch
+    # page-locked input for all three rows: network_predict pushes it with a blocking cudaMemcpy (src/cuda.c:153-158)
+    x = torch.from_numpy(synth.seeded_input(cfg, 0, "normal" if args.workload.startswith("conv") else "uniform")).pin_memory().numpy()
     ref.time_predict(net, x, max(args.warmup, 1))
     sec = ref.time_predict(net, x, args.steps) / args.steps
     # the same `network` after b200_attach: Darknet's loop, buffers and layout, this library's kernels per layer
@@ -282,7 +284,17 @@ def run_reference_gpu(args):
         asec = ref.time_predict(net, x, args.steps) / args.steps
         att = {"value": batch / asec, "unit": UNIT, "ms_per_step": asec * 1000.0, "layers_repointed": attached,
                "note": "forward_gpu pointers of the unmodified network re-pointed by b200_attach (TF32 plans, NCHW fp32 tensors at every layer boundary)"}
+    # and with the whole forward pass handed over (b200_attach_network), still through Darknet's network_predict
+    whole = None
+    if attached > 0:
+        ref.detach(net)
+    if ref.attach_network(net, dn.MODE_TF32) > 0:
+        ref.time_predict(net, x, max(args.warmup, 1))
+        wsec = ref.time_predict(net, x, args.steps) / args.steps
+        whole = {"value": batch / wsec, "unit": UNIT, "ms_per_step": wsec * 1000.0,
+                 "note": "b200_attach_network: layer 0's forward_gpu runs the library's own network object, [yolo] and last-layer outputs copied into Darknet's buffers"}
     print(json.dumps({"impl": "reference-gpu", "metric": metric, "value": batch / sec, "unit": UNIT, "ms_per_step": sec * 1000.0, "attached": att,
+                      "attached_network": whole,
                       "steps": args.steps, "dtype": "f32", "data": "synthetic",
                       "config": {"workload": f"{desc}, batch {batch}, the reference's CUDA build recompiled for sm_100a "
                                              "(im2col + cuBLAS sgemm per image), network_predict with host buffers"}}), flush=True)

@@ -42,6 +42,7 @@ struct Layer {
     float *host_slot[2] = {nullptr, nullptr};   // pinned result buffers of the two steps that may be in flight
     cudaEvent_t done = nullptr;    // compute stream: the layer's output is complete
     cudaEvent_t copied = nullptr;  // copy stream: the device-to-host copy of that output is complete
+    bool params_given = false;     // dnb_network_set_conv_params has been called for this convolution
     // softmax
     int groups = 1;
     float temperature = 1.f;
@@ -133,6 +134,7 @@ struct dnb_network {
     int *status_host = nullptr;           // pinned copy read after each predict
     int device = 0;
     bool weights_loaded = false;
+    int convs_with_params = 0;
     std::vector<cudaEvent_t> events;
 };
 
@@ -428,6 +430,37 @@ extern "C" int dnb_load_weights(dnb_network *net, const char *path)
     }
     net->weights_loaded = true;
     return DNB_OK;
+}
+
+// The same derived tensors from host arrays instead of a file: what a host that has already run the
+// reference's load_weights holds in l.weights, l.biases, l.scales, l.rolling_mean, l.rolling_variance.
+extern "C" int dnb_network_set_conv_params(dnb_network *net, int layer, const float *weights, const float *biases,
+                                           const float *scales, const float *rolling_mean, const float *rolling_variance)
+{
+    if (!net || layer < 0 || layer >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "set_conv_params: bad argument");
+    Layer &L = net->layers[layer];
+    if (L.kind != L_CONV) DNB_FAIL(DNB_EINVAL, "set_conv_params: layer %d is not convolutional", layer);
+    DNB_TRY(dnb_conv_plan_set_params(L.plan, weights, biases, scales, rolling_mean, rolling_variance));
+    if (!L.params_given) { L.params_given = true; ++net->convs_with_params; }
+    int convs = 0;
+    for (const Layer &K : net->layers) convs += K.kind == L_CONV;
+    if (net->convs_with_params == convs) net->weights_loaded = true;
+    return DNB_OK;
+}
+
+// Layer `layer`'s current output in Darknet's layout (NCHW f32) into device memory of the caller, on `stream`.
+extern "C" int dnb_network_export_layer(dnb_network *net, int layer, float *device_nchw, void *stream)
+{
+    if (!net || !device_nchw || layer < 0 || layer >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "export_layer: bad argument");
+    Layer &L = net->layers[layer];
+    if (!L.out.data) DNB_FAIL(DNB_EUNSUPPORTED, "layer %d is fused into the shortcut layer %d and has no output of its own", layer, layer + 1);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (L.out.layout == DNB_NCHW) {
+        DNB_CUDA(cudaMemcpyAsync(device_nchw, L.out.data, tensor_elems(&L.out) * sizeof(float), cudaMemcpyDeviceToDevice, s));
+        return DNB_OK;
+    }
+    dnb_tensor o{device_nchw, DNB_NCHW, DNB_F32, net->batch, L.out_c, L.out_h, L.out_w, 0};
+    return launch_convert(&L.out, &o, 0, 0, 0, s);
 }
 
 // One layer of forward_network_gpu's loop (src/network.c:772-785).

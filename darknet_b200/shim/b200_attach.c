@@ -19,6 +19,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <cuda_runtime_api.h>
+
 #include "darknet.h"
 
 #include "b200_attach.h"
@@ -37,6 +39,9 @@ typedef struct attached {
     int n;
     dnb_conv_plan **plans;      /* per layer, NULL where the layer is not a replaced convolution */
     forward_fn *original;       /* per layer, the pointer that was there before */
+    dnb_network *whole;         /* b200_attach_network: this library's own network object, or NULL */
+    float **saved_delta;        /* b200_attach_network: the delta_gpu pointers taken out of the layers */
+    char *pinned;               /* per layer: l.output was page-locked here (and is released by b200_detach) */
     struct attached *next;
 } attached;
 
@@ -120,12 +125,31 @@ static int route_is_covered(const network *net, const layer *l)
     return 1;
 }
 
+/* Darknet pulls results with a blocking cudaMemcpy into calloc'd host arrays (cuda_pull_array, src/cuda.c:160-165):
+ * from pageable memory that runs at a fraction of the link's rate.  The arrays it pulls at inference, every
+ * [yolo] layer's l.output and the last layer's, are page-locked in place while the network is attached. */
+static void pin_outputs(attached *a, network *net)
+{
+    a->pinned = calloc(net->n, 1);
+    for (int i = 0; i < net->n; ++i) {
+        layer *l = &net->layers[i];
+        if ((l->type != YOLO && i != net->n - 1) || !l->output) continue;
+        if (cudaHostRegister(l->output, (size_t)l->batch * l->outputs * sizeof(float), cudaHostRegisterDefault) == cudaSuccess) a->pinned[i] = 1;
+        else cudaGetLastError();   /* already locked or refused: the pull stays as slow as it was */
+    }
+}
+
 static void release(attached *a, network *net)
 {
     for (int i = 0; i < a->n; ++i) {
+        if (net && a->pinned && a->pinned[i]) cudaHostUnregister(net->layers[i].output);
         if (net && a->original[i]) net->layers[i].forward_gpu = a->original[i];
+        if (net && a->saved_delta && a->saved_delta[i]) net->layers[i].delta_gpu = a->saved_delta[i];
         if (a->plans[i]) dnb_conv_plan_destroy(a->plans[i]);
     }
+    if (a->whole) dnb_free_network(a->whole);
+    free(a->pinned);
+    free(a->saved_delta);
     free(a->plans);
     free(a->original);
     free(a);
@@ -172,9 +196,133 @@ int b200_attach(network *net, int mode)
             ++count;
         }
     }
+    pin_outputs(a, net);
     a->next = g_attached;
     g_attached = a;
     return count;
+}
+
+/* ------------------------------------------------------------------ whole-network attach
+ * The per-layer form above keeps Darknet's tensors (NCHW fp32) at every layer boundary, and Darknet's loop
+ * zero-fills every layer's delta before calling it (src/network.c:775-777).  This form hands the whole forward
+ * pass to the library's own network object (channels-last between layers, shortcuts fused into convolutions):
+ * layer 0's forward_gpu runs all layers and writes Darknet's l.output_gpu only where the reference still looks,
+ * i.e. every [yolo] layer (whose host copy the detection code reads) and the last layer (which
+ * pull_network_output copies, src/network.c:786); every other forward_gpu becomes a no-op and the delta_gpu
+ * pointers are set aside so that the loop has nothing to clear.  Intermediate l.output_gpu buffers are then
+ * not written: a host that reads them uses b200_attach instead. */
+static const char *const kActivationNames[] = {"logistic", "relu", "relie", "linear", "ramp", "tanh", "plse",
+                                               "leaky", "elu", "loggy", "stair", "hardtan", "lhtan", "selu"};
+
+/* The cfg text of the network as the structs describe it (sizes and indices resolved), or NULL when a layer
+ * type is outside the convolutional forward path. */
+static char *cfg_from_structs(const network *net)
+{
+    size_t cap = 4096 + (size_t)net->n * 512, len = 0;
+    char *t = malloc(cap);
+    if (!t) return NULL;
+    len += snprintf(t + len, cap - len, "[net]\nbatch=%d\nsubdivisions=1\nheight=%d\nwidth=%d\nchannels=%d\n", net->batch, net->h, net->w, net->c);
+    for (int i = 0; i < net->n; ++i) {
+        const layer *l = &net->layers[i];
+        if (cap - len < 1024) { free(t); return NULL; }
+        if ((int)l->activation < 0 || (int)l->activation > 13) { free(t); return NULL; }
+        const char *act = kActivationNames[(int)l->activation];
+        switch (l->type) {
+        case CONVOLUTIONAL:
+            if (l->binary && !l->xnor) { free(t); return NULL; }
+            len += snprintf(t + len, cap - len, "[convolutional]\nbatch_normalize=%d\nfilters=%d\nsize=%d\nstride=%d\npadding=%d\ngroups=%d\nactivation=%s\nxnor=%d\n",
+                            l->batch_normalize, l->n, l->size, l->stride, l->pad, l->groups, act, l->xnor);
+            break;
+        case MAXPOOL:
+            len += snprintf(t + len, cap - len, "[maxpool]\nsize=%d\nstride=%d\npadding=%d\n", l->size, l->stride, l->pad);
+            break;
+        case UPSAMPLE:
+            if (l->reverse) { free(t); return NULL; }
+            len += snprintf(t + len, cap - len, "[upsample]\nstride=%d\nscale=%.9g\n", l->stride, l->scale);
+            break;
+        case SHORTCUT:
+            len += snprintf(t + len, cap - len, "[shortcut]\nfrom=%d\nalpha=%.9g\nbeta=%.9g\nactivation=%s\n", l->index, l->alpha, l->beta, act);
+            break;
+        case ROUTE:
+            len += snprintf(t + len, cap - len, "[route]\nlayers=");
+            for (int k = 0; k < l->n; ++k) len += snprintf(t + len, cap - len, "%s%d", k ? "," : "", l->input_layers[k]);
+            len += snprintf(t + len, cap - len, "\n");
+            break;
+        case YOLO:
+            len += snprintf(t + len, cap - len, "[yolo]\nmask=");
+            for (int k = 0; k < l->n; ++k) len += snprintf(t + len, cap - len, "%s%d", k ? "," : "", l->mask ? l->mask[k] : k);
+            len += snprintf(t + len, cap - len, "\nnum=%d\nclasses=%d\n", l->total, l->classes);
+            break;
+        case AVGPOOL:
+            len += snprintf(t + len, cap - len, "[avgpool]\n");
+            break;
+        case SOFTMAX:
+            if (l->softmax_tree) { free(t); return NULL; }
+            len += snprintf(t + len, cap - len, "[softmax]\ngroups=%d\ntemperature=%.9g\n", l->groups, l->temperature);
+            break;
+        default:
+            free(t);
+            return NULL;
+        }
+    }
+    return t;
+}
+
+static void forward_whole_network_b200(layer l, network net)
+{
+    attached *a = find_attached(net.layers);
+    if (!a || !a->whole) error("darknet_b200: network called without being attached");
+    (void)l;
+    if (dnb_network_forward(a->whole, net.input_gpu, NULL)) fail("network");
+    for (int i = 0; i < a->n; ++i)
+        if (net.layers[i].type == YOLO || i == a->n - 1)
+            if (dnb_network_export_layer(a->whole, i, net.layers[i].output_gpu, NULL)) fail("export");
+}
+
+static void forward_nothing_b200(layer l, network net) { (void)l; (void)net; }
+
+/* What forward_yolo_layer_gpu leaves behind at inference (src/yolo_layer.c:347-362): the activated tensor in
+ * l.output_gpu, already written by layer 0's call, and its host copy in l.output. */
+static void forward_yolo_pull_b200(layer l, network net)
+{
+    (void)net;
+    cuda_pull_array(l.output_gpu, l.output, (size_t)l.batch * l.outputs);
+}
+
+int b200_attach_network(network *net, int mode)
+{
+    if (!net || net->n < 1 || find_attached(net->layers)) return -1;
+    char *cfg = cfg_from_structs(net);
+    if (!cfg) return -1;
+    dnb_network *whole = NULL;
+    int rc = dnb_parse_network_cfg_text(cfg, mode, 0, &whole);
+    free(cfg);
+    if (rc) return -1;
+    for (int i = 0; i < net->n && !rc; ++i) {
+        layer *l = &net->layers[i];
+        if (l->type != CONVOLUTIONAL) continue;
+        rc = dnb_network_set_conv_params(whole, i, l->weights, l->biases, l->batch_normalize ? l->scales : NULL,
+                                         l->batch_normalize ? l->rolling_mean : NULL, l->batch_normalize ? l->rolling_variance : NULL);
+    }
+    if (rc) { dnb_free_network(whole); return -1; }
+    attached *a = calloc(1, sizeof *a);
+    a->layers = net->layers;
+    a->n = net->n;
+    a->plans = calloc(net->n, sizeof *a->plans);
+    a->original = calloc(net->n, sizeof *a->original);
+    a->saved_delta = calloc(net->n, sizeof *a->saved_delta);
+    a->whole = whole;
+    for (int i = 0; i < net->n; ++i) {
+        layer *l = &net->layers[i];
+        a->original[i] = l->forward_gpu;
+        a->saved_delta[i] = l->delta_gpu;
+        l->delta_gpu = NULL;
+        l->forward_gpu = i == 0 ? forward_whole_network_b200 : (l->type == YOLO ? forward_yolo_pull_b200 : forward_nothing_b200);
+    }
+    pin_outputs(a, net);
+    a->next = g_attached;
+    g_attached = a;
+    return net->n;
 }
 
 void b200_detach(network *net)

@@ -25,6 +25,17 @@ struct network;
  * stride > 1, reverse upsample, routes over inputs of unequal size) keep the reference's pointer. */
 int b200_attach(struct network *net, int mode);
 
+/* The whole forward pass through this library's own network object (channels-last between layers, shortcut
+ * layers fused into convolutions), still behind Darknet's network_predict: layer 0's forward_gpu runs every
+ * layer, the other pointers become no-ops, and Darknet's device buffers are written only where the reference
+ * still looks: l.output_gpu (and the host copy l.output) of every [yolo] layer, and l.output_gpu of the last
+ * layer, which pull_network_output copies (src/network.c:786).  The layers' delta_gpu pointers are set aside
+ * until b200_detach so that forward_network_gpu has nothing to clear (src/network.c:775-777).  Returns the
+ * number of layers, or -1 when a layer type is outside the convolutional forward path (use b200_attach then)
+ * or the library refused the network (dnb_last_error()).  A host that reads intermediate l.output_gpu
+ * buffers uses b200_attach instead. */
+int b200_attach_network(struct network *net, int mode);
+
 /* Restores the reference's pointers and frees the plans.  Call before free_network. */
 void b200_detach(struct network *net);
 

@@ -12,7 +12,7 @@
  *      one call replaces one of the reference's forward_*_layer_gpu functions;
  *   2. a network object that mirrors the reference's parse_network_cfg /
  *      load_weights / network_predict for the layer types on this path;
- *   3. (separate header darknet_b200_attach.h) a shim that re-points the
+ *   3. (separate header b200_attach.h, implemented by darknet_b200/shim/b200_attach.c) a shim that re-points the
  *      forward_gpu function pointers of a real Darknet `network`.
  *
  * Each declaration cites the reference interface it stands in for, as
@@ -247,6 +247,12 @@ int dnb_parse_network_cfg_text(const char *cfg_text, int mode, int batch_overrid
  * builds every convolution's derived device tensors. */
 int dnb_load_weights(dnb_network *net, const char *weights_path);
 
+/* load_weights for a host that already holds the parameters in memory: the arrays the reference's
+ * load_convolutional_weights fills (src/parser.c:1164-1215) for convolution `layer`.  Once every convolution
+ * of the network has been given its parameters the network is ready to predict. */
+int dnb_network_set_conv_params(dnb_network *net, int layer, const float *weights, const float *biases,
+                                const float *scales, const float *rolling_mean, const float *rolling_variance);
+
 /* free_network (src/network.c:720-735). */
 void dnb_free_network(dnb_network *net);
 
@@ -290,6 +296,9 @@ const char *dnb_network_layer_kernel(const dnb_network *net, int layer);
  * (NCHW f32, batch*outputs floats): what reading l.output after
  * cuda_pull_array (src/cuda.c:160-165) gives in the reference. */
 int dnb_network_layer_output(dnb_network *net, int layer, float *host_out);
+/* The same into device memory of the caller (what l.output_gpu holds in the reference), asynchronously on
+ * `stream`: the hook an attach shim uses to hand results to layers the reference still runs. */
+int dnb_network_export_layer(dnb_network *net, int layer, float *device_nchw, void *stream);
 
 /* Host pointer to a [yolo] layer's output of the last predict (the reference
  * pulls it inside forward_yolo_layer_gpu, src/yolo_layer.c:360). */

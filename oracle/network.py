@@ -279,10 +279,15 @@ class ReferenceGpu(Reference):
         super().__init__()
         self.L.ref_attach_b200.argtypes = [C.c_void_p, C.c_int]
         self.L.ref_detach_b200.argtypes = [C.c_void_p]
+        self.L.ref_attach_network_b200.argtypes = [C.c_void_p, C.c_int]
 
     def attach(self, net, mode: int) -> int:
         """b200_attach: re-point forward_gpu of the covered layers at libdarknet_b200."""
         return self.L.ref_attach_b200(net, mode)
+
+    def attach_network(self, net, mode: int) -> int:
+        """b200_attach_network: the whole forward pass through the library's own network object."""
+        return self.L.ref_attach_network_b200(net, mode)
 
     def detach(self, net) -> None:
         self.L.ref_detach_b200(net)

@@ -56,6 +56,7 @@ float *ref_layer_output(void *h, int i)
 #include "b200_attach.h"
 /* The drop-in under test: re-point the network's forward_gpu pointers at libdarknet_b200. */
 int ref_attach_b200(void *h, int mode) { return b200_attach((network *)h, mode); }
+int ref_attach_network_b200(void *h, int mode) { return b200_attach_network((network *)h, mode); }
 void ref_detach_b200(void *h) { b200_detach((network *)h); }
 int ref_is_gpu_build(void) { return 1; }
 #else

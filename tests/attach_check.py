@@ -59,6 +59,16 @@ def main():
     ref.detach(net)
     back = ref.predict_all(net, x)
     res["detached_equals_stock"] = bool(all(np.array_equal(a, b) for a, b in zip(back, stock)))
+    # the whole-network form: only the [yolo] layers and the last layer are written to Darknet's buffers
+    res["whole_attached"] = ref.attach_network(net, mode)
+    whole = ref.predict_all(net, x)
+    watched = [i for i, k in enumerate(kinds) if k == "yolo" or i == len(kinds) - 1]
+    res["whole_vs_cpu"] = max(rel_to_max(whole[i], want[i]) for i in watched)
+    whole2 = ref.predict_all(net, x * 0.5)
+    res["whole_second_input_differs"] = bool(not np.array_equal(whole2[-1], whole[-1]))
+    ref.detach(net)
+    back = ref.predict_all(net, x)
+    res["whole_detached_equals_stock"] = bool(all(np.array_equal(a, b) for a, b in zip(back, stock)))
     print("ATTACH_RESULT " + json.dumps(res))
 
 

@@ -34,3 +34,8 @@ def test_attach_to_unmodified_darknet(name, mode):
     assert r["attached_vs_cpu"] < (1e-4 if mode == dn.MODE_FP32 else 1e-2)
     assert r["second_input_differs"]
     assert r["detached_equals_stock"]
+    # b200_attach_network: the whole forward pass behind the same network_predict
+    assert r["whole_attached"] == r["layers"]
+    assert r["whole_vs_cpu"] < (1e-4 if mode == dn.MODE_FP32 else 1e-2)
+    assert r["whole_second_input_differs"]
+    assert r["whole_detached_equals_stock"]

@@ -45,7 +45,7 @@ def test_attach_shim_exports_its_header():
     import ctypes
     text = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "b200_attach.h")).read(), flags=re.S)
     names = set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text))
-    assert names == {"b200_attach", "b200_detach"}
+    assert names == {"b200_attach", "b200_attach_network", "b200_detach"}
     src = open(os.path.join(ROOT, "darknet_b200", "shim", "b200_attach.c")).read()
     for n in names:
         assert re.search(r"^(int|void) %s\(" % n, src, flags=re.M), n
