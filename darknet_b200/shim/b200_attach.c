@@ -196,6 +196,13 @@ int b200_attach(network *net, int mode)
             ++count;
         }
     }
+    /* inference only from here to b200_detach: forward_network_gpu zero-fills every layer's delta before calling
+     * it (src/network.c:775-777), 30 GB per YOLOv3-608 batch of 64; with the pointers set aside it has nothing to clear */
+    a->saved_delta = calloc(net->n, sizeof *a->saved_delta);
+    for (int i = 0; i < net->n; ++i) {
+        a->saved_delta[i] = net->layers[i].delta_gpu;
+        net->layers[i].delta_gpu = NULL;
+    }
     pin_outputs(a, net);
     a->next = g_attached;
     g_attached = a;

@@ -22,7 +22,10 @@ struct network;
 /* mode: a dnb_mode (DNB_MODE_TF32, DNB_MODE_BF16 or DNB_MODE_FP32).  Returns the number of layers whose
  * forward_gpu now points into this library, or -1 with the reason in dnb_last_error().  On failure the
  * network is left as it was.  Layers it does not cover (convolutions with l.binary only, 1x1 with
- * stride > 1, reverse upsample, routes over inputs of unequal size) keep the reference's pointer. */
+ * stride > 1, reverse upsample, routes over inputs of unequal size) keep the reference's pointer.
+ * Attached networks are for inference: until b200_detach the layers' delta_gpu pointers are set aside (so that
+ * forward_network_gpu does not clear 30 GB of gradients per YOLOv3 batch, src/network.c:775-777) and the host
+ * arrays Darknet pulls results into are page-locked. */
 int b200_attach(struct network *net, int mode);
 
 /* The whole forward pass through this library's own network object (channels-last between layers, shortcut
