@@ -103,3 +103,30 @@ def test_yolov3_608_one_image_every_layer(tmp_path):
     out2 = net2.predict(x2).copy()
     out1 = net.predict(x).copy()
     assert np.array_equal(out2[1], out1[0])
+
+
+@pytest.mark.parametrize("name,gen,batch,seed", [
+    ("yolov3-tiny-416 batch 1 (the reference's own CPU-runnable case)", lambda b: synth.yolov3_tiny_cfg(batch=b, size=416), 1, 5),
+    ("resnet50-224 batch 2", lambda b: synth.resnet50_cfg(batch=b, size=224), 2, 6),
+])
+def test_other_benchmark_networks_at_full_resolution(name, gen, batch, seed, tmp_path):
+    cfg = gen(batch)
+    params = synth.seeded_params(cfg, seed)
+    x = synth.seeded_input(cfg, seed, "uniform")
+    wpath = str(tmp_path / "n.weights")
+    synth.write_weights(wpath, params)
+    want = orc.forward_network(cfg, params, x)
+    net = dn.Network(cfg, wpath, dn.MODE_TF32, text=True)
+    out = net.predict(x).copy()
+    worst, checked = 0.0, 0
+    for i, wnt in enumerate(want):
+        try:
+            got = net.layer_output(i)
+        except dn.DarknetB200Error:
+            continue
+        e = rel_to_max(got, wnt)
+        worst = max(worst, e)
+        checked += 1
+        assert e < TOL_TF32, f"{name}, layer {i}: rel error {e:.3g}"
+    assert rel_to_max(out.reshape(want[-1].shape), want[-1]) < TOL_TF32
+    print(f"{name}: {checked} layer outputs checked, worst rel error {worst:.3g}")
