@@ -423,6 +423,25 @@ def run_b200(args):
     peak = bf16_peak / (2.0 if args.mode == "tf32" else 1.0)
     big3 = np.array([bool(tc[i]) and sections[i][1].get("size") == "3" and shapes[i].c >= 64 for i in range(net.n)])
     big3_tflops = float(flops[big3].sum() / (mean_ms[big3].sum() / 1000.0) / 1e12) if big3.any() else None
+    # the other launches of the same kernel (1x1 layers, 3x3 layers with fewer than 64 input channels) are bound by
+    # HBM: algorithmic bytes = input + output of the layer in its storage type, the weights once, and the residual
+    # a fused [shortcut] reads, over the same event durations
+    es = 2.0 if args.mode == "bf16" else 4.0
+    small = np.array([bool(tc[i]) and not big3[i] for i in range(net.n)])
+    mem_bytes = 0.0
+    for i in np.nonzero(small)[0]:
+        c, h, w = net.layer_shape(int(i))
+        stride = int(sections[i][1].get("stride", 1))
+        sh = shapes[int(i)]
+        mem_bytes += es * per_gpu * (sh.c * (h * stride) * (w * stride) + sh.n * h * w) + es * sh.n * sh.c * sh.size * sh.size
+        if i + 1 < net.n and kinds[i + 1] == "shortcut" and mean_ms[i + 1] < 0.01:   # fused: its add is read by this launch
+            mem_bytes += es * per_gpu * sh.n * h * w
+    small_ms = float(mean_ms[small].sum())
+    hbm_part = None
+    if small.any() and small_ms > 0:
+        gbs = mem_bytes / (small_ms / 1000.0) / 1e9
+        hbm_part = {"launches_per_step": int(small.sum()), "ms_per_step": small_ms, "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"], "what": "1x1 layers and 3x3 layers with fewer than 64 input channels: HBM-bound launches of the same kernel"}
     roofline = {"kernel": "conv_tc_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak,
                 "traffic": (lambda t: None if t is None else t[0] * per_gpu + t[1])(NCU_DRAM_TRAFFIC.get((args.workload, args.mode, args.size))),
@@ -431,7 +450,9 @@ def run_b200(args):
                 "share_of_step": tc_ms / float(mean_ms.sum()),
                 "peak_source": f"{peaks['source']}: cuBLAS bf16 {'burst' if alone else 'sustained'} {bf16_peak} TFLOP/s"
                                + (" / 2 (TF32 runs at half the BF16 tensor rate)" if args.mode == "tf32" else ""),
-                "conv3x3_c64plus_tflops": big3_tflops}
+                "conv3x3_c64plus_tflops": big3_tflops,
+                "conv3x3_c64plus_frac": (big3_tflops / peak) if big3_tflops else None,
+                "hbm_bound_launches": hbm_part}
 
     if args.layers:
         with open(args.layers, "w") as f:
