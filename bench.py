@@ -360,6 +360,22 @@ def run_b200(args):
     total_images = per_gpu * world if args.scaling == "weak" else args.batch
     value = total_images / (ms_step / 1000.0)
 
+    # ---- the same forward replayed as one CUDA graph (no per-layer events): what a caller gets from
+    # dnb_network_enable_graph; matters at small batches, where the launches outweigh the kernels
+    gstream = torch.cuda.Stream()
+    net.enable_graph(True)
+    for _ in range(3):                                   # eager, capture, first replay
+        net.forward(x_dev, stream=gstream.cuda_stream)
+    gstream.synchronize()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record(gstream)
+    for _ in range(args.steps):
+        net.forward(x_dev, stream=gstream.cuda_stream)
+    g1.record(gstream)
+    gstream.synchronize()
+    graph_ms_step = max_over_ranks(g0.elapsed_time(g1), "cuda") / args.steps
+    net.enable_graph(False)
+
     # ---- end to end with HOST buffers.  Every step uploads its own images from pinned host memory and
     # its results are read on the host.  Two ways of calling: the blocking network_predict, and the same
     # split into submit/collect with two steps in flight (a caller streaming batches), where the copies of
@@ -493,6 +509,8 @@ def run_b200(args):
             "e2e": {"value": total_images / (e2e_ms_step / 1000.0), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms_step, "timer": "host wall clock around K submit/collect steps, two in flight",
                     "blocking_predict": {"value": total_images / (sync_ms_step / 1000.0), "ms_per_step": sync_ms_step}},
+            "graph_replay": {"value": total_images / (graph_ms_step / 1000.0), "unit": UNIT, "ms_per_step": graph_ms_step,
+                             "what": "the device-resident forward as one CUDA graph launch per step (dnb_network_enable_graph)"},
             "gpu_launches": net.launches * args.steps,
             "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "reference_gpu": ref_gpu}
     print(json.dumps(line), flush=True)

@@ -78,6 +78,7 @@ SIGNATURES = {
     "dnb_network_predict": (_I, [_P, _P, C.POINTER(C.POINTER(_F))]),
     "dnb_network_set_conv_params": (_I, [_P, _I, _P, _P, _P, _P, _P]),
     "dnb_network_export_layer": (_I, [_P, _I, _P, _P]),
+    "dnb_network_enable_graph": (_I, [_P, _I]),
     "dnb_network_submit": (_I, [_P, _P]),
     "dnb_network_collect": (_I, [_P, C.POINTER(C.POINTER(_F))]),
     "dnb_network_forward": (_I, [_P, _P, _P]),

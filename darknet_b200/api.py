@@ -188,6 +188,10 @@ class Network:
         check(lib().dnb_network_collect(self.handle, C.byref(out)))
         return np.ctypeslib.as_array(out, shape=(self.batch, self.outputs))
 
+    def enable_graph(self, on: bool = True) -> None:
+        """Replay forward() as a CUDA graph from the third call with the same tensor and (non-default) stream."""
+        check(lib().dnb_network_enable_graph(self.handle, int(on)))
+
     def forward(self, x_dev, stream=None):
         """Device-resident forward: x_dev is a CUDA float32 tensor [batch, c, h, w]."""
         assert x_dev.is_cuda and x_dev.is_contiguous() and x_dev.numel() == self.batch * self.inputs

@@ -135,6 +135,13 @@ struct dnb_network {
     int device = 0;
     bool weights_loaded = false;
     int convs_with_params = 0;
+    // CUDA-graph replay of the device-resident forward (dnb_network_enable_graph): one instantiated graph per
+    // (input pointer, stream) seen last; eager_runs counts forwards with that pair since it changed
+    bool graph_enabled = false;
+    cudaGraphExec_t graph_exec = nullptr;
+    const float *graph_input = nullptr;
+    cudaStream_t graph_stream = nullptr;
+    int eager_runs = 0;
     std::vector<cudaEvent_t> events;
 };
 
@@ -375,6 +382,7 @@ extern "C" void dnb_free_network(dnb_network *net)
     cudaFree(net->input_dev); cudaFree(net->input_nhwc.data); cudaFree(net->out_dev_nchw); cudaFree(net->export_dev);
     if (net->out_host) cudaFreeHost(net->out_host);
     if (net->status_host) cudaFreeHost(net->status_host);
+    if (net->graph_exec) cudaGraphExecDestroy(net->graph_exec);
     cudaFree(net->status_dev);
     for (cudaEvent_t e : net->events) cudaEventDestroy(e);
     for (Layer &L : net->layers) if (L.done) cudaEventDestroy(L.done);
@@ -506,14 +514,71 @@ static int forward_layer(dnb_network *net, int i, const float *device_input, cud
     return DNB_OK;
 }
 
+static int forward_eager(dnb_network *net, const float *device_input, cudaStream_t s)
+{
+    DNB_TRY(prepare_input(net, device_input, s));
+    for (int i = 0; i < (int)net->layers.size(); ++i) DNB_TRY(forward_layer(net, i, device_input, s));
+    return DNB_OK;
+}
+
+static void drop_graph(dnb_network *net)
+{
+    if (net->graph_exec) cudaGraphExecDestroy(net->graph_exec);
+    net->graph_exec = nullptr;
+    net->graph_input = nullptr;
+    net->graph_stream = nullptr;
+    net->eager_runs = 0;
+}
+
+extern "C" int dnb_network_enable_graph(dnb_network *net, int on)
+{
+    if (!net) DNB_FAIL(DNB_EINVAL, "enable_graph: null network");
+    net->graph_enabled = on != 0;
+    if (!on) drop_graph(net);
+    return DNB_OK;
+}
+
 extern "C" int dnb_network_forward(dnb_network *net, const float *device_input, void *stream)
 {
     if (!net || !device_input) DNB_FAIL(DNB_EINVAL, "network_forward: null argument");
     if (!net->weights_loaded) DNB_FAIL(DNB_EINVAL, "network_forward: load_weights has not been called");
     if (net->submitted != net->collected) DNB_FAIL(DNB_EINVAL, "network_forward: a submitted step is still in flight (the layers' outputs are shared); collect it first");
     cudaStream_t s = (cudaStream_t)stream;  // NULL is the legacy default stream, as everywhere in CUDA
-    DNB_TRY(prepare_input(net, device_input, s));
-    for (int i = 0; i < (int)net->layers.size(); ++i) DNB_TRY(forward_layer(net, i, device_input, s));
+    if (!net->graph_enabled || !s) return forward_eager(net, device_input, s);   // the legacy stream cannot be captured
+
+    // Graph replay: at small batches the 100-odd launches of a forward pass cost more than its kernels.  The
+    // first forward with a given (input, stream) runs eagerly (plans build their tensor maps and scratch then),
+    // the second is captured, every later one is a single cudaGraphLaunch.
+    if (net->graph_exec && net->graph_input == device_input && net->graph_stream == s) {
+        DNB_CUDA(cudaGraphLaunch(net->graph_exec, s));
+        return DNB_OK;
+    }
+    if (net->graph_input != device_input || net->graph_stream != s) {
+        drop_graph(net);
+        net->graph_input = device_input;
+        net->graph_stream = s;
+    }
+    if (net->eager_runs++ == 0) return forward_eager(net, device_input, s);
+    cudaGraph_t graph = nullptr;
+    DNB_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    const int rc = forward_eager(net, device_input, s);
+    const cudaError_t ce = cudaStreamEndCapture(s, &graph);
+    if (rc != DNB_OK || ce != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        net->graph_enabled = false;          // something on the path cannot be captured: stay eager from here on
+        drop_graph(net);
+        return forward_eager(net, device_input, s);
+    }
+    const cudaError_t ie = cudaGraphInstantiate(&net->graph_exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ie != cudaSuccess) {
+        cudaGetLastError();
+        net->graph_exec = nullptr;
+        net->graph_enabled = false;
+        return forward_eager(net, device_input, s);
+    }
+    DNB_CUDA(cudaGraphLaunch(net->graph_exec, s));
     return DNB_OK;
 }
 

@@ -282,6 +282,12 @@ int dnb_network_collect(dnb_network *net, float **output);
  * legacy default stream). */
 int dnb_network_forward(dnb_network *net, const float *device_input, void *stream);
 
+/* Replay dnb_network_forward as a CUDA graph: with `on`, the second call with the same input pointer and
+ * (non-NULL) stream is captured and every later one is one graph launch; a different pointer or stream
+ * starts over.  For small batches, where the launches of forward_network_gpu's loop (src/network.c:772-785)
+ * cost more than the kernels.  No counterpart in the reference. */
+int dnb_network_enable_graph(dnb_network *net, int on);
+
 /* Geometry queries (net->n, net->batch, net->inputs, net->outputs; layer
  * out_c/out_h/out_w/outputs and type as the section name, e.g. "convolutional"). */
 int dnb_network_num_layers(const dnb_network *net);

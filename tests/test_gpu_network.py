@@ -130,6 +130,43 @@ def test_network_submit_collect_equals_predict(name, tmp_path):
     assert not np.array_equal(want[0][0], want[1][0])
 
 
+@pytest.mark.parametrize("name", ["tiny64", "yolov3_64", "resnet50_32", "darknet19_xnor_32"])
+def test_network_graph_replay_equals_eager(name, tmp_path):
+    """dnb_network_enable_graph: the captured forward gives the bytes the eager one gives, reads the input
+    tensor's current contents on every replay, and is captured again for another tensor."""
+    cfg, pseed, iseed, dist = CASES[name]
+    params = synth.seeded_params(cfg, pseed)
+    net = build(cfg, params, tmp_path, dn.MODE_TF32)
+    x1 = synth.seeded_input(cfg, iseed, dist)
+    x2 = synth.seeded_input(cfg, iseed + 1, dist)
+    s = torch.cuda.Stream()
+    xd = torch.from_numpy(x1).cuda()
+    torch.cuda.synchronize()
+
+    def run(t):
+        net.forward(t, stream=s.cuda_stream)
+        s.synchronize()
+        return net.layer_output(net.n - 1).copy()
+
+    want1 = run(xd)                    # eager, graphs off
+    xd.copy_(torch.from_numpy(x2).cuda())
+    want2 = run(xd)
+    assert not np.array_equal(want1, want2)
+    net.enable_graph(True)
+    xd.copy_(torch.from_numpy(x1).cuda()); torch.cuda.synchronize()
+    for k in range(4):                 # eager, captured, replayed, replayed
+        assert np.array_equal(run(xd), want1), f"forward {k} with graphs on differs"
+    xd.copy_(torch.from_numpy(x2).cuda()); torch.cuda.synchronize()
+    assert np.array_equal(run(xd), want2)          # same pointer, new contents: the replay reads them
+    other = torch.from_numpy(x1).cuda()            # another pointer: eager again, then a new capture
+    torch.cuda.synchronize()
+    for k in range(3):
+        assert np.array_equal(run(other), want1)
+    net.enable_graph(False)
+    assert np.array_equal(run(xd), want2)
+    assert np.array_equal(net.predict(x1).reshape(want1.shape), want1)   # the host-buffer path is untouched
+
+
 def test_network_batch_override_and_errors(tmp_path):
     cfg = synth.yolov3_tiny_cfg(batch=1, size=64)
     params = synth.seeded_params(cfg, 1)
