@@ -46,38 +46,47 @@ conv_xnor_kernel(XnorArgs a)
 #pragma unroll
         for (int j = 0; j < 4; ++j) pop[i][j] = 0;
 
-    if (threadIdx.x < XT) valid_s[threadIdx.x] = 0;
+    // the block's 64 pixels are decoded once; the tap loop only adds offsets (-1: beyond the last pixel)
+    __shared__ int pb_s[XT], poh_s[XT], pow_s[XT];
+    if (threadIdx.x < XT) {
+        valid_s[threadIdx.x] = 0;
+        const long long pix = pix0 + threadIdx.x;
+        int b = -1, oh = 0, ow = 0;
+        if (pix < npix) {
+            ow = (int)(pix % g.out_w);
+            const long long t = pix / g.out_w;
+            oh = (int)(t % g.out_h);
+            b = (int)(t / g.out_h);
+        }
+        pb_s[threadIdx.x] = b; poh_s[threadIdx.x] = oh; pow_s[threadIdx.x] = ow;
+    }
 
     for (int tap = 0; tap < taps; ++tap) {
         const int kh = tap / g.size, kw = tap - kh * g.size;
         for (int w0 = 0; w0 < a.cwords; w0 += XW) {
             const int wn = min(XW, a.cwords - w0);
             __syncthreads();
-            // stage the input words of this tap: thread -> (pixel, word), words fastest for coalescing
-            for (int i = threadIdx.x; i < XT * XW; i += XTHREADS) {
-                const int p = i / XW, w = i % XW;
-                const long long pix = pix0 + p;
-                uint32_t v = 0, inside = 0;
-                if (pix < npix) {
-                    const int ow = (int)(pix % g.out_w);
-                    const long long t = pix / g.out_w;
-                    const int oh = (int)(t % g.out_h), b = (int)(t / g.out_h);
-                    const int ih = oh * g.stride + kh - g.pad, iw = ow * g.stride + kw - g.pad;
-                    if (ih >= 0 && ih < g.h && iw >= 0 && iw < g.w) {
-                        inside = 0xffffffffu;
-                        if (w < wn) v = __ldg(a.xbits + (((size_t)b * g.h + ih) * g.w + iw) * a.cwords + w0 + w);
-                    }
-                }
-                xs[w][p] = v;
-                if (w == 0) {
-                    mask_s[p] = inside;
-                    if (w0 == 0 && inside) valid_s[p] += 1;
-                }
+            if (threadIdx.x < XT) {   // is this tap inside the image for pixel p?
+                const int p = threadIdx.x;
+                const int ih = poh_s[p] * g.stride + kh - g.pad, iw = pow_s[p] * g.stride + kw - g.pad;
+                const bool inside = pb_s[p] >= 0 && ih >= 0 && ih < g.h && iw >= 0 && iw < g.w;
+                mask_s[p] = inside ? 0xffffffffu : 0u;
+                if (w0 == 0 && inside) valid_s[p] += 1;
             }
-            for (int i = threadIdx.x; i < XN * XW; i += XTHREADS) {
-                const int f = i / XW, w = i % XW;
+            // stage the wn input words of this tap for every pixel: (pixel, word) pairs, words fastest so that
+            // the loads of a warp are contiguous; layers with few words per pixel touch only those
+            for (int i = threadIdx.x; i < XT * wn; i += XTHREADS) {
+                const int p = i / wn, w = i - p * wn;
+                const int ih = poh_s[p] * g.stride + kh - g.pad, iw = pow_s[p] * g.stride + kw - g.pad;
+                uint32_t v = 0;
+                if (pb_s[p] >= 0 && ih >= 0 && ih < g.h && iw >= 0 && iw < g.w)
+                    v = __ldg(a.xbits + (((size_t)pb_s[p] * g.h + ih) * g.w + iw) * a.cwords + w0 + w);
+                xs[w][p] = v;
+            }
+            for (int i = threadIdx.x; i < XN * wn; i += XTHREADS) {
+                const int f = i / wn, w = i - f * wn;
                 const int n = n0 + f;
-                ws[w][f] = (n < g.n && w < wn) ? __ldg(a.wbits + ((size_t)n * taps + tap) * a.cwords + w0 + w) : 0u;
+                ws[w][f] = n < g.n ? __ldg(a.wbits + ((size_t)n * taps + tap) * a.cwords + w0 + w) : 0u;
             }
             __syncthreads();
             uint32_t m[4];
