@@ -64,6 +64,8 @@ def workload_cfg(name: str, batch: int, size: int) -> tuple[str, str, str]:
         return synth.single_conv_cfg(batch, 256, 52, 52, 512, 3), "conv3x3_256_512_52_images_per_s", "isolated 3x3 conv 256->512 at 52x52"
     if name == "conv1x1":
         return synth.single_conv_cfg(batch, 512, 52, 52, 256, 1), "conv1x1_512_256_52_images_per_s", "isolated 1x1 conv 512->256 at 52x52"
+    if name == "memlayers":   # maxpool / upsample / shortcut / route at the shapes of YOLOv3's 152x152 stage
+        return synth.memory_layers_cfg(batch, 128, size or 152), "memory_layers_152_images_per_s", "maxpool, upsample, shortcut, route chained (128 channels, 152x152)"
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -77,7 +79,7 @@ def parse_args():
     ap.add_argument("--mode", default="tf32", choices=["tf32", "bf16"])
     ap.add_argument("--batch", type=int, default=64, help="images per GPU per step")
     ap.add_argument("--size", type=int, default=0, help="input width = height (default: 608 yolov3, 416 tiny, 224 classifiers)")
-    ap.add_argument("--workload", default="yolov3", choices=["yolov3", "yolov3-tiny", "resnet50", "darknet19-xnor", "conv3x3", "conv1x1"])
+    ap.add_argument("--workload", default="yolov3", choices=["yolov3", "yolov3-tiny", "resnet50", "darknet19-xnor", "conv3x3", "conv1x1", "memlayers"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: --batch images on every GPU; strong: --batch images split over the GPUs")
     ap.add_argument("--cpu-sample", type=int, default=4, help="images of the CPU-baseline sample (0 = skip)")
@@ -432,7 +434,7 @@ def run_b200(args):
     tc_ms = float(mean_ms[tc].sum())
     tc_flops = float(flops[tc].sum())
     peaks = load_peaks()
-    achieved = tc_flops / (tc_ms / 1000.0) / 1e12
+    achieved = tc_flops / (tc_ms / 1000.0) / 1e12 if tc_ms > 0 else 0.0
     # a kernel timed alone is held against the burst figure, one timed inside a long step against the sustained one
     alone = args.workload.startswith("conv")
     bf16_peak = peaks["bf16_tflops"] if alone else peaks["bf16_sustained"]
@@ -469,6 +471,26 @@ def run_b200(args):
                 "conv3x3_c64plus_tflops": big3_tflops,
                 "conv3x3_c64plus_frac": (big3_tflops / peak) if big3_tflops else None,
                 "hbm_bound_launches": hbm_part}
+
+    if not tc.any():
+        # a network of memory-bound layers only: algorithmic bytes per layer (4*(in+out) for maxpool and upsample,
+        # 12 B per element for shortcut, 8 B per element for route) over the event time, against the HBM copy rate
+        es_m = 2.0 if args.mode == "bf16" else 4.0
+        total_b, per_layer = 0.0, []
+        net_opt = synth.parse_cfg(cfg)[0][1]
+        prev = (int(net_opt["channels"]), int(net_opt["height"]), int(net_opt["width"]))
+        for i in range(net.n):
+            c, h, w = net.layer_shape(i)
+            out_e = per_gpu * c * h * w
+            in_e = per_gpu * prev[0] * prev[1] * prev[2]
+            b = {"maxpool": es_m * (in_e + out_e), "upsample": es_m * (in_e + out_e), "shortcut": 3 * es_m * out_e, "route": 2 * es_m * out_e}.get(kinds[i], 0.0)
+            per_layer.append({"layer": i, "kind": kinds[i], "GB": b / 1e9, "ms": float(mean_ms[i]), "GBps": b / (mean_ms[i] / 1000.0) / 1e9 if mean_ms[i] > 0 else None})
+            total_b += b
+            prev = (c, h, w)
+        gbs = total_b / (float(mean_ms.sum()) / 1000.0) / 1e9
+        roofline = {"kernel": "maxpool / upsample / shortcut / route kernels", "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"], "traffic": None, "per_layer": per_layer,
+                    "peak_source": f"{peaks['source']}: STREAM-style copy"}
 
     if args.layers:
         with open(args.layers, "w") as f:
@@ -521,7 +543,7 @@ def run_b200(args):
 def main():
     args = parse_args()
     if not args.size:
-        args.size = {"yolov3": 608, "yolov3-tiny": 416}.get(args.workload, 224)
+        args.size = {"yolov3": 608, "yolov3-tiny": 416, "memlayers": 152}.get(args.workload, 224)
     if args.impl == "reference":
         run_reference(args)
     elif args.impl == "reference-gpu":

@@ -155,20 +155,42 @@ int launch_conv_xnor(const XnorArgs &a, cudaStream_t s)
 }
 
 // ------------------------------------------------------------------ sign-bit packing
-// NHWC: one warp per (pixel, word): lane = channel, one ballot.
+// NHWC: eight lanes per (pixel, word), four channels (one 16-byte or 8-byte load) per lane, so a warp packs four
+// words per iteration from 512 contiguous bytes; the eight nibbles are OR-ed together with three shuffles.
+// Padding channels hold zeros (the channels-last contract), so they pack as "not positive" by themselves.
 template <typename T>
-__global__ void pack_bits_nhwc_kernel(const T *__restrict__ x, uint32_t *__restrict__ bits, size_t npix, int C, int Cp, int cwords)
+__global__ void __launch_bounds__(256)
+pack_bits_nhwc_kernel(const T *__restrict__ x, uint32_t *__restrict__ bits, size_t npix, int C, int Cp, int cwords)
 {
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, sub = lane >> 3, q = lane & 7;
     const size_t warp0 = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
     const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
     const size_t total = npix * cwords;
-    for (size_t i = warp0; i < total; i += nwarps) {
-        const size_t p = i / cwords;
-        const int w = (int)(i % cwords), c = w * 32 + lane;
-        const float v = c < C ? to_float<T>(x[p * Cp + c]) : 0.f;
-        const uint32_t word = __ballot_sync(0xffffffffu, v > 0.f);
-        if (lane == 0) bits[i] = word;
+    (void)C;
+    for (size_t base = warp0 * 4; base < total; base += nwarps * 4) {
+        const size_t item = base + sub;
+        uint32_t nib = 0;
+        if (item < total) {
+            const size_t p = item / cwords;
+            const int w = (int)(item - p * cwords), c0 = w * 32 + q * 4;
+            if (c0 < Cp) {   // the pitch is a multiple of 8: a 4-channel piece is inside it or outside
+                float v0, v1, v2, v3;
+                if (sizeof(T) == 4) {
+                    const float4 f = __ldg(reinterpret_cast<const float4 *>(x + p * Cp + c0));
+                    v0 = f.x; v1 = f.y; v2 = f.z; v3 = f.w;
+                } else {
+                    const uint2 u = __ldg(reinterpret_cast<const uint2 *>(x + p * Cp + c0));
+                    v0 = __uint_as_float(u.x << 16); v1 = __uint_as_float(u.x & 0xffff0000u);
+                    v2 = __uint_as_float(u.y << 16); v3 = __uint_as_float(u.y & 0xffff0000u);
+                }
+                nib = (v0 > 0.f ? 1u : 0u) | (v1 > 0.f ? 2u : 0u) | (v2 > 0.f ? 4u : 0u) | (v3 > 0.f ? 8u : 0u);
+            }
+        }
+        uint32_t word = nib << (4 * q);
+        word |= __shfl_xor_sync(0xffffffffu, word, 1);
+        word |= __shfl_xor_sync(0xffffffffu, word, 2);
+        word |= __shfl_xor_sync(0xffffffffu, word, 4);
+        if (q == 0 && item < total) bits[item] = word;
     }
 }
 
@@ -193,7 +215,7 @@ int launch_pack_sign_bits(const dnb_tensor *x, uint32_t *bits, int cwords, cudaS
 {
     const size_t npix = (size_t)x->n * x->h * x->w;
     if (x->layout == DNB_NHWC) {
-        size_t warps = npix * cwords;
+        size_t warps = (npix * cwords + 3) / 4;   // four words per warp iteration
         size_t blocks = (warps * 32 + 255) / 256;
         size_t cap = (size_t)sm_count() * 8;
         int grid = (int)(blocks < cap ? (blocks ? blocks : 1) : cap);

@@ -18,6 +18,14 @@ static inline int grid_for(size_t work_items, int threads)
     return (int)blocks;
 }
 
+// Grid of the row-wise kernels: one block per output row, at most 8 resident blocks of 256 threads per SM.
+static inline int row_grid(int batch, int rows_per_image)
+{
+    const long long rows = (long long)batch * rows_per_image;
+    const long long cap = (long long)sm_count() * 8;
+    return (int)(rows < cap ? (rows > 0 ? rows : 1) : cap);
+}
+
 // 16-byte vector of T with elementwise helpers.
 template <typename T> struct Vec16 {
     static constexpr int N = 16 / sizeof(T);
@@ -27,37 +35,70 @@ template <typename T> struct Vec16 {
 // ------------------------------------------------------------------ maxpool
 // Darknet semantics (src/maxpool_layer.c:79-114): window origin -padding/2,
 // taps outside the image skipped, -FLT_MAX if none is inside.
-template <typename T>
-__global__ void maxpool_nhwc_kernel(const T *__restrict__ x, T *__restrict__ y, int B, int H, int W, int cvecs,
-                                    int OH, int OW, int size, int stride, int off)
+// One output row (b, oh) per block iteration, threads along the row's (ow, channel vector) pairs: the only
+// per-element index arithmetic is one 32-bit division (64-bit divisions per 16-byte vector made this kernel
+// instruction-bound at 58 % of the HBM rate).
+// SIZE: the window's extent at compile time (2, 3) so that all of a window's loads are in flight together (a
+// rolled loop issues load, compare, load, compare, ... and each thread then has one load in flight), or 0 for
+// any size at run time.
+template <typename T, int SIZE>
+__global__ void __launch_bounds__(256)
+maxpool_nhwc_kernel(const T *__restrict__ x, T *__restrict__ y, int B, int H, int W, int cvecs,
+                    int OH, int OW, int size_rt, int stride, int off)
 {
     using V = Vec16<T>;
-    const size_t total = (size_t)B * OH * OW * cvecs;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        int cv = (int)(i % cvecs);
-        size_t p = i / cvecs;
-        int ow = (int)(p % OW); p /= OW;
-        int oh = (int)(p % OH);
-        int b = (int)(p / OH);
-        float best[V::N];
+    const int size = SIZE > 0 ? SIZE : size_rt;
+    const int rows = B * OH, row_vecs = OW * cvecs;
+    const uint4 *xin = reinterpret_cast<const uint4 *>(x);
+    uint4 *yout = reinterpret_cast<uint4 *>(y);
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int b = row / OH, oh = row - b * OH;
+        const int ih0 = off + oh * stride;
+        const size_t in_img = (size_t)b * H * W * cvecs;
+        uint4 *yrow = yout + (size_t)row * row_vecs;
+        for (int j = threadIdx.x; j < row_vecs; j += blockDim.x) {
+            const int ow = j / cvecs, cv = j - ow * cvecs;
+            const int iw0 = off + ow * stride;
+            float best[V::N];
 #pragma unroll
-        for (int k = 0; k < V::N; ++k) best[k] = -FLT_MAX;
-        for (int n = 0; n < size; ++n) {
-            int ih = off + oh * stride + n;
-            if (ih < 0 || ih >= H) continue;
-            for (int m = 0; m < size; ++m) {
-                int iw = off + ow * stride + m;
-                if (iw < 0 || iw >= W) continue;
-                V v;
-                v.raw = __ldg(reinterpret_cast<const uint4 *>(x) + (((size_t)b * H + ih) * W + iw) * cvecs + cv);
+            for (int k = 0; k < V::N; ++k) best[k] = -FLT_MAX;
+            if (SIZE > 0) {
+                constexpr int WIN = SIZE > 0 ? SIZE * SIZE : 1;
+                V v[WIN];
+                bool in[WIN];
 #pragma unroll
-                for (int k = 0; k < V::N; ++k) best[k] = fmaxf(best[k], to_float<T>(v.v[k]));
+                for (int n = 0; n < SIZE; ++n)
+#pragma unroll
+                    for (int m = 0; m < SIZE; ++m) {
+                        const int ih = ih0 + n, iw = iw0 + m;
+                        in[n * SIZE + m] = ih >= 0 && ih < H && iw >= 0 && iw < W;
+                        if (in[n * SIZE + m]) v[n * SIZE + m].raw = __ldg(xin + in_img + ((size_t)ih * W + iw) * cvecs + cv);
+                    }
+#pragma unroll
+                for (int t = 0; t < WIN; ++t)
+                    if (in[t]) {
+#pragma unroll
+                        for (int k = 0; k < V::N; ++k) best[k] = fmaxf(best[k], to_float<T>(v[t].v[k]));
+                    }
+            } else
+            for (int n = 0; n < size; ++n) {
+                const int ih = ih0 + n;
+                if (ih < 0 || ih >= H) continue;
+                const uint4 *xrow = xin + in_img + (size_t)ih * W * cvecs + cv;
+                for (int m = 0; m < size; ++m) {
+                    const int iw = iw0 + m;
+                    if (iw < 0 || iw >= W) continue;
+                    V v;
+                    v.raw = __ldg(xrow + iw * cvecs);
+#pragma unroll
+                    for (int k = 0; k < V::N; ++k) best[k] = fmaxf(best[k], to_float<T>(v.v[k]));
+                }
             }
-        }
-        V o;
+            V o;
 #pragma unroll
-        for (int k = 0; k < V::N; ++k) o.v[k] = from_float<T>(best[k]);
-        reinterpret_cast<uint4 *>(y)[i] = o.raw;
+            for (int k = 0; k < V::N; ++k) o.v[k] = from_float<T>(best[k]);
+            yrow[j] = o.raw;
+        }
     }
 }
 
@@ -95,47 +136,55 @@ int launch_maxpool(const dnb_tensor *x, const dnb_tensor *y, int size, int strid
         DNB_FAIL(DNB_EINVAL, "maxpool: output is %dx%dx%dx%d, expected %dx%dx%dx%d", y->n, y->c, y->h, y->w, x->n, x->c, oh, ow);
     if (x->layout != y->layout || x->dtype != y->dtype) DNB_FAIL(DNB_EINVAL, "maxpool: input and output differ in layout or dtype");
     const int off = -(padding / 2);
+#define MAXPOOL_LAUNCH(T, ...)                                                                          \
+    do {                                                                                                \
+        if (size == 2) maxpool_nhwc_kernel<T, 2><<<row_grid(y->n, oh), 256, 0, s>>>(__VA_ARGS__);       \
+        else if (size == 3) maxpool_nhwc_kernel<T, 3><<<row_grid(y->n, oh), 256, 0, s>>>(__VA_ARGS__);  \
+        else maxpool_nhwc_kernel<T, 0><<<row_grid(y->n, oh), 256, 0, s>>>(__VA_ARGS__);                 \
+    } while (0)
     if (x->layout == DNB_NHWC) {
         if (x->cpitch != y->cpitch) DNB_FAIL(DNB_EINVAL, "maxpool: cpitch differs (%d vs %d)", x->cpitch, y->cpitch);
         if (x->dtype == DNB_F32) {
             int cv = x->cpitch / 4;
-            size_t total = (size_t)y->n * oh * ow * cv;
-            maxpool_nhwc_kernel<float><<<grid_for(total, 128), 128, 0, s>>>((const float *)x->data, (float *)y->data, x->n, x->h, x->w, cv, oh, ow, size, stride, off);
+            MAXPOOL_LAUNCH(float, (const float *)x->data, (float *)y->data, x->n, x->h, x->w, cv, oh, ow, size, stride, off);
         } else {
             int cv = x->cpitch / 8;
-            size_t total = (size_t)y->n * oh * ow * cv;
-            maxpool_nhwc_kernel<__nv_bfloat16><<<grid_for(total, 128), 128, 0, s>>>((const __nv_bfloat16 *)x->data, (__nv_bfloat16 *)y->data, x->n, x->h, x->w, cv, oh, ow, size, stride, off);
+            MAXPOOL_LAUNCH(__nv_bfloat16, (const __nv_bfloat16 *)x->data, (__nv_bfloat16 *)y->data, x->n, x->h, x->w, cv, oh, ow, size, stride, off);
         }
     } else {
         if (x->dtype != DNB_F32) DNB_FAIL(DNB_EINVAL, "maxpool: NCHW tensors must be f32");
         size_t total = (size_t)y->n * y->c * oh * ow;
         maxpool_nchw_kernel<<<grid_for(total, 128), 128, 0, s>>>((const float *)x->data, (float *)y->data, x->n * x->c, x->h, x->w, oh, ow, size, stride, off);
     }
+#undef MAXPOOL_LAUNCH
     DNB_LAUNCH_CHECK("maxpool");
     return DNB_OK;
 }
 
 // ------------------------------------------------------------------ upsample
+// One output row (b, oh) per block iteration; see maxpool_nhwc_kernel.
 template <typename T>
-__global__ void upsample_nhwc_kernel(const T *__restrict__ x, T *__restrict__ y, int B, int H, int W, int cvecs,
-                                     int stride, float scale)
+__global__ void __launch_bounds__(256)
+upsample_nhwc_kernel(const T *__restrict__ x, T *__restrict__ y, int B, int H, int W, int cvecs, int stride, float scale)
 {
     using V = Vec16<T>;
     const int OH = H * stride, OW = W * stride;
-    const size_t total = (size_t)B * OH * OW * cvecs;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        int cv = (int)(i % cvecs);
-        size_t p = i / cvecs;
-        int ow = (int)(p % OW); p /= OW;
-        int oh = (int)(p % OH);
-        int b = (int)(p / OH);
-        V v;
-        v.raw = __ldg(reinterpret_cast<const uint4 *>(x) + (((size_t)b * H + oh / stride) * W + ow / stride) * cvecs + cv);
-        if (scale != 1.f) {
+    const int rows = B * OH, row_vecs = OW * cvecs;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int b = row / OH, oh = row - b * OH;
+        const uint4 *xrow = reinterpret_cast<const uint4 *>(x) + ((size_t)b * H + oh / stride) * W * cvecs;
+        uint4 *yrow = reinterpret_cast<uint4 *>(y) + (size_t)row * row_vecs;
+#pragma unroll 4
+        for (int j = threadIdx.x; j < row_vecs; j += blockDim.x) {
+            const int ow = j / cvecs, cv = j - ow * cvecs;
+            V v;
+            v.raw = __ldg(xrow + (ow / stride) * cvecs + cv);
+            if (scale != 1.f) {
 #pragma unroll
-            for (int k = 0; k < V::N; ++k) v.v[k] = from_float<T>(scale * to_float<T>(v.v[k]));
+                for (int k = 0; k < V::N; ++k) v.v[k] = from_float<T>(scale * to_float<T>(v.v[k]));
+            }
+            yrow[j] = v.raw;
         }
-        reinterpret_cast<uint4 *>(y)[i] = v.raw;
     }
 }
 
@@ -165,12 +214,10 @@ int launch_upsample(const dnb_tensor *x, const dnb_tensor *y, int stride, float 
         if (x->cpitch != y->cpitch) DNB_FAIL(DNB_EINVAL, "upsample: cpitch differs");
         if (x->dtype == DNB_F32) {
             int cv = x->cpitch / 4;
-            size_t total = (size_t)y->n * y->h * y->w * cv;
-            upsample_nhwc_kernel<float><<<grid_for(total, 128), 128, 0, s>>>((const float *)x->data, (float *)y->data, x->n, x->h, x->w, cv, stride, scale);
+            upsample_nhwc_kernel<float><<<row_grid(y->n, y->h), 256, 0, s>>>((const float *)x->data, (float *)y->data, x->n, x->h, x->w, cv, stride, scale);
         } else {
             int cv = x->cpitch / 8;
-            size_t total = (size_t)y->n * y->h * y->w * cv;
-            upsample_nhwc_kernel<__nv_bfloat16><<<grid_for(total, 128), 128, 0, s>>>((const __nv_bfloat16 *)x->data, (__nv_bfloat16 *)y->data, x->n, x->h, x->w, cv, stride, scale);
+            upsample_nhwc_kernel<__nv_bfloat16><<<row_grid(y->n, y->h), 256, 0, s>>>((const __nv_bfloat16 *)x->data, (__nv_bfloat16 *)y->data, x->n, x->h, x->w, cv, stride, scale);
         }
     } else {
         if (x->dtype != DNB_F32) DNB_FAIL(DNB_EINVAL, "upsample: NCHW tensors must be f32");

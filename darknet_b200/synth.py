@@ -154,6 +154,15 @@ def single_conv_cfg(batch: int, c: int, h: int, w: int, filters: int, size: int,
     return _net(batch, w, h, c) + _conv(filters, size, stride, bn, act, xnor, groups, pad)
 
 
+def memory_layers_cfg(batch: int = 64, c: int = 128, size: int = 152) -> str:
+    """The memory-bound layer types of the path chained into one network without a convolution: maxpool 2x2/2,
+    upsample x2, maxpool 2x2/1 (the padded form of yolov3-tiny), shortcut, route, maxpool; the shapes are
+    those of YOLOv3's 152x152 stage.  For measuring those kernels against the HBM copy rate."""
+    return (_net(batch, size, size, c) +
+            "[maxpool]\nsize=2\nstride=2\n\n[upsample]\nstride=2\n\n[maxpool]\nsize=2\nstride=1\n\n"
+            "[shortcut]\nfrom=-2\nactivation=linear\n\n[route]\nlayers=-1,-3\n\n[maxpool]\nsize=2\nstride=2\n\n")
+
+
 # --------------------------------------------------------------------------- parameters
 
 

@@ -167,6 +167,27 @@ def test_network_graph_replay_equals_eager(name, tmp_path):
     assert np.array_equal(net.predict(x1).reshape(want1.shape), want1)   # the host-buffer path is untouched
 
 
+@pytest.mark.parametrize("mode", [dn.MODE_FP32, dn.MODE_TF32, dn.MODE_BF16])
+def test_network_of_memory_layers_only(mode, tmp_path):
+    """A network without a convolution (maxpool, upsample, padded maxpool, shortcut, route, maxpool): the
+    channels-last copy of the input feeds a maxpool, every layer against the checker.  Copies and compares are
+    exact in f32 storage; BF16 storage rounds the input once."""
+    cfg = synth.memory_layers_cfg(batch=3, c=24, size=20)
+    x = synth.seeded_input(cfg, 9, "normal")
+    want = orc.forward_network(cfg, [], x)
+    net = build(cfg, [], tmp_path, mode)
+    out = net.predict(x).copy()
+    for i, w in enumerate(want):
+        got = net.layer_output(i)
+        if mode == dn.MODE_BF16:
+            assert rel_to_max(got, w) < 2e-2
+        elif mode == dn.MODE_TF32:
+            assert rel_to_max(got, w) < 1e-3     # the input copy is rounded to TF32 once
+        else:
+            assert np.array_equal(got, w), f"layer {i}"
+    assert out.shape == (3, net.outputs)
+
+
 def test_network_batch_override_and_errors(tmp_path):
     cfg = synth.yolov3_tiny_cfg(batch=1, size=64)
     params = synth.seeded_params(cfg, 1)
