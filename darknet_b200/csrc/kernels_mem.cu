@@ -281,6 +281,50 @@ __global__ void shortcut_general_kernel(const T *__restrict__ x, const T *__rest
     }
 }
 
+// General shapes, channels-last: one output row (b, h) per block iteration, threads along the row's (w, 16-byte
+// channel vector) pairs.  The add tensor contributes where the reference's loops reach (src/blas.c:68-92): channels
+// below minc, and pixels (h, w) that are multiples of `sample`, read from (h/sample*stride, w/sample*stride).
+template <typename T>
+__global__ void __launch_bounds__(256)
+shortcut_rows_nhwc_kernel(const T *__restrict__ x, const T *__restrict__ add, T *__restrict__ y, ShortcutGeom g,
+                          int cpitch, int add_cpitch, int add_h, int add_w, float alpha, float beta, int act)
+{
+    using V = Vec16<T>;
+    const int cvecs = cpitch / V::N, rows = g.B * g.H2, row_vecs = g.W2 * cvecs;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int b = row / g.H2, h = row - b * g.H2;
+        const bool h_hit = h % g.sample == 0 && h / g.sample < g.minh;
+        const T *arow = add + ((size_t)b * add_h + (size_t)(h / g.sample) * g.stride) * add_w * add_cpitch;
+        const uint4 *xrow = reinterpret_cast<const uint4 *>(x) + (size_t)row * row_vecs;
+        uint4 *yrow = reinterpret_cast<uint4 *>(y) + (size_t)row * row_vecs;
+        for (int j = threadIdx.x; j < row_vecs; j += blockDim.x) {
+            const int w = j / cvecs, c0 = (j - w * cvecs) * V::N;
+            V a, o;
+            a.raw = __ldg(xrow + j);
+            const bool hit = h_hit && c0 < g.minc && w % g.sample == 0 && w / g.sample < g.minw;
+            float r[V::N];
+#pragma unroll
+            for (int k = 0; k < V::N; ++k) r[k] = to_float<T>(a.v[k]);
+            if (hit) {
+                const T *ap = arow + (size_t)(w / g.sample) * g.stride * add_cpitch + c0;
+                if (c0 + V::N <= g.minc) {          // the whole vector lies inside both tensors (pitches are multiples of 8)
+                    V d;
+                    d.raw = __ldg(reinterpret_cast<const uint4 *>(ap));
+#pragma unroll
+                    for (int k = 0; k < V::N; ++k) r[k] = alpha * r[k] + beta * to_float<T>(d.v[k]);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < V::N; ++k)
+                        if (c0 + k < g.minc) r[k] = alpha * r[k] + beta * to_float<T>(ap[k]);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < V::N; ++k) o.v[k] = from_float<T>(c0 + k < g.C2 ? activate(r[k], act) : 0.f);   // padding channels stay zero
+            yrow[j] = o.raw;
+        }
+    }
+}
+
 int launch_shortcut(const dnb_tensor *x, const dnb_tensor *add, const dnb_tensor *y, float alpha, float beta,
                     int activation, cudaStream_t s)
 {
@@ -330,6 +374,17 @@ int launch_shortcut(const dnb_tensor *x, const dnb_tensor *add, const dnb_tensor
         g.inner_is_c = 0;
         g.xs_w = 1; g.xs_h = x->w; g.xs_c = (long long)x->h * x->w; g.xs_b = (long long)x->c * g.xs_c;
         g.as_w = 1; g.as_h = add->w; g.as_c = (long long)add->h * add->w; g.as_b = (long long)add->c * g.as_c;
+    }
+    if (x->layout == DNB_NHWC && (long long)g.B * g.H2 < (1LL << 31) && (long long)g.W2 * x->cpitch < (1LL << 31)) {
+        if (x->dtype == DNB_F32)
+            shortcut_rows_nhwc_kernel<float><<<row_grid(g.B, g.H2), 256, 0, s>>>((const float *)x->data, (const float *)add->data, (float *)y->data, g,
+                                                                              x->cpitch, add->cpitch, add->h, add->w, alpha, beta, activation);
+        else
+            shortcut_rows_nhwc_kernel<__nv_bfloat16><<<row_grid(g.B, g.H2), 256, 0, s>>>((const __nv_bfloat16 *)x->data, (const __nv_bfloat16 *)add->data,
+                                                                                      (__nv_bfloat16 *)y->data, g, x->cpitch, add->cpitch, add->h, add->w,
+                                                                                      alpha, beta, activation);
+        DNB_LAUNCH_CHECK("shortcut");
+        return DNB_OK;
     }
     size_t total = (size_t)g.B * g.C2 * g.H2 * g.W2;
     if (x->dtype == DNB_F32)
