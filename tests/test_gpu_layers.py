@@ -267,6 +267,10 @@ STEM_CASES = {
     "gray_n32_logistic": dict(b=2, c=1, h=24, w=24, n=32, size=3, act="logistic"),
     "two_channels": dict(b=1, c=2, h=16, w=130, n=32, size=3),
     "many_tiles": dict(b=4, c=3, h=160, w=160, n=32, size=3, dist="uniform"),
+    "rgb7x7_s2_n64": dict(b=2, c=3, h=46, w=46, n=64, size=7, stride=2, dist="uniform"),
+    "rgb7x7_n16_ragged": dict(b=3, c=3, h=37, w=29, n=16, size=7, dist="uniform"),
+    "rgb5x5_n32_logistic": dict(b=2, c=3, h=24, w=40, n=32, size=5, act="logistic"),
+    "rgb7x7_many_tiles": dict(b=4, c=3, h=112, w=112, n=64, size=7, stride=2, dist="uniform"),
 }
 
 
