@@ -130,3 +130,24 @@ def test_other_benchmark_networks_at_full_resolution(name, gen, batch, seed, tmp
         assert e < TOL_TF32, f"{name}, layer {i}: rel error {e:.3g}"
     assert rel_to_max(out.reshape(want[-1].shape), want[-1]) < TOL_TF32
     print(f"{name}: {checked} layer outputs checked, worst rel error {worst:.3g}")
+
+
+@pytest.mark.parametrize("size", [320, 416])
+@pytest.mark.parametrize("mode,tol", [(dn.MODE_TF32, 1e-2), (dn.MODE_BF16, 6e-2)])
+def test_yolov3_other_input_sizes(size, mode, tol, tmp_path):
+    """The other customary YOLOv3 resolutions (10/20/40 and 13/26/52 maps instead of 19/38/76): pixel tiles,
+    batch folding and tile counts all differ from the benchmark's.  One image, the three heads against the checker
+    (BF16 end to end through 75 convolutions: 6e-2, as in test_gpu_network.py)."""
+    cfg = synth.yolov3_cfg(batch=1, size=size)
+    params = synth.seeded_params(cfg, 7)
+    x = synth.seeded_input(cfg, 7, "uniform")
+    wpath = str(tmp_path / "y.weights")
+    synth.write_weights(wpath, params)
+    want = orc.forward_network(cfg, params, x)
+    net = dn.Network(cfg, wpath, mode, text=True)
+    net.predict(x)
+    heads = [i for i in range(net.n) if net.layer_type(i) == "yolo"]
+    assert len(heads) == 3
+    for i in heads:
+        e = rel_to_max(net.yolo_output(i), want[i])
+        assert e < tol, f"size {size}, head {i}: rel error {e:.3g}"
