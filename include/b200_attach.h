@@ -9,6 +9,9 @@
  * device buffers (net.input_gpu, l.output_gpu: NCHW fp32).  Every other layer type keeps the
  * reference's kernel.  The file that implements this, darknet_b200/shim/b200_attach.c, is compiled inside
  * the Darknet tree (it includes darknet.h, whose struct layout depends on the build flags).
+ *
+ * Like Darknet's own network functions these calls are not thread-safe: attach, predict and detach a given
+ * network from one thread at a time (the registry of attached networks is a plain list).
  */
 #ifndef B200_ATTACH_H
 #define B200_ATTACH_H
