@@ -136,3 +136,43 @@ def test_weights_file_format(tmp_path):
     assert np.array_equal(body[:6], params[0].biases) and np.array_equal(body[6:12], params[0].scales)
     assert np.array_equal(body[24:n0], params[0].weights.reshape(-1))
     assert np.array_equal(body[n0:n0 + 3], params[1].biases)
+
+
+def test_bench_workloads_are_well_formed():
+    """Every workload bench.py can name parses, has the layer mix it advertises, and the byte / FLOP accounting
+    the roofline uses matches the published totals (YOLOv3-608: 140.69 GFLOP per image)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    kinds = {}
+    for name, size in [("yolov3", 608), ("yolov3-tiny", 416), ("resnet50", 224), ("darknet19-xnor", 224), ("conv3x3", 224),
+                       ("conv1x1", 224), ("memlayers", 152)]:
+        cfg, metric, desc = bench.workload_cfg(name, 2, size)
+        secs = synth.parse_cfg(cfg)
+        assert secs[0][0] == "net" and int(secs[0][1]["batch"]) == 2 and metric.endswith("images_per_s") and desc
+        kinds[name] = [k for k, _ in secs[1:]]
+    assert kinds["yolov3"].count("convolutional") == 75 and kinds["yolov3"].count("shortcut") == 23 and kinds["yolov3"].count("yolo") == 3
+    assert kinds["yolov3-tiny"].count("maxpool") == 6
+    assert kinds["memlayers"] == ["maxpool", "upsample", "maxpool", "shortcut", "route", "maxpool"]
+    assert kinds["conv3x3"] == ["convolutional"] and kinds["conv1x1"] == ["convolutional"]
+    # FLOPs as examples/darknet.c:87-88 counts them
+    cfg = synth.yolov3_cfg(1, 608)
+    h = w = 608
+    total, dims = 0.0, []
+    shapes = {s.index: s for s in synth.conv_shapes(cfg)}
+    for i, (k, o) in enumerate(synth.parse_cfg(cfg)[1:]):
+        if k == "convolutional":
+            st = int(o.get("stride", 1))
+            h, w = (h - 1) // st + 1, (w - 1) // st + 1
+            s_ = shapes[i]
+            total += 2.0 * s_.n * s_.size * s_.size * s_.c * h * w
+        elif k == "upsample":
+            h, w = h * 2, w * 2
+        elif k == "route":
+            ids = [int(t) for t in o["layers"].split(",")]
+            h, w = dims[ids[0] if ids[0] >= 0 else i + ids[0]]
+        dims.append((h, w))
+    assert abs(total - 140_691_900_416.0) < 1.0
+    peaks = bench.load_peaks()
+    assert peaks["hbm_gbs"] > 1000 and peaks["bf16_tflops"] >= peaks["bf16_sustained"] > 100
