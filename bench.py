@@ -75,7 +75,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-gpu"])
-    ap.add_argument("--ref-gpu-batch", type=int, default=8, help="images per network_predict call of the reference's own CUDA build (0: skip that row)")
+    ap.add_argument("--ref-gpu-batch", type=int, default=0,
+                    help="b200 arm: also time the reference's own CUDA build and the attach shim in a child process at this batch "
+                         "(0, the default: skip); --impl reference-gpu: images per network_predict call (default 8)")
     ap.add_argument("--mode", default="tf32", choices=["tf32", "bf16"])
     ap.add_argument("--batch", type=int, default=64, help="images per GPU per step")
     ap.add_argument("--size", type=int, default=0, help="input width = height (default: 608 yolov3, 416 tiny, 224 classifiers)")
@@ -266,7 +268,7 @@ def run_reference_gpu(args):
     if not orc.ReferenceGpu.available():
         print(json.dumps({"impl": "reference-gpu", "unavailable": "oracle/_ref/libdarknet_ref_gpu.so was not built (make -C oracle refgpu)"}), flush=True)
         return
-    batch = max(1, args.ref_gpu_batch)
+    batch = args.ref_gpu_batch if args.ref_gpu_batch > 0 else 8
     cfg, metric, desc = workload_cfg(args.workload, batch, args.size)
     d = tempfile.mkdtemp(prefix="dnb_refgpu_")
     write_net_files(d, cfg)
