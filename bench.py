@@ -3,6 +3,9 @@
 
     python bench.py --gpus N --steps K --warmup W            this library on N B200s
     python bench.py --impl reference --steps K --warmup W    the reference's CPU path on the host cores
+    python bench.py --impl reference-gpu [--ref-gpu-batch B] extra, never part of the default run: the reference's own CUDA
+                                                             build (recompiled for sm_100a) through its network_predict,
+                                                             stock and with this library attached (b200_attach[_network])
 
 One step = one forward of one batch of synthetic images (seeded U[0,1) input,
 seeded He-normal weights: no dataset or checkpoint is involved).  For N > 1 the
@@ -12,9 +15,10 @@ collective on the data path; ranks meet only at the barriers around the timed
 region, and the slowest rank's time is the job's time.
 
 Prints ONE JSON line (rank 0).  `value` is the whole job's images/s with inputs
-resident in HBM; `e2e` the same through network_predict with pinned HOST
-buffers (H2D of the batch and D2H of the three detection heads inside the timed
-region); `roofline` describes the tensor-core convolution kernel, timed with
+resident in HBM; `e2e` the same through the C ABI with pinned HOST buffers (H2D of
+the batch and D2H of the three detection heads inside the timed region, two steps
+in flight; `e2e.blocking_predict` is the blocking network_predict call);
+`graph_replay` the device-resident forward as one CUDA graph per step; `roofline` describes the tensor-core convolution kernel, timed with
 CUDA events between layers inside the timed region; `cpu_baseline` is the
 unmodified reference (CPU build under oracle/_ref, else the CPU checker) timed
 on a bounded sample on this box's host cores.
