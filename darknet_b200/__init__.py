@@ -62,6 +62,7 @@ SIGNATURES = {
     "dnb_conv_shortcut_forward": (_I, [_P, _TP, _TP, _TP, _F, _F, _I, _P]),
     "dnb_conv_plan_check_status": (_I, [_P]),
     "dnb_conv_xnor_forward_static": (_I, [C.POINTER(ConvDesc), _TP, _P, _P, _P, _P, _TP, _P]),
+    "dnb_conv_plan_set_diagnostics": (_I, [_P, C.c_longlong, _I]),
     "dnb_conv_plan_kernel": (C.c_char_p, [_P]),
     "dnb_maxpool_forward": (_I, [_TP, _TP, _I, _I, _I, _P]),
     "dnb_upsample_forward": (_I, [_TP, _TP, _I, _F, _P]),
@@ -90,6 +91,9 @@ SIGNATURES = {
     "dnb_network_layer_type": (C.c_char_p, [_P, _I]),
     "dnb_network_layer_kernel": (C.c_char_p, [_P, _I]),
     "dnb_network_layer_output": (_I, [_P, _I, _P]),
+    "dnb_network_layer_output_images": (_I, [_P, _I, _I, _I, _P]),
+    "dnb_network_check_status": (_I, [_P]),
+    "dnb_network_set_diagnostics": (_I, [_P, _I, C.c_longlong, _I]),
     "dnb_network_yolo_output": (_I, [_P, _I, C.POINTER(C.POINTER(_F))]),
     "dnb_network_flops": (C.c_double, [_P]),
     "dnb_network_launches": (_I, [_P]),

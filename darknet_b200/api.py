@@ -77,6 +77,10 @@ class ConvPlan:
     def check_status(self):
         check(lib().dnb_conv_plan_check_status(self.handle))
 
+    def set_diagnostics(self, wait_limit_cycles: int = 0, debug_bits: int = 0):
+        """Bound of the device-side waits in SM cycles (0: default) and diagnostic bits (32: withhold a load)."""
+        check(lib().dnb_conv_plan_set_diagnostics(self.handle, wait_limit_cycles, debug_bits))
+
     def close(self):
         if self.handle:
             lib().dnb_conv_plan_destroy(self.handle)
@@ -202,6 +206,19 @@ class Network:
         out = np.empty((self.batch, c, h, w), np.float32)
         check(lib().dnb_network_layer_output(self.handle, i, _ptr(out)))
         return out
+
+    def layer_output_images(self, i: int, first: int, count: int = 1) -> np.ndarray:
+        """Images first .. first+count-1 of layer i's output, NCHW f32."""
+        c, h, w = self.layer_shape(i)
+        out = np.empty((count, c, h, w), np.float32)
+        check(lib().dnb_network_layer_output_images(self.handle, i, first, count, _ptr(out)))
+        return out
+
+    def check_status(self):
+        check(lib().dnb_network_check_status(self.handle))
+
+    def set_diagnostics(self, layer: int, wait_limit_cycles: int = 0, debug_bits: int = 0):
+        check(lib().dnb_network_set_diagnostics(self.handle, layer, wait_limit_cycles, debug_bits))
 
     def yolo_output(self, i: int) -> np.ndarray:
         c, h, w = self.layer_shape(i)

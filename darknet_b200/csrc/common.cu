@@ -30,6 +30,15 @@ int sm_count()
     return cached[dev];
 }
 
+int check_current_device(int device, const char *what)
+{
+    int cur = -1;
+    DNB_CUDA(cudaGetDevice(&cur));
+    if (cur != device)
+        DNB_FAIL(DNB_EINVAL, "%s: created on CUDA device %d but device %d is current; nothing was launched (dnb_set_device(%d) first)", what, device, cur, device);
+    return DNB_OK;
+}
+
 int check_tensor(const dnb_tensor *t, const char *what)
 {
     if (!t) DNB_FAIL(DNB_EINVAL, "%s: null tensor", what);

@@ -48,6 +48,10 @@ inline size_t elem_size(int dtype) { return dtype == DNB_BF16 ? 2 : 4; }
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// DNB_EINVAL unless `device` (where a plan or network was created) is the calling thread's current device:
+// nothing is launched over another GPU's pointers.
+int check_current_device(int device, const char *what);
+
 // Validation helpers (return DNB_OK or set the error).
 int check_tensor(const dnb_tensor *t, const char *what);
 inline size_t tensor_elems(const dnb_tensor *t)

@@ -8,6 +8,9 @@
 
 namespace dnb {
 
+// Default bound of the kernels' device-side waits: about one second of SM clock cycles.
+constexpr long long DEFAULT_WAIT_CYCLES = 2000000000LL;
+
 // ---- conv_direct.cu
 struct DirectArgs {
     const void *x;                       // input, any layout through element strides
@@ -35,6 +38,7 @@ struct alignas(64) StemTcArgs {
     int y_dtype, y_cpitch;
     int n_pad, tmem_cols, tiles, npix;   // filled by the launcher
     int *status;
+    long long wait_limit;                // bound of every device-side wait, SM clock cycles
     ConvGeom g;
     ConvEpilogue ep;
 };
@@ -64,7 +68,9 @@ struct alignas(64) TcArgs {
     // weights then travel in two rings: a_stages boxes of a_slot bytes, b_stages weight tiles of b_bytes.
     int halo, a_stages, b_stages, a_slot, a_box_bytes, a_pitch;
     int tmem_cols;        // TMEM columns the CTA allocates: a power of two >= 2*bn (two accumulators)
-    int debug;            // timing experiments only (DNB_TC_DEBUG): 1 no residual loads, 2 no output stores, 4 no wait before a residual request, 8 empty epilogue, 16 no MMAs
+    int debug;            // timing experiments only (DNB_TC_DEBUG): 1 no residual loads, 2 no output stores, 4 no wait before a residual request, 8 empty epilogue, 16 no MMAs;
+                          // 32 (dnb_conv_plan_set_diagnostics): each CTA withholds the last operand load of its first tile, so a bounded wait runs out
+    long long wait_limit; // bound of every device-side wait, SM clock cycles
     int stage_bufs;       // staging buffers of the epilogue: 2, or 4 with a fused residual (tiles land in them first)
     int ctas_per_sm;      // 2 for narrow tiles (TMEM and shared memory are sized so that two CTAs share an SM), else 1
     int a_bytes, b_bytes; // shared-memory bytes of one stage's activation / weight tile (1024-multiples)
@@ -139,4 +145,6 @@ struct dnb_conv_plan {
     int tc_res_cpitch;
     int tc_y_cpitch, tc_y_dtype;
     int device;
+    long long wait_limit;    // bound of the kernels' waits in cycles (0: the default, about one second)
+    int debug_bits;          // OR-ed into the launch block's debug field (dnb_conv_plan_set_diagnostics)
 };

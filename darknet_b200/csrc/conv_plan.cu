@@ -67,6 +67,9 @@ extern "C" int dnb_conv_plan_create(const dnb_conv_desc *d, int mode, dnb_conv_p
     if (d->xnor) p->kernel = K_XNOR;
     else if (mode == DNB_MODE_FP32 || d->groups != 1 || d->c < 8) p->kernel = K_DIRECT;
     else p->kernel = mode == DNB_MODE_BF16 ? K_TC_BF16 : K_TC_TF32;
+    // the tensor-core kernel reads strided inputs through stride*stride lattices and carries maps for strides 1
+    // and 2 only; wider strides (none in the benchmark networks) run on the CUDA-core kernel
+    if ((p->kernel == K_TC_TF32 || p->kernel == K_TC_BF16) && d->stride > 2) p->kernel = K_DIRECT;
     // RGB first layers of the TF32 / BF16 modes: tensor cores with thread-built im2col rows (DNB_STEM_TC=0 keeps the FP32 kernel)
     const char *stem_env = getenv("DNB_STEM_TC");
     p->stem_tc = p->kernel == K_DIRECT && mode != DNB_MODE_FP32 && !d->xnor && conv_stem_tc_covers(p->g) && !(stem_env && atoi(stem_env) == 0);
@@ -168,6 +171,20 @@ extern "C" int dnb_conv_plan_set_params(dnb_conv_plan *p, const float *weights, 
         DNB_TRY(upload(&p->w_mean, m));
     }
     p->params_set = true;
+    // The launch block caches a tensor map over the weights just replaced: have the next forward rebuild it.
+    p->tc_x_ptr = p->tc_y_ptr = p->tc_res_ptr = nullptr;
+    return DNB_OK;
+}
+
+// Shortens the bound of the plan's device-side waits (cycles; 0 restores the default of about one second) and
+// sets diagnostic bits of the tensor-core kernel.  Bit 32 makes every CTA withhold one operand load, so that a
+// wait runs out: the way the time-out path is exercised without faulting the device.
+extern "C" int dnb_conv_plan_set_diagnostics(dnb_conv_plan *p, long long wait_limit_cycles, int debug_bits)
+{
+    if (!p || wait_limit_cycles < 0) DNB_FAIL(DNB_EINVAL, "conv diagnostics: bad argument");
+    p->wait_limit = wait_limit_cycles;
+    p->debug_bits = debug_bits;
+    p->tc_x_ptr = p->tc_y_ptr = p->tc_res_ptr = nullptr;
     return DNB_OK;
 }
 
@@ -267,7 +284,8 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     // twice the warps hide the per-tile hand-offs that dominate layers with few K iterations.
     a.ctas_per_sm = 1;
     a.stage_bufs = residual ? 4 : 2;
-    a.debug = getenv("DNB_TC_DEBUG") ? atoi(getenv("DNB_TC_DEBUG")) : 0;
+    a.debug = (getenv("DNB_TC_DEBUG") ? atoi(getenv("DNB_TC_DEBUG")) : 0) | p->debug_bits;
+    a.wait_limit = p->wait_limit > 0 ? p->wait_limit : DEFAULT_WAIT_CYCLES;
     int stages = 0;
     const bool allow2 = getenv("DNB_TC_CTAS") ? atoi(getenv("DNB_TC_CTAS")) >= 2 : true;
     a.a_stages = a.b_stages = a.a_slot = a.a_box_bytes = a.a_pitch = 0;
@@ -408,6 +426,7 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
 {
     if (!p) DNB_FAIL(DNB_EINVAL, "conv: null plan");
     if (!p->params_set) DNB_FAIL(DNB_EINVAL, "conv: dnb_conv_plan_set_params has not been called");
+    DNB_TRY(check_current_device(p->device, "conv"));
     const ConvGeom &g = p->g;
     void *y_nhwc = nullptr;
     float *y_nchw = nullptr;
@@ -441,6 +460,7 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
             DNB_CUDA(cudaMemset(p->status, 0, sizeof(int)));
         }
         a.status = p->status;
+        a.wait_limit = p->wait_limit > 0 ? p->wait_limit : DEFAULT_WAIT_CYCLES;
         a.g = g; a.ep = ep;
         return launch_conv_stem_tc(a, s);
     }
@@ -494,6 +514,7 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
     TcArgs &a = p->tc;
     a.y_nhwc = y_nhwc; a.y_dtype = y_dtype; a.y_cpitch = y_cpitch; a.y_nchw = y_nchw;
     a.ep = ep;
+    a.status = p->status;   // a network points its plans at the status word of the step being enqueued
     return launch_conv_tc(a, s);
 }
 

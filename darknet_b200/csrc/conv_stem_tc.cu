@@ -110,6 +110,7 @@ conv_stem_tc_kernel(const __grid_constant__ StemTcArgs a)
     uint8_t *const y = reinterpret_cast<uint8_t *>(a.y);
     const size_t y_row_bytes = (size_t)a.y_cpitch * (OUT_BF16 ? 2 : 4);
     int *const status = a.status;
+    const long long wait_limit = a.wait_limit;
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n_pad >> 3) << 17) | ((128u >> 4) << 24);   // TF32 x TF32 -> f32, M 128, N n_pad
     const uint64_t db = make_smem_desc(smem_u32(sB), 128);
     const uint64_t da0 = make_smem_desc(smem_u32(sA), 128);
@@ -156,7 +157,7 @@ conv_stem_tc_kernel(const __grid_constant__ StemTcArgs a)
         if (it > 0) {
             // ---- epilogue of the previous tile (its MMAs were issued at the end of the previous iteration)
             const int pb = (it - 1) & 1;
-            if (!mbar_wait(bar0, (uint32_t)((it - 1) & 1), abort_flag, status, ST_WAIT_ACC)) {
+            if (!mbar_wait(bar0, (uint32_t)((it - 1) & 1), abort_flag, status, ST_WAIT_ACC, 0, wait_limit)) {
                 failed = true;
             } else {
                 tc_fence_after();
@@ -226,6 +227,9 @@ conv_stem_tc_kernel(const __grid_constant__ StemTcArgs a)
             if (tma) {
                 if (lane == 0) tma_store_wait_read1();   // all but the store just issued have read their rows
                 __syncwarp();
+                // Staged rows narrower than an im2col row (fewer than 128 bytes of output per pixel) put this thread's
+                // im2col row over rows that OTHER warps staged two tiles ago: every warp's stores must have read them.
+                if (out_row_bytes < 128) __syncthreads();
             }
             uint8_t *row = sA + buf * ST_A_BYTES + row_off;
 #pragma unroll
@@ -338,6 +342,7 @@ conv_stem_tc_wide_kernel(const __grid_constant__ StemTcArgs a)
     const int npix = a.npix, tiles = a.tiles, plane = g.out_h * g.out_w;
     const int runtime_act = a.ep.activation, do_round = a.ep.round_tf32;
     int *const status = a.status;
+    const long long wait_limit = a.wait_limit;
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n_pad >> 3) << 17) | ((128u >> 4) << 24);
     const uint64_t db0 = make_smem_desc(smem_u32(sB), 128);
     const uint64_t da0 = make_smem_desc(smem_u32(sA), 128);
@@ -372,7 +377,7 @@ conv_stem_tc_wide_kernel(const __grid_constant__ StemTcArgs a)
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb) {
             const uint32_t buf = kcount & 1u, use = kcount >> 1;
-            if (use > 0 && !mbar_wait(done0 + 8 * buf, (use - 1) & 1u, abort_flag, status, ST_WAIT_ACC)) failed = true;
+            if (use > 0 && !mbar_wait(done0 + 8 * buf, (use - 1) & 1u, abort_flag, status, ST_WAIT_ACC, 0, wait_limit)) failed = true;
             float v[32];
 #pragma unroll
             for (int t = 0; t < 32; ++t) {
@@ -409,7 +414,7 @@ conv_stem_tc_wide_kernel(const __grid_constant__ StemTcArgs a)
         }
         if (stop) break;
         // ---- epilogue: all of the tile's MMAs have retired, the row buffers are free for the staged output
-        if (!mbar_wait(acc_bar, (uint32_t)(it & 1), abort_flag, status, ST_WAIT_ACC)) failed = true;
+        if (!mbar_wait(acc_bar, (uint32_t)(it & 1), abort_flag, status, ST_WAIT_ACC, 0, wait_limit)) failed = true;
         if (!failed) {
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);

@@ -145,6 +145,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     const int wt = a.wt, ht = a.ht, bt = a.bt, row_bytes = a.row_bytes;
     const uint32_t a_bytes = a.a_bytes;
     const int grid_stride = gridDim.x;
+    const long long wait_limit = a.wait_limit;
 
     if (warp == 0) {
         // ---------------- TMA producer: one thread runs the loop, the other lanes wait at the __syncwarp
@@ -154,6 +155,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         const CUtensorMap *wmap = &a.tmw;
         int *status = a.status;
         const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
+        const bool withhold = (a.debug & 32) != 0;
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
@@ -170,13 +172,13 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 const int ow0 = (pt % tiles_w) * wt, oh0 = ((pt / tiles_w) % tiles_h) * ht, b0 = (pt / ptiles_wh) * bt;
                 const int n0 = nt * bn;
                 for (int cb = 0; cb < c_blocks && ok; ++cb) {
-                    ok = mbar_wait_thread(empty0 + 8 * stage, phase ^ 1, abort_flag, status, WAIT_EMPTY);
+                    ok = mbar_wait_thread(empty0 + 8 * stage, phase ^ 1, abort_flag, status, WAIT_EMPTY, wait_limit);
                     if (!ok) break;
                     mbar_expect_tx(full0 + 8 * stage, a_tx);
                     tma_load_4d(ring + stage * a_slot, maps, full0 + 8 * stage, cb * bk, ow0 - cpad, oh0 - cpad, b0);
                     if (++stage == a_stages) { stage = 0; phase ^= 1; }
                     for (int tap = 0; tap < taps; ++tap) {
-                        ok = mbar_wait_thread(emptyb0 + 8 * sb, phase_b ^ 1, abort_flag, status, WAIT_EMPTY);
+                        ok = mbar_wait_thread(emptyb0 + 8 * sb, phase_b ^ 1, abort_flag, status, WAIT_EMPTY, wait_limit);
                         if (!ok) break;
                         mbar_expect_tx(fullb0 + 8 * sb, b_tx);
                         tma_load_3d(ring_b + sb * b_slot, wmap, fullb0 + 8 * sb, cb * bk, n0, tap);
@@ -199,8 +201,11 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 if (cstride == 2) { ph = dh & 1; qh = (dh - ph) >> 1; pw = dw & 1; qw = (dw - pw) >> 1; }
                 const CUtensorMap *mx = maps + (ph * cstride + pw);
                 for (int cb = 0; cb < c_blocks; ++cb) {
-                    ok = mbar_wait_thread(empty0 + 8 * stage, phase ^ 1, abort_flag, status, WAIT_EMPTY);
+                    ok = mbar_wait_thread(empty0 + 8 * stage, phase ^ 1, abort_flag, status, WAIT_EMPTY, wait_limit);
                     if (!ok) break;
+                    // wait-expiry test (debug bit 32): the last operand load of this CTA's first tile is never
+                    // requested, so the MMA role's wait for it runs out and the CTA takes the abort path
+                    if (withhold && tile == (int)blockIdx.x && tap == taps - 1 && cb == c_blocks - 1) { ok = false; break; }
                     const uint32_t bar = full0 + 8 * stage;
                     const uint32_t sa = ring + stage * stage_bytes;
                     mbar_expect_tx(bar, tx_bytes);
@@ -244,18 +249,18 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok; tile += grid_stride, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
-                ok = mbar_wait_thread(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1, abort_flag, status, WAIT_ACC_EMPTY);
+                ok = mbar_wait_thread(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1, abort_flag, status, WAIT_ACC_EMPTY, wait_limit);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * acc_stride;
                 uint32_t accumulate = 0u;
                 for (int cb = 0; cb < c_blocks && ok; ++cb) {
-                    ok = mbar_wait_thread(full0 + 8 * stage, phase, abort_flag, status, WAIT_FULL);
+                    ok = mbar_wait_thread(full0 + 8 * stage, phase, abort_flag, status, WAIT_FULL, wait_limit);
                     if (!ok) break;
                     const uint64_t dbox = dbox0 + stage * a_step;
                     int kh = 0, kw = 0;
                     for (int tap = 0; tap < taps; ++tap) {
-                        ok = mbar_wait_thread(fullb0 + 8 * sb, phase_b, abort_flag, status, WAIT_FULL);
+                        ok = mbar_wait_thread(fullb0 + 8 * sb, phase_b, abort_flag, status, WAIT_FULL, wait_limit);
                         if (!ok) break;
                         tc_fence_after();
                         const uint64_t da = dbox + (uint64_t)((kh * pitch + kw) * 8);   // 128-byte rows in 16-byte units
@@ -280,12 +285,12 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok; tile += grid_stride, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            ok = mbar_wait_thread(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1, abort_flag, status, WAIT_ACC_EMPTY);
+            ok = mbar_wait_thread(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1, abort_flag, status, WAIT_ACC_EMPTY, wait_limit);
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * acc_stride;
             for (int ki = 0; ki < k_iters; ++ki) {
-                ok = mbar_wait_thread(full0 + 8 * stage, phase, abort_flag, status, WAIT_FULL);
+                ok = mbar_wait_thread(full0 + 8 * stage, phase, abort_flag, status, WAIT_FULL, wait_limit);
                 if (!ok) break;
                 tc_fence_after();
                 if (dbg_mma & 16) {
@@ -367,7 +372,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 }
                 loaded_nt = nt;
             }
-            mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, abort_flag, status, WAIT_ACC_FULL, 32);
+            mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, abort_flag, status, WAIT_ACC_FULL, 32, wait_limit);
             epilogue_bar();                 // all four warps agree on the abort flag from here
             if (*abort_flag) break;
             tc_fence_after();
@@ -394,7 +399,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 if (residual) {
                     // this chunk's residual tile (TMA zero-fills pixels and channels outside the tensor)
                     const uint32_t rb = chunk_count & 3u;
-                    if (!(dbg & 1)) mbar_wait(smem_u32(&sh->res_full[rb]), (chunk_count >> 2) & 1, abort_flag, status, WAIT_RESIDUAL);
+                    if (!(dbg & 1)) mbar_wait(smem_u32(&sh->res_full[rb]), (chunk_count >> 2) & 1, abort_flag, status, WAIT_RESIDUAL, 0, wait_limit);
                     const uint8_t *rrow = stage_out + (size_t)rb * 128 * srb + (size_t)m * srb;
 #pragma unroll
                     for (int q = 0; q < RES_V; ++q) res[q] = *reinterpret_cast<const uint4 *>(rrow + ((q ^ q_xor) << 4));

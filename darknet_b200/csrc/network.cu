@@ -130,8 +130,9 @@ struct dnb_network {
     float *out_host_slot[2] = {nullptr, nullptr};  // pinned output-layer results ([0] is out_host)
     cudaEvent_t in_ready[2] = {nullptr, nullptr}, fwd_done[2] = {nullptr, nullptr}, copy_done[2] = {nullptr, nullptr};
     unsigned long long submitted = 0, collected = 0;
-    int *status_dev = nullptr;            // one time-out status word shared by every convolution plan
-    int *status_host = nullptr;           // pinned copy read after each predict
+    int *status_dev = nullptr;            // two time-out status words, one per step that may be in flight; every plan of
+                                          // the network is pointed at the word of the step being enqueued
+    int *status_host = nullptr;           // pinned copies, read when the step is collected
     int device = 0;
     bool weights_loaded = false;
     int convs_with_params = 0;
@@ -144,6 +145,8 @@ struct dnb_network {
     int eager_runs = 0;
     std::vector<cudaEvent_t> events;
 };
+
+static void drop_graph(dnb_network *net);
 
 static int alloc_activation(dnb_network *net, dnb_tensor *t, int c, int h, int w)
 {
@@ -341,10 +344,10 @@ static int build_network(const char *text, int mode, int batch_override, dnb_net
             DNB_CUDA(cudaEventCreateWithFlags(&L.done, cudaEventDisableTiming));
             DNB_CUDA(cudaEventCreateWithFlags(&L.copied, cudaEventDisableTiming));
         }
-    DNB_CUDA(cudaMalloc((void **)&net->status_dev, sizeof(int)));
-    DNB_CUDA(cudaMemset(net->status_dev, 0, sizeof(int)));
-    DNB_CUDA(cudaMallocHost((void **)&net->status_host, sizeof(int)));
-    *net->status_host = 0;
+    DNB_CUDA(cudaMalloc((void **)&net->status_dev, 2 * sizeof(int)));
+    DNB_CUDA(cudaMemset(net->status_dev, 0, 2 * sizeof(int)));
+    DNB_CUDA(cudaMallocHost((void **)&net->status_host, 2 * sizeof(int)));
+    net->status_host[0] = net->status_host[1] = 0;
     for (Layer &L : net->layers)
         if (L.plan) { L.plan->status = net->status_dev; L.plan->status_shared = true; }
     guard.n = nullptr;
@@ -437,6 +440,7 @@ extern "C" int dnb_load_weights(dnb_network *net, const char *path)
         ++index;
     }
     net->weights_loaded = true;
+    drop_graph(net);   // a captured forward holds the pointers of the parameter tensors just replaced
     return DNB_OK;
 }
 
@@ -448,7 +452,9 @@ extern "C" int dnb_network_set_conv_params(dnb_network *net, int layer, const fl
     if (!net || layer < 0 || layer >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "set_conv_params: bad argument");
     Layer &L = net->layers[layer];
     if (L.kind != L_CONV) DNB_FAIL(DNB_EINVAL, "set_conv_params: layer %d is not convolutional", layer);
+    if (net->submitted != net->collected) DNB_FAIL(DNB_EINVAL, "set_conv_params: a submitted step is still in flight; collect it first");
     DNB_TRY(dnb_conv_plan_set_params(L.plan, weights, biases, scales, rolling_mean, rolling_variance));
+    drop_graph(net);   // a captured forward holds the pointers of the parameter tensors just replaced
     if (!L.params_given) { L.params_given = true; ++net->convs_with_params; }
     int convs = 0;
     for (const Layer &K : net->layers) convs += K.kind == L_CONV;
@@ -470,6 +476,17 @@ extern "C" int dnb_network_export_layer(dnb_network *net, int layer, float *devi
     dnb_tensor o{device_nchw, DNB_NCHW, DNB_F32, net->batch, L.out_c, L.out_h, L.out_w, 0};
     return launch_convert(&L.out, &o, 0, 0, 0, s);
 }
+
+// Every convolution launched from here on reports an expired wait in the status word of step slot `slot`.
+static void point_status(dnb_network *net, int slot)
+{
+    for (Layer &L : net->layers)
+        if (L.plan) L.plan->status = net->status_dev + slot;
+}
+
+static const char *const kTimeoutText =
+    "a device-side wait expired in a convolution (code %d: 101 ring slot free, 102 operands landed, 103 accumulator free, "
+    "104 accumulator ready, 105 residual tile, 106 shared memory window not 1024-byte aligned); the outputs are incomplete";
 
 // One layer of forward_network_gpu's loop (src/network.c:772-785).
 // Transposes the network input into channels-last form when the first layer wants that.
@@ -543,6 +560,8 @@ extern "C" int dnb_network_forward(dnb_network *net, const float *device_input, 
     if (!net || !device_input) DNB_FAIL(DNB_EINVAL, "network_forward: null argument");
     if (!net->weights_loaded) DNB_FAIL(DNB_EINVAL, "network_forward: load_weights has not been called");
     if (net->submitted != net->collected) DNB_FAIL(DNB_EINVAL, "network_forward: a submitted step is still in flight (the layers' outputs are shared); collect it first");
+    DNB_TRY(check_current_device(net->device, "network_forward"));
+    point_status(net, 0);
     cudaStream_t s = (cudaStream_t)stream;  // NULL is the legacy default stream, as everywhere in CUDA
     if (!net->graph_enabled || !s) return forward_eager(net, device_input, s);   // the legacy stream cannot be captured
 
@@ -604,8 +623,10 @@ extern "C" int dnb_network_submit(dnb_network *net, const float *input)
     if (!net || !input) DNB_FAIL(DNB_EINVAL, "network_submit: null argument");
     if (!net->weights_loaded) DNB_FAIL(DNB_EINVAL, "network_submit: load_weights has not been called");
     if (net->submitted - net->collected >= 2) DNB_FAIL(DNB_EINVAL, "network_submit: two steps are already in flight; collect one first");
+    DNB_TRY(check_current_device(net->device, "network_submit"));
     const int slot = (int)(net->submitted & 1);
     if (slot == 1) DNB_TRY(ensure_second_slot(net));
+    point_status(net, slot);
     cudaStream_t s = net->stream, cs = net->copy_stream, hs = net->h2d_stream;
     float *in_dev = net->input_slot[slot];
     // the slot's buffers are free: the step that used them last has been collected
@@ -636,7 +657,7 @@ extern "C" int dnb_network_submit(dnb_network *net, const float *input)
     DNB_CUDA(cudaStreamWaitEvent(cs, net->fwd_done[slot], 0));
     if (last.kind != L_YOLO)
         DNB_CUDA(cudaMemcpyAsync(net->out_host_slot[slot], net->out_dev_nchw, (size_t)net->batch * net->outputs * sizeof(float), cudaMemcpyDeviceToHost, cs));
-    DNB_CUDA(cudaMemcpyAsync(net->status_host, net->status_dev, sizeof(int), cudaMemcpyDeviceToHost, cs));
+    DNB_CUDA(cudaMemcpyAsync(net->status_host + slot, net->status_dev + slot, sizeof(int), cudaMemcpyDeviceToHost, cs));
     DNB_CUDA(cudaEventRecord(net->copy_done[slot], cs));
     ++net->submitted;
     return DNB_OK;
@@ -651,12 +672,14 @@ extern "C" int dnb_network_collect(dnb_network *net, float **output)
     ++net->collected;
     DNB_CUDA(cudaEventSynchronize(net->copy_done[slot]));   // follows fwd_done[slot] and every copy of the step
     for (Layer &L : net->layers) if (L.kind == L_YOLO) L.host_out = L.host_slot[slot];
-    if (*net->status_host) {
-        const int code = *net->status_host;
-        *net->status_host = 0;
-        cudaMemsetAsync(net->status_dev, 0, sizeof(int), net->stream);
-        DNB_FAIL(DNB_ETIMEOUT, "network_predict: a device-side wait expired in a convolution (code %d: 101 ring slot free, 102 operands "
-                 "landed, 103 accumulator free, 104 accumulator ready, 105 residual tile, 106 shared memory window not 1024-byte aligned); the outputs are incomplete", code);
+    if (net->status_host[slot]) {
+        // this step's own word: the other step in flight keeps its word and its verdict
+        const int code = net->status_host[slot];
+        net->status_host[slot] = 0;
+        cudaMemsetAsync(net->status_dev + slot, 0, sizeof(int), net->stream);   // before the slot's next step, which follows on this stream
+        char text[512];
+        snprintf(text, sizeof(text), kTimeoutText, code);
+        DNB_FAIL(DNB_ETIMEOUT, "network_predict: %s", text);
     }
     Layer &last = net->layers.back();
     *output = last.kind == L_YOLO ? last.host_out : net->out_host_slot[slot];
@@ -696,17 +719,20 @@ extern "C" const char *dnb_network_layer_kernel(const dnb_network *net, int i)
     return L.plan ? dnb_conv_plan_kernel(L.plan) : kKindNames[L.kind];
 }
 
-extern "C" int dnb_network_layer_output(dnb_network *net, int i, float *host_out)
+// Images [first, first + count) of layer i's output, NCHW f32, to the host.
+extern "C" int dnb_network_layer_output_images(dnb_network *net, int i, int first, int count, float *host_out)
 {
     if (!net || !host_out || i < 0 || i >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "layer_output: bad argument");
+    if (first < 0 || count < 1 || first + count > net->batch) DNB_FAIL(DNB_EINVAL, "layer_output: images %d..%d of a batch of %d", first, first + count - 1, net->batch);
     Layer &L = net->layers[i];
     if (net->submitted != net->collected) DNB_FAIL(DNB_EINVAL, "layer_output: a submitted step is still in flight; collect it first");
     if (!L.out.data)
         DNB_FAIL(DNB_EUNSUPPORTED, "layer %d is fused into the shortcut layer %d and has no output of its own (DNB_FUSE_SHORTCUT=0 keeps it)", i, i + 1);
-    const size_t elems = (size_t)net->batch * L.out_c * L.out_h * L.out_w;
+    const size_t per_image = (size_t)L.out_c * L.out_h * L.out_w;
+    const size_t elems = (size_t)count * per_image;
     DNB_CUDA(cudaDeviceSynchronize());  // the forward may have run on any stream
     if (L.out.layout == DNB_NCHW) {
-        DNB_CUDA(cudaMemcpy(host_out, L.out.data, elems * sizeof(float), cudaMemcpyDeviceToHost));
+        DNB_CUDA(cudaMemcpy(host_out, (const float *)L.out.data + (size_t)first * per_image, elems * sizeof(float), cudaMemcpyDeviceToHost));
         return DNB_OK;
     }
     if (elems > net->export_elems) {
@@ -715,11 +741,53 @@ extern "C" int dnb_network_layer_output(dnb_network *net, int i, float *host_out
         DNB_CUDA(cudaMalloc((void **)&net->export_dev, elems * sizeof(float)));
         net->export_elems = elems;
     }
-    dnb_tensor o{net->export_dev, DNB_NCHW, DNB_F32, net->batch, L.out_c, L.out_h, L.out_w, 0};
-    DNB_TRY(launch_convert(&L.out, &o, 0, 0, 0, net->stream));
+    // a run of whole images of a channels-last tensor is itself a channels-last tensor
+    dnb_tensor in = L.out;
+    in.n = count;
+    in.data = (char *)L.out.data + (size_t)first * L.out_h * L.out_w * L.out.cpitch * elem_size(L.out.dtype);
+    dnb_tensor o{net->export_dev, DNB_NCHW, DNB_F32, count, L.out_c, L.out_h, L.out_w, 0};
+    DNB_TRY(launch_convert(&in, &o, 0, 0, 0, net->stream));
     DNB_CUDA(cudaStreamSynchronize(net->stream));
     DNB_CUDA(cudaMemcpy(host_out, net->export_dev, elems * sizeof(float), cudaMemcpyDeviceToHost));
     return DNB_OK;
+}
+
+extern "C" int dnb_network_layer_output(dnb_network *net, int i, float *host_out)
+{
+    if (!net) DNB_FAIL(DNB_EINVAL, "layer_output: bad argument");
+    return dnb_network_layer_output_images(net, i, 0, net->batch, host_out);
+}
+
+// Waits for the device, then reads and clears both status words: DNB_ETIMEOUT if a bounded wait expired in any
+// convolution since the last check.  For callers of the device-resident dnb_network_forward, which returns
+// before its kernels have run; dnb_network_collect reports the same for submitted steps.
+extern "C" int dnb_network_check_status(dnb_network *net)
+{
+    if (!net) DNB_FAIL(DNB_EINVAL, "check_status: null network");
+    if (net->submitted != net->collected) DNB_FAIL(DNB_EINVAL, "check_status: a submitted step is still in flight; collect it first");
+    int v[2] = {0, 0};
+    DNB_CUDA(cudaDeviceSynchronize());
+    DNB_CUDA(cudaMemcpy(v, net->status_dev, sizeof(v), cudaMemcpyDeviceToHost));
+    if (v[0] || v[1]) {
+        DNB_CUDA(cudaMemset(net->status_dev, 0, sizeof(v)));
+        char text[512];
+        snprintf(text, sizeof(text), kTimeoutText, v[0] ? v[0] : v[1]);
+        DNB_FAIL(DNB_ETIMEOUT, "network_forward: %s", text);
+    }
+    return DNB_OK;
+}
+
+extern "C" int dnb_conv_plan_set_diagnostics(dnb_conv_plan *p, long long wait_limit_cycles, int debug_bits);
+
+// dnb_conv_plan_set_diagnostics for convolution `layer` of the network.
+extern "C" int dnb_network_set_diagnostics(dnb_network *net, int layer, long long wait_limit_cycles, int debug_bits)
+{
+    if (!net || layer < 0 || layer >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "set_diagnostics: bad argument");
+    Layer &L = net->layers[layer];
+    if (L.kind != L_CONV) DNB_FAIL(DNB_EINVAL, "set_diagnostics: layer %d is not convolutional", layer);
+    // launches already enqueued carry their own copy of the argument block: only later ones see the change
+    drop_graph(net);
+    return dnb_conv_plan_set_diagnostics(L.plan, wait_limit_cycles, debug_bits);
 }
 
 extern "C" int dnb_network_yolo_output(dnb_network *net, int i, const float **host_out)
@@ -757,6 +825,8 @@ extern "C" int dnb_network_forward_timed(dnb_network *net, const float *device_i
     if (!net || !device_input || slot < 0 || slot > 4096) DNB_FAIL(DNB_EINVAL, "network_forward_timed: bad argument");
     if (!net->weights_loaded) DNB_FAIL(DNB_EINVAL, "network_forward_timed: load_weights has not been called");
     if (net->submitted != net->collected) DNB_FAIL(DNB_EINVAL, "network_forward_timed: a submitted step is still in flight; collect it first");
+    DNB_TRY(check_current_device(net->device, "network_forward_timed"));
+    point_status(net, 0);
     const int n = (int)net->layers.size();
     while ((int)net->events.size() < (slot + 1) * (n + 1)) {
         cudaEvent_t e;

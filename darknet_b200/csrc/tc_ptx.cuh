@@ -6,7 +6,9 @@
 
 namespace dnb {
 
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about one second
+// Default bound of every device-side wait, in SM clock cycles (about one second).  The bound travels in the
+// kernels' argument blocks, so a caller (or a test) can shorten it for one plan.
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -50,7 +52,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t pa
 }
 
 // Bounded wait for a loop that a single thread runs (the TMA and MMA roles): no warp traffic at all.
-__device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+__device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
+                                                 long long limit = WAIT_LIMIT_CYCLES)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
@@ -58,7 +61,7 @@ __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, 
     while (!mbar_try_wait_hint(bar, parity, 1000u)) {
         if ((++spins & 0x3f) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
@@ -69,7 +72,7 @@ __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, 
 }
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
-                                          unsigned backoff_ns = 0)
+                                          unsigned backoff_ns = 0, long long limit = WAIT_LIMIT_CYCLES)
 {
     int ok = 1;
     if ((threadIdx.x & 31) == 0) {
@@ -80,7 +83,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                 if (backoff_ns) __nanosleep(backoff_ns);
                 if ((++spins & 0x3f) == 0) {
                     if (*abort_flag) { ok = 0; break; }
-                    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                    if (clock64() - t0 > limit) {
                         *abort_flag = 1;
                         atomicCAS(status, 0, code);
                         ok = 0;

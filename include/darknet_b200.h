@@ -179,6 +179,17 @@ int dnb_conv_xnor_forward_static(const dnb_conv_desc *desc, const dnb_tensor *x,
  * counterpart (its kernels have no waits). */
 int dnb_conv_plan_check_status(dnb_conv_plan *plan);
 
+/* Diagnostics of a plan's device-side waits.  wait_limit_cycles: the bound of every
+ * wait inside the plan's kernels in SM clock cycles (0 = the default, about one
+ * second).  debug_bits: 0, or 32 to make every CTA of the tensor-core kernel withhold
+ * one operand load so that a wait runs out; the launch then ends early with its
+ * status word set, the context stays usable, and dnb_conv_plan_check_status /
+ * dnb_network_collect report DNB_ETIMEOUT.  This is how the time-out path is
+ * exercised (host-side injection: nothing faults, traps or hangs); other bits are
+ * timing experiments and give wrong results.  The reference has no counterpart:
+ * its kernels have no waits (src/convolutional_kernels.cu:73-135). */
+int dnb_conv_plan_set_diagnostics(dnb_conv_plan *plan, long long wait_limit_cycles, int debug_bits);
+
 /* Name of the kernel a plan dispatches to ("tc_tf32", "tc_bf16", "direct_fp32",
  * "xnor_popc"); static storage. */
 const char *dnb_conv_plan_kernel(const dnb_conv_plan *plan);
@@ -288,6 +299,17 @@ int dnb_network_forward(dnb_network *net, const float *device_input, void *strea
  * cost more than the kernels.  No counterpart in the reference. */
 int dnb_network_enable_graph(dnb_network *net, int on);
 
+/* Waits for the device, then reads and clears the network's status words:
+ * DNB_ETIMEOUT if a bounded wait expired in a convolution since the last check (its
+ * outputs are incomplete).  For callers of dnb_network_forward, which returns before
+ * its kernels ran; dnb_network_collect / dnb_network_predict report the same for
+ * their own step.  check_error(cudaPeekAtLastError()) after each launch is the
+ * nearest thing in the reference (src/cuda.c:27-49). */
+int dnb_network_check_status(dnb_network *net);
+
+/* dnb_conv_plan_set_diagnostics for convolution `layer` of the network. */
+int dnb_network_set_diagnostics(dnb_network *net, int layer, long long wait_limit_cycles, int debug_bits);
+
 /* Geometry queries (net->n, net->batch, net->inputs, net->outputs; layer
  * out_c/out_h/out_w/outputs and type as the section name, e.g. "convolutional"). */
 int dnb_network_num_layers(const dnb_network *net);
@@ -305,6 +327,10 @@ int dnb_network_layer_output(dnb_network *net, int layer, float *host_out);
 /* The same into device memory of the caller (what l.output_gpu holds in the reference), asynchronously on
  * `stream`: the hook an attach shim uses to hand results to layers the reference still runs. */
 int dnb_network_export_layer(dnb_network *net, int layer, float *device_nchw, void *stream);
+
+/* Images [first, first+count) of that output only: count*outputs floats.  For
+ * checking a few images of a large batch without pulling whole layers. */
+int dnb_network_layer_output_images(dnb_network *net, int layer, int first, int count, float *host_out);
 
 /* Host pointer to a [yolo] layer's output of the last predict (the reference
  * pulls it inside forward_yolo_layer_gpu, src/yolo_layer.c:360). */

@@ -14,7 +14,7 @@ import pytest
 import torch
 
 import darknet_b200 as dn
-from conftest import rel_to_max
+from conftest import parity, rel_to_max
 from darknet_b200 import synth
 from gpu_util import dev_nhwc, empty_nhwc, host_from_nhwc
 from oracle import network as orc
@@ -59,8 +59,7 @@ def test_isolated_layer_at_full_size(c, n, size):
     for img in (0, 63):   # the checker redoes two images (6.4 GFLOP each for the 3x3 layer)
         want = orc.conv_forward(x[img:img + 1], w, p["biases"], p["scales"], p["mean"], p["var"], stride=1, pad=size // 2,
                                 groups=1, activation=act)
-        err = rel_to_max(got[img:img + 1], want)
-        assert err < TOL_TF32, f"image {img}: rel error {err:.3g}"
+        parity(got[img:img + 1], want, TOL_TF32, f"image {img}")
     # images are independent: the reversed batch gives the reversed output, bit for bit
     got_rev = gpu_conv(x[::-1].copy(), w, p, act, size)
     assert np.array_equal(got_rev[::-1], got)
@@ -90,10 +89,9 @@ def test_yolov3_608_one_image_every_layer(tmp_path):
             got = net.layer_output(i)
         except dn.DarknetB200Error:
             continue                                        # a convolution whose shortcut was fused has no output of its own
-        e = rel_to_max(got, wnt)
+        e = parity(got, wnt, TOL_TF32, f"layer {i}")
         worst = max(worst, e)
         checked += 1
-        assert e < TOL_TF32, f"layer {i}: rel error {e:.3g}"
     assert checked >= 107 - 23
     print(f"yolov3-608: {checked} layer outputs checked, worst rel error {worst:.3g}")
     # a batch of two: each image's heads equal the single-image run, bit for bit
@@ -124,11 +122,10 @@ def test_other_benchmark_networks_at_full_resolution(name, gen, batch, seed, tmp
             got = net.layer_output(i)
         except dn.DarknetB200Error:
             continue
-        e = rel_to_max(got, wnt)
+        e = parity(got, wnt, TOL_TF32, f"{name}, layer {i}")
         worst = max(worst, e)
         checked += 1
-        assert e < TOL_TF32, f"{name}, layer {i}: rel error {e:.3g}"
-    assert rel_to_max(out.reshape(want[-1].shape), want[-1]) < TOL_TF32
+    parity(out.reshape(want[-1].shape), want[-1], TOL_TF32)
     print(f"{name}: {checked} layer outputs checked, worst rel error {worst:.3g}")
 
 
@@ -149,5 +146,4 @@ def test_yolov3_other_input_sizes(size, mode, tol, tmp_path):
     heads = [i for i in range(net.n) if net.layer_type(i) == "yolo"]
     assert len(heads) == 3
     for i in heads:
-        e = rel_to_max(net.yolo_output(i), want[i])
-        assert e < tol, f"size {size}, head {i}: rel error {e:.3g}"
+        parity(net.yolo_output(i), want[i], tol, f"size {size}, head {i}")

@@ -12,7 +12,7 @@ import pytest
 import torch
 
 import darknet_b200 as dn
-from conftest import rel_to_max
+from conftest import parity, rel_to_max
 from gpu_util import bf16_round, dev_nchw, dev_nhwc, empty_nchw, empty_nhwc, host_from_nhwc, padding_is_zero
 from oracle import network as orc
 
@@ -102,7 +102,7 @@ def test_shortcut(xs, adds, act, layout):
         dn.shortcut(xd, ad, yd, 1.0, 1.0, act)
         got = host_from_nhwc(yt, c)
         assert padding_is_zero(yt, c)
-    assert rel_to_max(got, want) < TOL_FP32
+    parity(got, want, TOL_FP32)
 
 
 def test_shortcut_bf16_storage():
@@ -114,7 +114,7 @@ def test_shortcut_bf16_storage():
     at, ad = dev_nhwc(add, torch.bfloat16)
     yt, yd = empty_nhwc(2, 64, 10, 10, torch.bfloat16)
     dn.shortcut(xd, ad, yd)
-    assert rel_to_max(host_from_nhwc(yt, 64), want) < 2 ** -8
+    parity(host_from_nhwc(yt, 64), want, 2 ** -8)
 
 
 @pytest.mark.parametrize("chans,hw", [((256, 512), (19, 19)), ((128, 256, 3), (13, 11)), ((255,), (7, 7)), ((12, 20), (5, 5))])
@@ -166,7 +166,7 @@ def test_yolo_head(layout):
     xt, xd = dev_nhwc(x) if layout == "nhwc" else dev_nchw(x)
     yt, yd = empty_nchw(2, 255, 13, 13)
     dn.yolo(xd, yd, 3, 80)
-    assert rel_to_max(yt.cpu().numpy(), want) < TOL_FP32
+    parity(yt.cpu().numpy(), want, TOL_FP32)
 
 
 @pytest.mark.parametrize("layout", ["nhwc", "nchw"])
@@ -186,8 +186,8 @@ def test_avgpool_softmax(layout):
     dn.softmax(ad, sd)
     got_a = at.cpu().numpy() if layout == "nchw" else host_from_nhwc(at, 1000)
     got_s = st.cpu().numpy() if layout == "nchw" else host_from_nhwc(st, 1000)
-    assert rel_to_max(got_a, want_a) < 1e-5
-    assert rel_to_max(got_s, want_s) < 1e-5
+    parity(got_a, want_a, 1e-5)
+    parity(got_s, want_s, 1e-5)
 
 
 # ------------------------------------------------------------------ convolution
@@ -256,7 +256,7 @@ def test_conv_direct_fp32(name, layouts):
     case = conv_case(100, **DIRECT_CASES[name])
     plan, got, _ = run_conv(case, dn.MODE_FP32, layouts[0], layouts[1])
     assert plan.kernel == "direct_fp32"
-    assert rel_to_max(got, oracle_conv(case)) < 1e-5
+    parity(got, oracle_conv(case), 1e-5)
 
 
 STEM_CASES = {
@@ -285,13 +285,12 @@ def test_conv_stem_tensor_core(name, mode):
     tol = TOL_TF32 if mode == dn.MODE_TF32 else TOL_BF16
     plan, got, _ = run_conv(case, mode, "nchw", "nhwc")
     assert plan.kernel == "stem_tc_tf32"
-    err = rel_to_max(got, want)
-    assert err < tol, f"{name}: rel error {err:.3g}"
+    parity(got, want, tol, name)
     if mode == dn.MODE_TF32:
         _, got2, _ = run_conv(case, mode, "nhwc", "nhwc")     # channels-last f32 input through the same strides
         assert np.array_equal(got, got2)
         _, got3, _ = run_conv(case, mode, "nchw", "nchw")     # fallback: exact FP32 arithmetic
-        assert rel_to_max(got3, want) < 1e-5
+        parity(got3, want, 1e-5)
 
 
 TC_CASES = {
@@ -324,12 +323,11 @@ def test_conv_tc_tf32(name):
     want = oracle_conv(case)
     plan, got, got2 = run_conv(case, dn.MODE_TF32, "nchw", "nchw", both=True)
     assert plan.kernel == "tc_tf32"
-    err = rel_to_max(got, want)
-    assert err < TOL_TF32, f"{name}: rel error {err:.3g}"
+    parity(got, want, TOL_TF32, name)
     assert np.array_equal(got, got2), "NCHW and NHWC copies of one launch differ"
     # channels-last in, channels-last out (the layout used between layers)
     _, got3, _ = run_conv(case, dn.MODE_TF32, "nhwc", "nhwc")
-    assert rel_to_max(got3, want) < TOL_TF32
+    parity(got3, want, TOL_TF32)
 
 
 @pytest.mark.parametrize("name", list(TC_CASES))
@@ -338,10 +336,9 @@ def test_conv_tc_bf16(name):
     want = oracle_conv(case)
     plan, got, _ = run_conv(case, dn.MODE_BF16, "nchw", "nchw")
     assert plan.kernel == "tc_bf16"
-    err = rel_to_max(got, want)
-    assert err < TOL_BF16, f"{name}: rel error {err:.3g}"
+    parity(got, want, TOL_BF16, name)
     _, got3, _ = run_conv(case, dn.MODE_BF16, "nhwc", "nhwc")
-    assert rel_to_max(got3, want) < TOL_BF16
+    parity(got3, want, TOL_BF16)
 
 
 HALO_CASES = {
@@ -365,14 +362,13 @@ def test_conv_tc_halo_mode(name, mode, tol, monkeypatch):
     _, got, _ = run_conv(case, mode, "nhwc", "nhwc")
     monkeypatch.setenv("DNB_TC_HALO", "0")
     _, plain, _ = run_conv(case, mode, "nhwc", "nhwc")
-    err = rel_to_max(got, want)
-    assert err < tol, f"{name}: rel error {err:.3g}"
+    parity(got, want, tol, name)
     # same products in another summation order: a few results land on the neighbouring TF32 (bf16) value when rounded for storage
-    assert rel_to_max(got, plain) < (2e-3 if mode == dn.MODE_TF32 else 1e-2)
+    parity(got, plain, (2e-3 if mode == dn.MODE_TF32 else 1e-2))
     monkeypatch.setenv("DNB_TC_HALO", "2")
     _, got_nchw, got_nhwc = run_conv(case, mode, "nchw", "nchw", both=True)
     assert np.array_equal(got_nchw, got_nhwc)
-    assert rel_to_max(got_nchw, want) < tol
+    parity(got_nchw, want, tol)
 
 
 def test_conv_tc_all_ones_counts_taps():
@@ -419,7 +415,7 @@ def test_conv_xnor(name, in_layout):
     plan.forward(xd, yd, y2d)
     want = oracle_conv(case, xnor=True)
     # the CPU adds +-mean one product at a time in fp32; mean * integer differs from that sum in the last bits
-    assert rel_to_max(yt.cpu().numpy(), want) < 1e-5
+    parity(yt.cpu().numpy(), want, 1e-5)
     assert np.array_equal(host_from_nhwc(y2t, n), yt.cpu().numpy()) and padding_is_zero(y2t, n)
 
 
@@ -473,5 +469,5 @@ def test_conv_with_fused_shortcut(mode, tol, act2, shape):
                                                 C.c_void_p(torch.cuda.current_stream().cuda_stream)))
     torch.cuda.synchronize()
     plan.check_status()
-    assert rel_to_max(host_from_nhwc(yt, n), want) < tol
+    parity(host_from_nhwc(yt, n), want, tol)
     assert padding_is_zero(yt, n)

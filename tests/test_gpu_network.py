@@ -14,7 +14,7 @@ import pytest
 import torch
 
 import darknet_b200 as dn
-from conftest import rel_to_max
+from conftest import parity, rel_to_max
 from darknet_b200 import synth
 from oracle import network as orc
 
@@ -59,18 +59,17 @@ def test_network_matches_oracle_and_golden(name, mode, fuse, tmp_path, golden, m
             skipped += 1
             continue
         assert got.shape == w.shape or got.size == w.size
-        err = rel_to_max(got, w)
+        err = parity(got, w, TOL[mode], f"{name} layer {i} ({kinds[i]}, {net.layer_kernel(i)})")
         worst = max(worst, err)
-        assert err < TOL[mode], f"{name} layer {i} ({kinds[i]}, {net.layer_kernel(i)}): rel error {err:.3g}"
         # golden sample straight from the unmodified reference
         sample = golden[f"{name}/{i}/sample"]
         g = got.reshape(-1)[make_golden.sample_index(got.size)]
         assert np.abs(g - sample).max() / max(np.abs(w).max(), 1e-30) < TOL[mode]
     # network_predict returns the last layer, yolo heads are pulled to the host as well
-    assert rel_to_max(out.reshape(-1), want[-1].reshape(-1)) < TOL[mode]
+    parity(out.reshape(-1), want[-1].reshape(-1), TOL[mode])
     for i, k in enumerate(kinds):
         if k == "yolo":
-            assert rel_to_max(net.yolo_output(i), want[i]) < TOL[mode]
+            parity(net.yolo_output(i), want[i], TOL[mode])
     if fuse and mode != dn.MODE_FP32 and "shortcut" in kinds:
         assert skipped > 0, "no convolution was fused with its shortcut"
     if not fuse:
@@ -180,9 +179,9 @@ def test_network_of_memory_layers_only(mode, tmp_path):
     for i, w in enumerate(want):
         got = net.layer_output(i)
         if mode == dn.MODE_BF16:
-            assert rel_to_max(got, w) < 2e-2
+            parity(got, w, 2e-2)
         elif mode == dn.MODE_TF32:
-            assert rel_to_max(got, w) < 1e-3     # the input copy is rounded to TF32 once
+            parity(got, w, 1e-3)     # the input copy is rounded to TF32 once
         else:
             assert np.array_equal(got, w), f"layer {i}"
     assert out.shape == (3, net.outputs)
@@ -238,8 +237,8 @@ def test_xnor_network_teacher_forced(tmp_path):
         xt, xd = dev_nchw(xin)
         yt, yd = empty_nchw(*want[i].shape)
         plan.forward(xd, yd)
-        assert rel_to_max(yt.cpu().numpy(), want[i]) < 1e-5, f"layer {i}"
+        parity(yt.cpu().numpy(), want[i], 1e-5, f"layer {i}")
     net = build(cfg, params, tmp_path, dn.MODE_TF32)
     net.predict(x)
     assert [net.layer_kernel(i) for i in range(net.n)].count("xnor_popc") == 17
-    assert rel_to_max(net.layer_output(0), want[0]) < 1e-3   # fp32 stem, stored rounded to TF32 for the next layer
+    parity(net.layer_output(0), want[0], 1e-3)   # fp32 stem, stored rounded to TF32 for the next layer

@@ -15,7 +15,7 @@ import darknet_b200 as dn
 from darknet_b200 import synth
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF_CFG = "/root/reference/cfg"
+REF_CFG = os.path.join(os.environ.get("DARKNET_ROOT", os.path.join(os.sep, "root", "reference")), "cfg")   # the reference tree, where it is mounted
 
 
 def declared_symbols():
@@ -73,6 +73,22 @@ def test_plan_validation_needs_no_device():
     assert L.dnb_conv_plan_create(C.byref(bad), 7, C.byref(h)) == dn.EINVAL
     with pytest.raises(dn.DarknetB200Error):
         dn.check(L.dnb_conv_plan_create(None, 0, C.byref(h)))
+
+
+def test_wide_strides_fall_back_to_the_cuda_core_kernel():
+    """The tensor-core kernel carries input maps for strides 1 and 2; a wider stride is decided when the plan is
+    made (the CUDA-core kernel takes it), not at the first forward."""
+    L = dn.lib()
+    for mode in (dn.MODE_TF32, dn.MODE_BF16):
+        h = C.c_void_p()
+        d = dn.ConvDesc(1, 16, 16, 16, 16, 1, 3, 3, 1, 0, 3, 0)
+        assert L.dnb_conv_plan_create(C.byref(d), mode, C.byref(h)) == dn.OK
+        assert L.dnb_conv_plan_kernel(h) == b"direct_fp32"
+        L.dnb_conv_plan_destroy(h)
+        d2 = dn.ConvDesc(1, 16, 16, 16, 16, 1, 3, 2, 1, 0, 3, 0)
+        assert L.dnb_conv_plan_create(C.byref(d2), mode, C.byref(h)) == dn.OK
+        assert L.dnb_conv_plan_kernel(h).startswith(b"tc_")
+        L.dnb_conv_plan_destroy(h)
 
 
 def test_degenerate_geometry_is_refused():

@@ -8,8 +8,12 @@ they run (fixed-arena serving loops, plug-ins in processes that forbid allocatio
 after start-up): its scratch is a fixed array inside the library image.  The test
 hands it device buffers it owns (torch is only the allocator of the test's own
 inputs and outputs), calls it twice in a row, and checks both results against
-dnb_conv_forward on an xnor plan, within the tolerance of the xnor tests (1e-5 of
-the layer maximum; the two paths run the same kernels, so they agree bit for bit).
+dnb_conv_forward on an xnor plan and against the CPU checker's xnor convolution,
+within the tolerance of the xnor tests (1e-5 of the layer maximum: the CPU adds
++-mean one product at a time, the GPU multiplies the integer sum by the mean).
+The plan path runs the same kernels; the checker also validates the host-side
+packing of sign bits, filter means and folded batchnorm that a caller of this
+entry point has to do itself.
 """
 import ctypes as C
 
@@ -18,8 +22,9 @@ import pytest
 import torch
 
 import darknet_b200 as dn
-from conftest import rel_to_max
+from conftest import parity
 from gpu_util import dev_nchw, dev_nhwc, empty_nchw, empty_nhwc, host_from_nhwc
+from oracle import network as orc
 
 pytestmark = pytest.mark.gpu
 
@@ -59,6 +64,8 @@ def test_static_xnor_matches_plan(layout):
     plan.forward(xd, rd)
     torch.cuda.synchronize()
     want = rt.cpu().numpy() if layout == "nchw" else host_from_nhwc(rt, n)
+    want_cpu = orc.conv_forward(x, w, biases, scales, mean, var, stride=1, pad=1, groups=1, activation="leaky", xnor=True)
+    want_cpu_neg = orc.conv_forward(-x, w, biases, scales, mean, var, stride=1, pad=1, groups=1, activation="leaky", xnor=True)
 
     bits, wmean, s, sh = pack_params(w, scales, mean, var, biases)
     dev = [torch.from_numpy(a).cuda() for a in (bits.view(np.int32), wmean, s, sh)]
@@ -73,7 +80,8 @@ def test_static_xnor_matches_plan(layout):
                                                        C.c_void_p(dev[3].data_ptr()), C.byref(yd), stream))
         torch.cuda.synchronize()
         got = yt.cpu().numpy() if layout == "nchw" else host_from_nhwc(yt, n)
-        assert rel_to_max(got, want) < 1e-5, f"call {call}"
+        parity(got, want, 1e-5, f"call {call} against the plan path")
+        parity(got, want_cpu, 1e-5, f"call {call} against the CPU checker")
         # a different input between the calls, so that stale scratch would show
         if call == 0:
             x2 = -x
@@ -83,6 +91,8 @@ def test_static_xnor_matches_plan(layout):
                                                            C.c_void_p(dev[1].data_ptr()), C.c_void_p(dev[2].data_ptr()),
                                                            C.c_void_p(dev[3].data_ptr()), C.byref(td), stream))
             torch.cuda.synchronize()
+            got_neg = tt.cpu().numpy() if layout == "nchw" else host_from_nhwc(tt, n)
+            parity(got_neg, want_cpu_neg, 1e-5, "negated input against the CPU checker")
 
 
 def test_static_xnor_rejects_oversized_layer():
