@@ -21,7 +21,10 @@ in flight; `e2e.blocking_predict` is the blocking network_predict call);
 `graph_replay` the device-resident forward as one CUDA graph per step; `roofline` describes the tensor-core convolution kernel, timed with
 CUDA events between layers inside the timed region; `cpu_baseline` is the
 unmodified reference (CPU build under oracle/_ref, else the CPU checker) timed
-on a bounded sample on this box's host cores.
+on a bounded sample on this box's host cores.  More keys: `strong` (N > 1: the same 64 images
+split over the ranks, graph replay), `host_copy_ceiling` (plain pinned-memory copies of the step's bytes
+on all ranks at once: what the host side can move, and `e2e` as a fraction of it), `other_configs`
+(N = 1: ResNet-50 batch 256 and xnor Darknet-19 batch 128, value and roofline).
 """
 from __future__ import annotations
 
@@ -42,9 +45,9 @@ import numpy as np  # noqa: E402
 
 UNIT = "images/s"
 
-# DRAM traffic of the tensor-core convolution kernel from ncu (dram__bytes_read.sum + dram__bytes_write.sum), as
-# (bytes per image, bytes per launch set independent of the batch); see profiles/conv_tc_dram_traffic_*.md and
-# profiles/conv_tc_conv*_b64_tf32.md for the captures.  Scaled by the images one step processes.
+# DRAM traffic of the tensor-core convolution kernel as ncu measured it (dram__bytes_read.sum + dram__bytes_write.sum
+# summed over the kernel's launches of one forward), as (bytes per image, bytes per forward independent of the batch:
+# the weights, read once per launch).  Scaled by the images one step processes.
 NCU_DRAM_TRAFFIC = {
     ("yolov3", "tf32", 608): (544_230_624.0, 247_579_648.0),
     ("conv3x3", "tf32", 224): (485.0e6 / 64, 0.0),
@@ -68,6 +71,12 @@ def workload_cfg(name: str, batch: int, size: int) -> tuple[str, str, str]:
         return synth.single_conv_cfg(batch, 256, 52, 52, 512, 3), "conv3x3_256_512_52_images_per_s", "isolated 3x3 conv 256->512 at 52x52"
     if name == "conv1x1":
         return synth.single_conv_cfg(batch, 512, 52, 52, 256, 1), "conv1x1_512_256_52_images_per_s", "isolated 1x1 conv 512->256 at 52x52"
+    if name.startswith("conv:"):   # conv:C,HW,N,SIZE[,STRIDE]: any single layer, for profiling (batchnorm + leaky)
+        v = [int(t) for t in name[5:].split(",")]
+        c, hw, n, k = v[:4]
+        st = v[4] if len(v) > 4 else 1
+        return (synth.single_conv_cfg(batch, c, hw, hw, n, k, stride=st), f"conv{k}x{k}_{c}_{n}_{hw}_images_per_s",
+                f"isolated {k}x{k}/{st} conv {c}->{n} at {hw}x{hw}")
     if name == "memlayers":   # maxpool / upsample / shortcut / route at the shapes of YOLOv3's 152x152 stage
         return synth.memory_layers_cfg(batch, 128, size or 152), "memory_layers_152_images_per_s", "maxpool, upsample, shortcut, route chained (128 channels, 152x152)"
     raise SystemExit(f"unknown workload {name}")
@@ -85,11 +94,14 @@ def parse_args():
     ap.add_argument("--mode", default="tf32", choices=["tf32", "bf16"])
     ap.add_argument("--batch", type=int, default=64, help="images per GPU per step")
     ap.add_argument("--size", type=int, default=0, help="input width = height (default: 608 yolov3, 416 tiny, 224 classifiers)")
-    ap.add_argument("--workload", default="yolov3", choices=["yolov3", "yolov3-tiny", "resnet50", "darknet19-xnor", "conv3x3", "conv1x1", "memlayers"])
+    ap.add_argument("--workload", default="yolov3",
+                    help="yolov3 (the headline), yolov3-tiny, resnet50, darknet19-xnor, conv3x3, conv1x1, memlayers, or conv:C,HW,N,SIZE[,STRIDE] "
+                         "for one convolutional layer of that shape")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: --batch images on every GPU; strong: --batch images split over the GPUs")
     ap.add_argument("--cpu-sample", type=int, default=4, help="images of the CPU-baseline sample (0 = skip)")
     ap.add_argument("--layers", default="", help="write a per-layer time table to this file")
+    ap.add_argument("--no-extras", action="store_true", help="skip the strong-scaling, copy-ceiling and other-configuration records")
     return ap.parse_args()
 
 
@@ -308,6 +320,135 @@ def run_reference_gpu(args):
                                              "(im2col + cuBLAS sgemm per image), network_predict with host buffers"}}), flush=True)
 
 
+def roofline_of(net, cfg: str, per_gpu: int, mean_ms, mode: str, workload: str, size: int):
+    """Roofline object of a network's dominant kernel from per-layer CUDA-event times: the tensor-core convolution
+    (FLOPs against the measured tensor peak, with its HBM-bound launches split out), the popcount convolution of an
+    xnor network (word-popcounts per second), or the memory-bound layer kernels (bytes against the HBM copy rate).
+    Returns (roofline, flops per layer, layer kinds, layer kernels)."""
+    from darknet_b200 import synth
+    kinds = [net.layer_type(i) for i in range(net.n)]
+    kernels = [net.layer_kernel(i) for i in range(net.n)]
+    flops = np.zeros(net.n)
+    sections = synth.parse_cfg(cfg)[1:]
+    shapes = {s.index: s for s in synth.conv_shapes(cfg)}
+    for i, (k, opt) in enumerate(sections):
+        if k == "convolutional":
+            c, h, w = net.layer_shape(i)
+            s = shapes[i]
+            flops[i] = 2.0 * s.n * s.size * s.size * (s.c // s.groups) * h * w * per_gpu
+    tc = np.array([kn.startswith("tc_") for kn in kernels])
+    tc_ms = float(mean_ms[tc].sum())
+    tc_flops = float(flops[tc].sum())
+    peaks = load_peaks()
+    achieved = tc_flops / (tc_ms / 1000.0) / 1e12 if tc_ms > 0 else 0.0
+    # a kernel timed alone is held against the burst figure, one timed inside a long step against the sustained one
+    alone = workload.startswith("conv")
+    bf16_peak = peaks["bf16_tflops"] if alone else peaks["bf16_sustained"]
+    peak = bf16_peak / (2.0 if mode == "tf32" else 1.0)
+    big3 = np.array([bool(tc[i]) and sections[i][1].get("size") == "3" and shapes[i].c >= 64 for i in range(net.n)])
+    big3_tflops = float(flops[big3].sum() / (mean_ms[big3].sum() / 1000.0) / 1e12) if big3.any() else None
+    # the other launches of the same kernel (1x1 layers, 3x3 layers with fewer than 64 input channels) are bound by
+    # HBM: algorithmic bytes = input + output of the layer in its storage type, the weights once, and the residual
+    # a fused [shortcut] reads, over the same event durations
+    es = 2.0 if mode == "bf16" else 4.0
+    small = np.array([bool(tc[i]) and not big3[i] for i in range(net.n)])
+    mem_bytes = 0.0
+    for i in np.nonzero(small)[0]:
+        c, h, w = net.layer_shape(int(i))
+        stride = int(sections[i][1].get("stride", 1))
+        sh = shapes[int(i)]
+        mem_bytes += es * per_gpu * (sh.c * (h * stride) * (w * stride) + sh.n * h * w) + es * sh.n * sh.c * sh.size * sh.size
+        if i + 1 < net.n and kinds[i + 1] == "shortcut" and mean_ms[i + 1] < 0.01:   # fused: its add is read by this launch
+            mem_bytes += es * per_gpu * sh.n * h * w
+    small_ms = float(mean_ms[small].sum())
+    hbm_part = None
+    if small.any() and small_ms > 0:
+        gbs = mem_bytes / (small_ms / 1000.0) / 1e9
+        hbm_part = {"launches_per_step": int(small.sum()), "ms_per_step": small_ms, "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"], "what": "1x1 layers and 3x3 layers with fewer than 64 input channels: HBM-bound launches of the same kernel"}
+    roofline = {"kernel": "conv_tc_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak,
+                "traffic": (lambda t: None if t is None else t[0] * per_gpu + t[1])(NCU_DRAM_TRAFFIC.get((workload, mode, size))),
+                "traffic_unit": "bytes per step per GPU (ncu dram read+write of all launches of this kernel)",
+                "launches_per_step": int(tc.sum()), "avg_launch_ms": tc_ms / max(int(tc.sum()), 1),
+                "share_of_step": tc_ms / float(mean_ms.sum()),
+                "peak_source": f"{peaks['source']}: cuBLAS bf16 {'burst' if alone else 'sustained'} {bf16_peak} TFLOP/s"
+                               + (" / 2 (TF32 runs at half the BF16 tensor rate)" if mode == "tf32" else ""),
+                "conv3x3_c64plus_tflops": big3_tflops,
+                "conv3x3_c64plus_frac": (big3_tflops / peak) if big3_tflops else None,
+                "hbm_bound_launches": hbm_part}
+
+    if not tc.any():
+        # a network of memory-bound layers only: algorithmic bytes per layer (4*(in+out) for maxpool and upsample,
+        # 12 B per element for shortcut, 8 B per element for route) over the event time, against the HBM copy rate
+        es_m = 2.0 if mode == "bf16" else 4.0
+        total_b, per_layer = 0.0, []
+        net_opt = synth.parse_cfg(cfg)[0][1]
+        prev = (int(net_opt["channels"]), int(net_opt["height"]), int(net_opt["width"]))
+        for i in range(net.n):
+            c, h, w = net.layer_shape(i)
+            out_e = per_gpu * c * h * w
+            in_e = per_gpu * prev[0] * prev[1] * prev[2]
+            b = {"maxpool": es_m * (in_e + out_e), "upsample": es_m * (in_e + out_e), "shortcut": 3 * es_m * out_e, "route": 2 * es_m * out_e}.get(kinds[i], 0.0)
+            per_layer.append({"layer": i, "kind": kinds[i], "GB": b / 1e9, "ms": float(mean_ms[i]), "GBps": b / (mean_ms[i] / 1000.0) / 1e9 if mean_ms[i] > 0 else None})
+            total_b += b
+            prev = (c, h, w)
+        gbs = total_b / (float(mean_ms.sum()) / 1000.0) / 1e9
+        roofline = {"kernel": "maxpool / upsample / shortcut / route kernels", "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"], "traffic": None, "per_layer": per_layer,
+                    "peak_source": f"{peaks['source']}: STREAM-style copy"}
+
+    xn = np.array([kn.startswith("xnor") for kn in kernels])
+    if xn.any() and float(mean_ms[xn].sum()) > float(mean_ms[tc].sum()):
+        # an xnor network: the popcount convolution dominates.  Work = one 32-bit xnor + popcount per 32 input channels
+        # per tap per filter per output pixel; no published peak exists for it, the fraction is against the integer
+        # pipe's popc issue rate (16 per SM per clock at the sampled clock is the figure NVIDIA documents for sm_100)
+        words = 0.0
+        for i in np.nonzero(xn)[0]:
+            c, h, w = net.layer_shape(int(i))
+            sh = shapes[int(i)]
+            words += float(per_gpu) * sh.n * sh.size * sh.size * ((sh.c + 31) // 32) * h * w
+        x_ms = float(mean_ms[xn].sum())
+        rate = words / (x_ms / 1000.0) / 1e12
+        roofline = {"kernel": "conv_xnor_kernel", "bound": "popc issue", "achieved": rate, "unit": "T word-popcounts/s", "peak": None, "frac": None,
+                    "binary_tops": rate * 64.0, "traffic": None, "launches_per_step": int(xn.sum()), "ms_per_step": x_ms,
+                    "share_of_step": x_ms / float(mean_ms.sum()),
+                    "what": "bit-packed xnor + popcount GEMM on the integer pipe; binary_tops counts 2 x 32 binary operations per word"}
+    return roofline, flops, kinds, kernels
+
+
+def side_config(workload: str, batch: int, size: int, mode_name: str, steps: int):
+    """Device-resident forward of another benchmark configuration on the current GPU: images/s from CUDA events
+    around `steps` forwards after three warm-ups, and the roofline object of its dominant kernel."""
+    import torch
+
+    import darknet_b200 as dn
+    from darknet_b200 import synth
+    cfg, metric, desc = workload_cfg(workload, batch, size)
+    d = tempfile.mkdtemp(prefix="dnb_side_")
+    write_net_files(d, cfg)
+    net = dn.Network(cfg, os.path.join(d, "net.weights"), dn.MODE_TF32 if mode_name == "tf32" else dn.MODE_BF16, text=True)
+    x_dev = torch.from_numpy(synth.seeded_input(cfg, 0, "uniform")).cuda()
+    stream = torch.cuda.current_stream()
+    for _ in range(3):
+        net.forward(x_dev)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for k in range(steps):
+        net.forward_timed(x_dev, slot=k)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    mean_ms = np.stack([net.timed_ms(k) for k in range(steps)]).astype(np.float64).mean(axis=0)
+    roofline, flops, _, _ = roofline_of(net, cfg, batch, mean_ms, mode_name, workload, size)
+    rec = {"metric": metric, "value": batch / (ms / 1000.0), "unit": UNIT, "ms_per_step": ms, "steps": steps, "dtype": mode_name,
+           "config": {"workload": f"{desc}, batch {batch}, device-resident"}, "gpu_launches": net.launches * steps,
+           "tflops_algorithmic": float(flops.sum()) / (ms / 1000.0) / 1e12, "roofline": roofline}
+    net.close()
+    return rec
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -419,84 +560,76 @@ def run_b200(args):
     d2h_last = 0 if kinds[-1] == "yolo" else 4 * per_gpu * net.outputs
     d2h = d2h_last + sum(4 * per_gpu * int(np.prod(net.layer_shape(i))) for i, k in enumerate(kinds) if k == "yolo")
     h2d = 4 * per_gpu * net.inputs
+    mean_ms = layer_ms.mean(axis=0)
+    launches_per_step = net.launches
+    extras = not args.no_extras and args.workload == "yolov3" and args.scaling == "weak"
+
+    # ---- what the host side can move: every rank copies one step's bytes (its images up, its head outputs down) between
+    # the same kind of pinned buffers and its GPU, all ranks at once, upload and download on their own streams, plain
+    # asynchronous copies and nothing else.  `e2e` can at best reach this.
+    copy_ceiling = None
+    if extras:
+        up, down = torch.cuda.Stream(), torch.cuda.Stream()
+        dev_out = torch.empty(max(d2h // 4, 1), dtype=torch.float32, device="cuda")
+        host_out = torch.empty(max(d2h // 4, 1), dtype=torch.float32).pin_memory()
+        dev_in = torch.empty_like(x_dev)
+
+        def copy_steps(k):
+            for _ in range(k):
+                with torch.cuda.stream(up):
+                    dev_in.copy_(x_host, non_blocking=True)
+                with torch.cuda.stream(down):
+                    host_out.copy_(dev_out, non_blocking=True)
+            up.synchronize()
+            down.synchronize()
+
+        copy_steps(2)
+        barrier()
+        t0 = time.perf_counter()
+        copy_steps(args.steps)
+        copy_ms_step = max_over_ranks((time.perf_counter() - t0) * 1000.0, "cuda") / args.steps
+        agg = (h2d + d2h) * world / (copy_ms_step / 1000.0) / 1e9
+        copy_ceiling = {"ms_per_step": copy_ms_step, "aggregate_gb_per_s": agg, "per_gpu_gb_per_s": agg / world,
+                        "images_per_s": total_images / (copy_ms_step / 1000.0),
+                        "e2e_fraction": copy_ms_step / e2e_ms_step,
+                        "what": f"{world} rank(s) at once: {h2d / 1e6:.0f} MB up and {d2h / 1e6:.0f} MB down per rank per step, pinned memory, one "
+                                "asynchronous copy each way on separate streams, no kernels; e2e_fraction = this time / the e2e step time"}
+        del dev_out, host_out, dev_in
+
+    # ---- strong scaling, the benchmark configuration's own split: --batch images cut into one contiguous slice per
+    # rank (replicated weights, no collective), the device-resident forward replayed as a CUDA graph
+    strong = None
+    if extras and world > 1:
+        s_per = shard_batch(args.batch, world, rank)[1]
+        s_cfg = workload_cfg(args.workload, s_per, args.size)[0]
+        s_net = dn.Network(s_cfg, os.path.join(wdir, "net.weights"), mode, text=True)
+        sx = x_dev[:s_per].contiguous()
+        s_net.enable_graph(True)
+        for _ in range(4):
+            s_net.forward(sx, stream=gstream.cuda_stream)
+        gstream.synchronize()
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(gstream)
+        for _ in range(args.steps):
+            s_net.forward(sx, stream=gstream.cuda_stream)
+        s1.record(gstream)
+        gstream.synchronize()
+        strong_ms = max_over_ranks(s0.elapsed_time(s1), "cuda") / args.steps
+        one_gpu = per_gpu / (graph_ms_step / 1000.0)          # a whole batch on one GPU, same replay, same run
+        strong = {"images_per_step": args.batch, "images_per_gpu": s_per, "ms_per_step": strong_ms, "value": args.batch / (strong_ms / 1000.0),
+                  "unit": UNIT, "one_gpu_value": one_gpu, "speedup": (args.batch / (strong_ms / 1000.0)) / one_gpu,
+                  "efficiency": (args.batch / (strong_ms / 1000.0)) / one_gpu / world,
+                  "what": f"{args.batch} images split over {world} GPUs, device-resident forward as one CUDA graph per rank, max over ranks; "
+                          "one_gpu_value is the same batch on one GPU measured in this run"}
+        s_net.close()
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    # ---- roofline of the dominant kernel: the tcgen05 convolution
-    kernels = [net.layer_kernel(i) for i in range(net.n)]
-    flops = np.zeros(net.n)
-    sections = synth.parse_cfg(cfg)[1:]
-    shapes = {s.index: s for s in synth.conv_shapes(cfg)}
-    for i, (k, opt) in enumerate(sections):
-        if k == "convolutional":
-            c, h, w = net.layer_shape(i)
-            s = shapes[i]
-            flops[i] = 2.0 * s.n * s.size * s.size * (s.c // s.groups) * h * w * per_gpu
-    tc = np.array([kn.startswith("tc_") for kn in kernels])
-    mean_ms = layer_ms.mean(axis=0)
-    tc_ms = float(mean_ms[tc].sum())
-    tc_flops = float(flops[tc].sum())
-    peaks = load_peaks()
-    achieved = tc_flops / (tc_ms / 1000.0) / 1e12 if tc_ms > 0 else 0.0
-    # a kernel timed alone is held against the burst figure, one timed inside a long step against the sustained one
-    alone = args.workload.startswith("conv")
-    bf16_peak = peaks["bf16_tflops"] if alone else peaks["bf16_sustained"]
-    peak = bf16_peak / (2.0 if args.mode == "tf32" else 1.0)
-    big3 = np.array([bool(tc[i]) and sections[i][1].get("size") == "3" and shapes[i].c >= 64 for i in range(net.n)])
-    big3_tflops = float(flops[big3].sum() / (mean_ms[big3].sum() / 1000.0) / 1e12) if big3.any() else None
-    # the other launches of the same kernel (1x1 layers, 3x3 layers with fewer than 64 input channels) are bound by
-    # HBM: algorithmic bytes = input + output of the layer in its storage type, the weights once, and the residual
-    # a fused [shortcut] reads, over the same event durations
-    es = 2.0 if args.mode == "bf16" else 4.0
-    small = np.array([bool(tc[i]) and not big3[i] for i in range(net.n)])
-    mem_bytes = 0.0
-    for i in np.nonzero(small)[0]:
-        c, h, w = net.layer_shape(int(i))
-        stride = int(sections[i][1].get("stride", 1))
-        sh = shapes[int(i)]
-        mem_bytes += es * per_gpu * (sh.c * (h * stride) * (w * stride) + sh.n * h * w) + es * sh.n * sh.c * sh.size * sh.size
-        if i + 1 < net.n and kinds[i + 1] == "shortcut" and mean_ms[i + 1] < 0.01:   # fused: its add is read by this launch
-            mem_bytes += es * per_gpu * sh.n * h * w
-    small_ms = float(mean_ms[small].sum())
-    hbm_part = None
-    if small.any() and small_ms > 0:
-        gbs = mem_bytes / (small_ms / 1000.0) / 1e9
-        hbm_part = {"launches_per_step": int(small.sum()), "ms_per_step": small_ms, "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": gbs / peaks["hbm_gbs"], "what": "1x1 layers and 3x3 layers with fewer than 64 input channels: HBM-bound launches of the same kernel"}
-    roofline = {"kernel": "conv_tc_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak,
-                "traffic": (lambda t: None if t is None else t[0] * per_gpu + t[1])(NCU_DRAM_TRAFFIC.get((args.workload, args.mode, args.size))),
-                "traffic_unit": "bytes per step per GPU (ncu dram read+write of all launches of this kernel)",
-                "launches_per_step": int(tc.sum()), "avg_launch_ms": tc_ms / max(int(tc.sum()), 1),
-                "share_of_step": tc_ms / float(mean_ms.sum()),
-                "peak_source": f"{peaks['source']}: cuBLAS bf16 {'burst' if alone else 'sustained'} {bf16_peak} TFLOP/s"
-                               + (" / 2 (TF32 runs at half the BF16 tensor rate)" if args.mode == "tf32" else ""),
-                "conv3x3_c64plus_tflops": big3_tflops,
-                "conv3x3_c64plus_frac": (big3_tflops / peak) if big3_tflops else None,
-                "hbm_bound_launches": hbm_part}
-
-    if not tc.any():
-        # a network of memory-bound layers only: algorithmic bytes per layer (4*(in+out) for maxpool and upsample,
-        # 12 B per element for shortcut, 8 B per element for route) over the event time, against the HBM copy rate
-        es_m = 2.0 if args.mode == "bf16" else 4.0
-        total_b, per_layer = 0.0, []
-        net_opt = synth.parse_cfg(cfg)[0][1]
-        prev = (int(net_opt["channels"]), int(net_opt["height"]), int(net_opt["width"]))
-        for i in range(net.n):
-            c, h, w = net.layer_shape(i)
-            out_e = per_gpu * c * h * w
-            in_e = per_gpu * prev[0] * prev[1] * prev[2]
-            b = {"maxpool": es_m * (in_e + out_e), "upsample": es_m * (in_e + out_e), "shortcut": 3 * es_m * out_e, "route": 2 * es_m * out_e}.get(kinds[i], 0.0)
-            per_layer.append({"layer": i, "kind": kinds[i], "GB": b / 1e9, "ms": float(mean_ms[i]), "GBps": b / (mean_ms[i] / 1000.0) / 1e9 if mean_ms[i] > 0 else None})
-            total_b += b
-            prev = (c, h, w)
-        gbs = total_b / (float(mean_ms.sum()) / 1000.0) / 1e9
-        roofline = {"kernel": "maxpool / upsample / shortcut / route kernels", "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": gbs / peaks["hbm_gbs"], "traffic": None, "per_layer": per_layer,
-                    "peak_source": f"{peaks['source']}: STREAM-style copy"}
+    roofline, flops, kinds, kernels = roofline_of(net, cfg, per_gpu, mean_ms, args.mode, args.workload, args.size)
 
     if args.layers:
         with open(args.layers, "w") as f:
@@ -506,8 +639,23 @@ def run_b200(args):
                 f.write(f"{i} {kinds[i]} {kernels[i]} {c} {h} {w} {mean_ms[i]:.4f} {flops[i] / 1e9:.2f} "
                         f"{(flops[i] / (mean_ms[i] / 1000.0) / 1e12) if mean_ms[i] > 0 else 0:.1f}\n")
 
+    # ---- the other benchmark configurations that fit one GPU, device-resident (N = 1 only)
+    other = None
+    if extras and world == 1:
+        net.close()
+        del x_dev
+        torch.cuda.empty_cache()
+        other = {}
+        for name, batch, o_mode in (("resnet50", 256, args.mode), ("darknet19-xnor", 128, "tf32")):
+            try:
+                other[name] = side_config(name, batch, 224, o_mode, max(args.steps, 5))
+            except Exception as e:   # noqa: BLE001
+                other[name] = {"unavailable": repr(e)[:300]}
+
     cpu = None
-    if world == 1 and args.cpu_sample > 0:
+    if args.cpu_sample > 0:
+        n_cpu = args.cpu_sample if world == 1 else 1    # rank 0's host cores are shared with the other ranks' processes by then idle
+        args.cpu_sample = n_cpu
         ref = CpuReference(args.workload, args.size, args.cpu_sample)
         ref.seconds()   # first touch of the reference's freshly allocated buffers
         sec = ref.seconds()
@@ -539,8 +687,9 @@ def run_b200(args):
                     "blocking_predict": {"value": total_images / (sync_ms_step / 1000.0), "ms_per_step": sync_ms_step}},
             "graph_replay": {"value": total_images / (graph_ms_step / 1000.0), "unit": UNIT, "ms_per_step": graph_ms_step,
                              "what": "the device-resident forward as one CUDA graph launch per step (dnb_network_enable_graph)"},
-            "gpu_launches": net.launches * args.steps,
-            "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "reference_gpu": ref_gpu}
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "reference_gpu": ref_gpu,
+            "strong": strong, "host_copy_ceiling": copy_ceiling, "other_configs": other}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -64,6 +64,8 @@ SIGNATURES = {
     "dnb_conv_xnor_forward_static": (_I, [C.POINTER(ConvDesc), _TP, _P, _P, _P, _P, _TP, _P]),
     "dnb_conv_plan_set_diagnostics": (_I, [_P, C.c_longlong, _I]),
     "dnb_conv_plan_kernel": (C.c_char_p, [_P]),
+    "dnb_conv_plan_describe": (_I, [_P, C.c_char_p, _I]),
+    "dnb_network_layer_describe": (_I, [_P, _I, C.c_char_p, _I]),
     "dnb_maxpool_forward": (_I, [_TP, _TP, _I, _I, _I, _P]),
     "dnb_upsample_forward": (_I, [_TP, _TP, _I, _F, _P]),
     "dnb_shortcut_forward": (_I, [_TP, _TP, _TP, _F, _F, _I, _P]),

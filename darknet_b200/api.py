@@ -67,6 +67,12 @@ class ConvPlan:
     def kernel(self) -> str:
         return lib().dnb_conv_plan_kernel(self.handle).decode()
 
+    def describe(self) -> str:
+        """Kernel and tiling of the plan as one line (tiling fields are known after the first forward)."""
+        buf = C.create_string_buffer(256)
+        check(lib().dnb_conv_plan_describe(self.handle, buf, 256))
+        return buf.value.decode()
+
     def forward(self, x: Tensor, y: Tensor, y2: Tensor | None = None, stream=None):
         check(lib().dnb_conv_forward(self.handle, C.byref(x), C.byref(y), C.byref(y2) if y2 is not None else None, _stream(stream)))
 
@@ -156,6 +162,11 @@ class Network:
 
     def layer_kernel(self, i: int) -> str:
         return lib().dnb_network_layer_kernel(self.handle, i).decode()
+
+    def layer_describe(self, i: int) -> str:
+        buf = C.create_string_buffer(256)
+        check(lib().dnb_network_layer_describe(self.handle, i, buf, 256))
+        return buf.value.decode()
 
     def predict_ptr(self, host_ptr: int) -> np.ndarray:
         """network_predict on a raw host pointer to batch*inputs floats."""

@@ -72,6 +72,8 @@ struct alignas(64) TcArgs {
                           // 32 (dnb_conv_plan_set_diagnostics): each CTA withholds the last operand load of its first tile, so a bounded wait runs out
     long long wait_limit; // bound of every device-side wait, SM clock cycles
     int stage_bufs;       // staging buffers of the epilogue: 2, or 4 with a fused residual (tiles land in them first)
+    int pair;             // 1: clusters of two CTAs share every MMA (cta_group::2); total_tiles then counts PAIRS of pixel tiles,
+                          // b_bytes and the weight map's box cover half a filter tile, bn is 256
     int ctas_per_sm;      // 2 for narrow tiles (TMEM and shared memory are sized so that two CTAs share an SM), else 1
     int a_bytes, b_bytes; // shared-memory bytes of one stage's activation / weight tile (1024-multiples)
     int store_row_bytes;  // bytes of one staged output row (128, 64 or 32) = swizzle span of tmy

@@ -93,6 +93,18 @@ extern "C" const char *dnb_conv_plan_kernel(const dnb_conv_plan *p)
     return p->stem_tc ? "stem_tc_tf32" : kKernelNames[p->kernel];
 }
 
+extern "C" int dnb_conv_plan_describe(const dnb_conv_plan *p, char *buf, int len)
+{
+    if (!p || !buf || len < 1) DNB_FAIL(DNB_EINVAL, "conv describe: bad argument");
+    const TcArgs &a = p->tc;
+    if ((p->kernel == K_TC_TF32 || p->kernel == K_TC_BF16) && p->tc_x_ptr)
+        snprintf(buf, len, "%s pair=%d halo=%d bn=%d tile=%dx%dx%d tiles=%d stages=%d ctas_per_sm=%d srb=%d", kKernelNames[p->kernel], a.pair, a.halo,
+                 a.bn, a.wt, a.ht, a.bt, a.total_tiles, a.stages, a.ctas_per_sm, a.store_row_bytes);
+    else
+        snprintf(buf, len, "%s", dnb_conv_plan_kernel(p));
+    return DNB_OK;
+}
+
 template <typename T>
 static int upload(T **dst, const std::vector<T> &src)
 {
@@ -258,11 +270,26 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
         a.bn /= 2;
         a.n_tiles = (p->n_pad + a.bn - 1) / a.bn;
     }
-    a.total_tiles = ptiles * a.n_tiles;
+    // CTA pairs (cta_group::2): for layers whose filters come in whole tiles of 256 and whose K loop is long enough to
+    // be bound by operand traffic.  Each CTA of a pair loads its own 128 pixels and half of the 256-filter weight tile:
+    // a third fewer bytes from L2 into shared memory per MMA, and 32 KB ring slots (six of them) instead of 48 KB (four).
+    // DNB_TC_PAIR: 0 never, 1 (default) the 3x3 layers, 2 every layer the geometry allows.
+    a.pair = 0;
+    {
+        const char *e = getenv("DNB_TC_PAIR");
+        const int knob = e ? atoi(e) : 1;
+        const bool legal = !a.halo && a.row_bytes == 128 && g.n % 256 == 0 && (ptiles + 1) / 2 * (g.n / 256) >= sm_count() / 2;
+        if (legal && (knob == 2 || (knob == 1 && g.size >= 3))) {
+            a.pair = 1;
+            a.bn = 256;
+            a.n_tiles = p->n_pad / 256;
+        }
+    }
+    a.total_tiles = a.pair ? (ptiles + 1) / 2 * a.n_tiles : ptiles * a.n_tiles;
     a.n_pad = p->n_pad;
     a.n_tot = a.n_tiles * a.bn;
     a.a_bytes = 128 * a.row_bytes;
-    a.b_bytes = round_up(a.bn * a.row_bytes, 1024);
+    a.b_bytes = round_up((a.pair ? a.bn / 2 : a.bn) * a.row_bytes, 1024);
     const int max_smem = conv_tc_max_smem();
     if (max_smem <= 0) DNB_FAIL(DNB_ECUDA, "conv: cannot query shared memory of the current device");
     // staged output rows: the widest of 128 / 64 / 32 bytes that the output pitch allows and that keeps
@@ -283,7 +310,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     // Narrow tiles (bn <= 128) leave TMEM and, with a short ring, shared memory for a second CTA on the SM:
     // twice the warps hide the per-tile hand-offs that dominate layers with few K iterations.
     a.ctas_per_sm = 1;
-    a.stage_bufs = residual ? 4 : 2;
+    a.stage_bufs = (residual && !a.pair) ? 4 : 2;   // a pair reads the residual with plain loads: nothing lands in the staging buffers
     a.debug = (getenv("DNB_TC_DEBUG") ? atoi(getenv("DNB_TC_DEBUG")) : 0) | p->debug_bits;
     a.wait_limit = p->wait_limit > 0 ? p->wait_limit : DEFAULT_WAIT_CYCLES;
     int stages = 0;
@@ -314,7 +341,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
         stages = 2;
     }
     if (!a.halo) {
-        if (allow2 && a.tmem_cols <= 256) {
+        if (allow2 && a.tmem_cols <= 256 && !a.pair) {
             const int max2 = getenv("DNB_TC_MAX2") ? atoi(getenv("DNB_TC_MAX2")) : 4;   // ring slots per CTA when two share the SM
             const long budget = (228L * 1024) / 2 - 2048;   // per CTA when two share the SM (1 KB each is reserved by the system)
             for (int srb2 = srb; srb2 >= min_srb; srb2 /= 2) {   // narrower staged rows if that is what makes two CTAs fit
@@ -369,7 +396,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     {
         uint64_t dims[3] = {(uint64_t)p->c_pad, (uint64_t)p->n_pad, (uint64_t)a.taps};
         uint64_t strides[2] = {(uint64_t)p->c_pad * es, (uint64_t)p->c_pad * es * p->n_pad};
-        uint32_t box[3] = {(uint32_t)a.bk, (uint32_t)a.bn, 1u};
+        uint32_t box[3] = {(uint32_t)a.bk, (uint32_t)(a.pair ? a.bn / 2 : a.bn), 1u};
         DNB_TRY(encode_tensor_map(&a.tmw, bf16, 3, p->w_tc, dims, strides, box, a.row_bytes));
     }
     if (y_nhwc) {

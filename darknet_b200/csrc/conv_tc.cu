@@ -82,7 +82,11 @@ __device__ __forceinline__ float act_apply(float x, int runtime_act)
 // CPC: output columns per staged chunk (16, 32 or 64); OUT_BF16: storage type of the operands and of the
 // NHWC output (bf16 for BF16 plans, f32 with TF32 products otherwise).
 // One staged row is CPC * sizeof(output element) bytes = the swizzle span of the store map.
-template <int ACT, int CPC, bool OUT_BF16, int ACT2>
+// PAIR: the kernel runs as clusters of two CTAs that share every MMA (cta_group::2): one tile index names two
+// adjacent pixel tiles (one per CTA) under one 256-filter tile; each CTA loads its own 128 pixels and HALF of the
+// weight tile, so a third fewer operand bytes cross L2 -> shared memory per MMA and the ring is six slots deep.
+// The even CTA issues the MMAs for both; each CTA drains its own 128 accumulator rows.
+template <int ACT, int CPC, bool OUT_BF16, int ACT2, bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS)
 conv_tc_kernel(const __grid_constant__ TcArgs a)
 {
@@ -107,6 +111,8 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     volatile int *abort_flag = &sh->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;   // 0: the CTA that issues the pair's MMAs
+    const bool leader = cta_rank == 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < MAX_STAGES; ++s) {
@@ -119,7 +125,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&sh->acc_full[i]), 1);
-            mbar_init(smem_u32(&sh->acc_empty[i]), 4);
+            mbar_init(smem_u32(&sh->acc_empty[i]), PAIR ? 8 : 4);   // the epilogue warps of both CTAs of a pair
         }
         for (int i = 0; i < MAX_RES_BUFS; ++i) mbar_init(smem_u32(&sh->res_full[i]), 1);
         sh->abort_flag = 0;
@@ -128,11 +134,17 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     }
     const uint32_t tmem_cols = (uint32_t)a.tmem_cols, acc_stride = tmem_cols / 2;
     if (warp == 1) {  // TMEM: two accumulators of tmem_cols/2 columns each (512 in all for 256-filter tiles), whole warp
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(tmem_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {   // the same warp of both CTAs, the same shared-memory offset for the result
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();   // the other CTA's barriers are initialised before anything is signalled across the pair
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
 
@@ -144,13 +156,17 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     const int tiles_w = a.tiles_w, tiles_h = a.tiles_h, ptiles_wh = tiles_w * tiles_h;
     const int wt = a.wt, ht = a.ht, bt = a.bt, row_bytes = a.row_bytes;
     const uint32_t a_bytes = a.a_bytes;
-    const int grid_stride = gridDim.x;
+    const int grid_stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    // tile index -> pixel tile of this CTA.  The last pair of an odd number of pixel tiles gives its second CTA a
+    // tile past the batch: its loads are zero-filled, its stores are skipped.
+    auto pixel_tile = [&](int tile) { return PAIR ? 2 * (tile / n_tiles) + (int)cta_rank : tile / n_tiles; };
     const long long wait_limit = a.wait_limit;
 
     if (warp == 0) {
         // ---------------- TMA producer: one thread runs the loop, the other lanes wait at the __syncwarp
         const int ksize = a.g.size, cstride = a.g.stride, cpad = a.g.pad;
-        const uint32_t tx_bytes = 128u * row_bytes + (uint32_t)bn * row_bytes;
+        const uint32_t tx_bytes = 128u * row_bytes + (uint32_t)(PAIR ? bn >> 1 : bn) * row_bytes;
         const CUtensorMap *maps = a.tmx;
         const CUtensorMap *wmap = &a.tmw;
         int *status = a.status;
@@ -187,12 +203,12 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 }
             }
         } else
-        for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok; tile += grid_stride) {
-            const int nt = tile % n_tiles, pt = tile / n_tiles;
+        for (int tile = first_tile; lane == 0 && tile < total_tiles && ok; tile += grid_stride) {
+            const int nt = tile % n_tiles, pt = pixel_tile(tile);
             const int ow0 = (pt % tiles_w) * wt;
             const int oh0 = ((pt / tiles_w) % tiles_h) * ht;
             const int b0 = (pt / ptiles_wh) * bt;
-            const int n0 = nt * bn;
+            const int n0 = nt * bn + (PAIR ? (int)cta_rank * (bn >> 1) : 0);   // a pair's CTAs load one half of the filter tile each
             int kh = 0, kw = 0;
             for (int tap = 0; tap < taps && ok; ++tap) {
                 // input row = oh*stride + kh - pad = stride*(oh + q) + parity
@@ -205,12 +221,19 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                     if (!ok) break;
                     // wait-expiry test (debug bit 32): the last operand load of this CTA's first tile is never
                     // requested, so the MMA role's wait for it runs out and the CTA takes the abort path
-                    if (withhold && tile == (int)blockIdx.x && tap == taps - 1 && cb == c_blocks - 1) { ok = false; break; }
+                    if (withhold && tile == first_tile && tap == taps - 1 && cb == c_blocks - 1) { ok = false; break; }
                     const uint32_t bar = full0 + 8 * stage;
                     const uint32_t sa = ring + stage * stage_bytes;
-                    mbar_expect_tx(bar, tx_bytes);
-                    tma_load_4d(sa, mx, bar, cb * bk, ow0 + qw, oh0 + qh, b0);
-                    tma_load_3d(sa + a_bytes, wmap, bar, cb * bk, n0, tap);
+                    if (PAIR) {
+                        // one barrier, in the even CTA, counts the bytes of both CTAs' loads of this slot
+                        if (leader) mbar_expect_tx(bar, 2u * tx_bytes);
+                        tma_load_4d_pair(sa, mx, bar, cb * bk, ow0 + qw, oh0 + qh, b0);
+                        tma_load_3d_pair(sa + a_bytes, wmap, bar, cb * bk, n0, tap);
+                    } else {
+                        mbar_expect_tx(bar, tx_bytes);
+                        tma_load_4d(sa, mx, bar, cb * bk, ow0 + qw, oh0 + qh, b0);
+                        tma_load_3d(sa + a_bytes, wmap, bar, cb * bk, n0, tap);
+                    }
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
                 if (++kw == ksize) { kw = 0; ++kh; }
@@ -224,7 +247,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         // sits after the k loop.
         constexpr bool is_bf16 = OUT_BF16;       // operands and channels-last output share the storage type
         const uint32_t fmt = is_bf16 ? 1u : 2u;  // BF16 : TF32
-        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bn >> 3) << 17) | ((128u >> 4) << 24);
+        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bn >> 3) << 17) | (((PAIR ? 256u : 128u) >> 4) << 24);
         const int k_steps = row_bytes / 32;      // one MMA consumes 32 bytes of K per row
         const uint64_t da0 = make_smem_desc(ring, row_bytes), db0 = make_smem_desc(ring + a_bytes, row_bytes);
         const uint64_t slot_step = stage_bytes >> 4;   // descriptor address field counts 16-byte units
@@ -282,7 +305,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 if (ok) umma_commit(smem_u32(&sh->acc_full[acc]));
             }
         } else
-        for (int tile = blockIdx.x; lane == 0 && tile < total_tiles && ok; tile += grid_stride, ++it) {
+        for (int tile = first_tile; lane == 0 && leader && tile < total_tiles && ok; tile += grid_stride, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             ok = mbar_wait_thread(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1, abort_flag, status, WAIT_ACC_EMPTY, wait_limit);
@@ -294,6 +317,11 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 if (!ok) break;
                 tc_fence_after();
                 if (dbg_mma & 16) {
+                } else if (PAIR) {   // the same descriptors address both CTAs' shared memory; row_bytes is 128 in pair mode
+                    umma_pair<is_bf16>(d_tmem, da, db, idesc, ki != 0);
+                    umma_pair<is_bf16>(d_tmem, da + 2, db + 2, idesc, 1u);
+                    umma_pair<is_bf16>(d_tmem, da + 4, db + 4, idesc, 1u);
+                    umma_pair<is_bf16>(d_tmem, da + 6, db + 6, idesc, 1u);
                 } else if (k_steps == 4) {
                     umma<is_bf16>(d_tmem, da, db, idesc, ki != 0);
                     umma<is_bf16>(d_tmem, da + 2, db + 2, idesc, 1u);
@@ -302,11 +330,14 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 } else {
                     for (int k = 0; k < k_steps; ++k) umma<is_bf16>(d_tmem, da + 2 * k, db + 2 * k, idesc, (ki | k) != 0);
                 }
-                umma_commit(empty0 + 8 * stage);   // frees the slot when these MMAs retire
+                // frees the slot (in both CTAs of a pair) when these MMAs retire
+                if (PAIR) umma_commit_pair(empty0 + 8 * stage); else umma_commit(empty0 + 8 * stage);
                 da += slot_step; db += slot_step;
                 if (++stage == stages) { stage = 0; phase ^= 1; da = da0; db = db0; }
             }
-            if (ok) umma_commit(smem_u32(&sh->acc_full[acc]));   // accumulator complete when all MMAs above retire
+            if (ok) {   // accumulator complete (in both CTAs of a pair) when all MMAs above retire
+                if (PAIR) umma_commit_pair(smem_u32(&sh->acc_full[acc])); else umma_commit(smem_u32(&sh->acc_full[acc]));
+            }
         }
         __syncwarp();
     } else {
@@ -319,8 +350,13 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         float *const y_nchw = a.y_nchw;
         const int runtime_act = a.ep.activation, do_round = a.ep.round_tf32;
         constexpr bool residual = ACT2 != ACT2_NONE;
+        // A CTA pair reads the residual with plain 16-byte loads, one staged chunk ahead, instead of TMA tiles into the
+        // staging buffers: residual tile loads inside the pair kernel raised an illegal-instruction fault on B200 whose
+        // cause was not found, so that combination is not built.  Each thread reads its own pixel's 128 contiguous bytes.
+        constexpr bool res_direct = residual && PAIR;
+        constexpr bool res_tiles = residual && !PAIR;
         const CUtensorMap *rmap = &a.tmr;
-        const uint32_t buf_mask = residual ? 3u : 1u;   // staging buffers in rotation
+        const uint32_t buf_mask = res_tiles ? 3u : 1u;   // staging buffers in rotation
         constexpr int res_ahead = 3;   // residual tiles requested ahead of the chunk being finished (of four buffers)
         const int act2 = a.ep.activation2;
         const float res_alpha = a.ep.alpha, res_beta = a.ep.beta;
@@ -337,11 +373,13 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         // and does not stop at tile boundaries: what bounds a layer with a fused residual is how many bytes of it
         // are in flight, so the requests must not drain while the epilogue waits for the next accumulator.
         uint32_t pf_count = 0;                 // chunks requested so far (buffer = count & 3)
-        int pf_tile = blockIdx.x, pf_c0 = 0;   // the next chunk to request
+        int pf_tile = first_tile, pf_c0 = 0;   // the next chunk to request
         const int dbg = a.debug;
+        // diagnostics: bit 1 no residual loads at all, bit 64 none in the second CTA of a pair (wrong results, no waits)
+        const bool no_res = (dbg & 1) != 0;
         auto request_residual = [&]() {
-            if (pf_tile >= total_tiles || (dbg & 1)) return;
-            const int nt = pf_tile % n_tiles, pt = pf_tile / n_tiles;
+            if (pf_tile >= total_tiles || no_res) return;
+            const int nt = pf_tile % n_tiles, pt = pixel_tile(pf_tile);
             const int ow0 = (pt % tiles_w) * wt, oh0 = ((pt / tiles_w) % tiles_h) * ht, b0 = (pt / ptiles_wh) * bt;
             const uint32_t rb = pf_count & 3u, bar = smem_u32(&sh->res_full[rb]);
             mbar_expect_tx(bar, 128u * srb);
@@ -350,14 +388,16 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             pf_c0 += CPC;
             if (pf_c0 >= bn) { pf_c0 = 0; pf_tile += grid_stride; }
         };
-        if (residual && store_thread)
+        if (res_tiles && store_thread)
             for (int d = 0; d < res_ahead; ++d) request_residual();
+        const uint8_t *const res_base = reinterpret_cast<const uint8_t *>(a.ep.residual);
+        const size_t res_pix_bytes = (size_t)a.ep.res_cpitch * (OUT_BF16 ? 2 : 4);
         const float *const ep_scale = a.ep.scale, *const ep_shift = a.ep.shift;
         const int n_pad = a.n_pad;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += grid_stride, ++it) {
+        for (int tile = first_tile; tile < total_tiles; tile += grid_stride, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            const int nt = tile % n_tiles, pt = tile / n_tiles;
+            const int nt = tile % n_tiles, pt = pixel_tile(tile);
             const int ow0 = (pt % tiles_w) * wt, oh0 = ((pt / tiles_w) % tiles_h) * ht, b0 = (pt / ptiles_wh) * bt;
             const int ow = ow0 + wl, oh = oh0 + hl, b = b0 + bl;
             const bool pix_ok = ow < g.out_w && oh < g.out_h && b < g.batch;
@@ -381,10 +421,18 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             // arithmetic, the staged row, the store.  The loop is deliberately NOT unrolled: its body has to
             // stay resident in the instruction cache next to the MMA warp's loop.
             const size_t plane = (size_t)g.out_h * g.out_w;
+            constexpr int RES_V = CPC * (OUT_BF16 ? 2 : 4) / 16;      // 16-byte pieces of a staged row
+            // direct residual: this pixel's row of the residual tensor, the next chunk's 128 bytes always in flight
+            const uint4 *res_row = nullptr;
+            uint4 res_next[res_direct ? RES_V : 1];
+            if (res_direct) {
+                if (pix_ok && !no_res) res_row = reinterpret_cast<const uint4 *>(res_base + (((size_t)b * g.out_h + oh) * g.out_w + ow) * res_pix_bytes + (size_t)nt * bn * (OUT_BF16 ? 2 : 4));
+#pragma unroll
+                for (int q = 0; q < RES_V; ++q) res_next[q] = res_row ? __ldg(res_row + q) : make_uint4(0u, 0u, 0u, 0u);
+            }
 #pragma unroll 1
             for (int c0 = (dbg & 8) ? bn : 0; c0 < bn; c0 += CPC) {
                 uint32_t r[CPC];
-                constexpr int RES_V = CPC * (OUT_BF16 ? 2 : 4) / 16;      // 16-byte pieces of a staged row
 #pragma unroll
                 for (int u = 0; u < CPC / 16; ++u) {
                     if (c0 + 16 * u < bn) {
@@ -396,10 +444,19 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 }
                 tmem_ld_wait();
                 uint4 res[RES_V];
-                if (residual) {
+                if (res_direct) {
+#pragma unroll
+                    for (int q = 0; q < RES_V; ++q) res[q] = res_next[q];
+                    if (c0 + CPC < bn && res_row) {
+                        const uint4 *nx = res_row + (size_t)(c0 + CPC) * (OUT_BF16 ? 2 : 4) / 16;
+#pragma unroll
+                        for (int q = 0; q < RES_V; ++q) res_next[q] = __ldg(nx + q);
+                    }
+                }
+                if (res_tiles) {
                     // this chunk's residual tile (TMA zero-fills pixels and channels outside the tensor)
                     const uint32_t rb = chunk_count & 3u;
-                    if (!(dbg & 1)) mbar_wait(smem_u32(&sh->res_full[rb]), (chunk_count >> 2) & 1, abort_flag, status, WAIT_RESIDUAL, 0, wait_limit);
+                    if (!no_res) mbar_wait(smem_u32(&sh->res_full[rb]), (chunk_count >> 2) & 1, abort_flag, status, WAIT_RESIDUAL, 0, wait_limit);
                     const uint8_t *rrow = stage_out + (size_t)rb * 128 * srb + (size_t)m * srb;
 #pragma unroll
                     for (int q = 0; q < RES_V; ++q) res[q] = *reinterpret_cast<const uint4 *>(rrow + ((q ^ q_xor) << 4));
@@ -441,7 +498,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                     }
                 }
                 const uint32_t buf = chunk_count & buf_mask;
-                if (!residual) {
+                if (!res_tiles) {
                     if (store_thread && chunk_count >= 2) tma_store_wait_read1();   // the store that last read this buffer is done
                     epilogue_bar();
                 }   // with a residual the buffer is this thread's to overwrite: its tile landed after that store, and
@@ -469,9 +526,9 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 epilogue_bar();
                 if (store_thread) {
                     // the TMA unit clips the box at the tensor's extents: ragged tiles need no predicates
-                    if (y_nhwc && !(dbg & 2)) tma_store_4d(ymap, smem_u32(stage_out + (size_t)buf * 128 * srb), nl0, ow0, oh0, b0);
+                    if (y_nhwc && !(dbg & 2) && (!PAIR || b0 < g.batch)) tma_store_4d(ymap, smem_u32(stage_out + (size_t)buf * 128 * srb), nl0, ow0, oh0, b0);
                     tma_store_commit();
-                    if (residual) {
+                    if (res_tiles) {
                         // the tile three chunks on goes into the buffer of the previous chunk, once that chunk's
                         // store has read it (only the store just issued may still be pending)
                         if (!(dbg & 4)) tma_store_wait_read1();
@@ -494,7 +551,9 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sh->acc_empty[acc]));
+            if (lane == 0) {   // a pair's accumulator is free when the epilogues of both CTAs have drained their rows
+                if (PAIR) mbar_arrive_leader(smem_u32(&sh->acc_empty[acc])); else mbar_arrive(smem_u32(&sh->acc_empty[acc]));
+            }
         }
         if (store_thread) tma_store_wait_all();
     }
@@ -506,10 +565,15 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     }
     tc_fence_before();
     __syncthreads();
+    // A pair leaves together: neither CTA may exit, or free TMEM, while the other can still signal its barriers or
+    // run MMAs into its TMEM.  Every wait above is bounded, so both CTAs get here.
+    if (PAIR) cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
+    if (PAIR) cluster_sync_all();
 }
 
 // ------------------------------------------------------------------ host side
@@ -532,6 +596,27 @@ int conv_tc_max_smem()
     return v;
 }
 
+// Resident clusters of two CTAs of a pair-mode kernel with `smem` bytes of dynamic shared memory (cached per kernel).
+template <typename K>
+static int max_pair_clusters(K kernel, size_t smem)
+{
+    static int cached = 0;
+    static size_t cached_smem = 0;
+    if (cached && cached_smem == smem) return cached;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (unsigned)(sm_count() / 2));
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = sm_count() / 2; }
+    cached = n; cached_smem = smem;
+    return n;
+}
+
 int launch_conv_tc(const TcArgs &a, cudaStream_t s)
 {
     const size_t smem = conv_tc_smem_bytes(a);
@@ -545,12 +630,33 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
     // dynamic shared memory is per kernel symbol and cheap, so it is set on every launch
 #define DNB_TC_LAUNCH(ACT, CPC, OBF, ACT2)                                                                                       \
     do {                                                                                                                         \
-        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<ACT, CPC, OBF, ACT2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)); \
-        conv_tc_kernel<ACT, CPC, OBF, ACT2><<<grid, TC_THREADS, smem, s>>>(a);                                                  \
+        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<ACT, CPC, OBF, ACT2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)); \
+        conv_tc_kernel<ACT, CPC, OBF, ACT2, false><<<grid, TC_THREADS, smem, s>>>(a);                                           \
+    } while (0)
+    // pair mode: clusters of two CTAs, one CTA per SM, as many clusters as are resident at once (or pair tiles, if fewer)
+#define DNB_TC_LAUNCH_PAIR(ACT, CPC, OBF, ACT2)                                                                                  \
+    do {                                                                                                                         \
+        auto kern = conv_tc_kernel<ACT, CPC, OBF, ACT2, true>;                                                                   \
+        DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));                            \
+        const int clusters_max = max_pair_clusters(kern, smem);                                                                  \
+        const int clusters = a.total_tiles < clusters_max ? a.total_tiles : clusters_max;                                        \
+        cudaLaunchConfig_t cfg = {};                                                                                             \
+        cfg.gridDim = dim3(2 * (unsigned)clusters);                                                                              \
+        cfg.blockDim = dim3(TC_THREADS);                                                                                         \
+        cfg.dynamicSmemBytes = smem;                                                                                             \
+        cfg.stream = s;                                                                                                          \
+        cudaLaunchAttribute attr[1];                                                                                             \
+        attr[0].id = cudaLaunchAttributeClusterDimension;                                                                        \
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;                                \
+        cfg.attrs = attr; cfg.numAttrs = 1;                                                                                      \
+        DNB_CUDA(cudaLaunchKernelEx(&cfg, kern, a));                                                                             \
     } while (0)
 #define DNB_TC_LAUNCH_ACT(ACT, ACT2)                                        \
     do {                                                                    \
-        if (!obf && cpc == 32) DNB_TC_LAUNCH(ACT, 32, false, ACT2);         \
+        if (a.pair && !obf && cpc == 32) DNB_TC_LAUNCH_PAIR(ACT, 32, false, ACT2); \
+        else if (a.pair && obf && cpc == 64) DNB_TC_LAUNCH_PAIR(ACT, 64, true, ACT2); \
+        else if (a.pair) DNB_FAIL(DNB_EINVAL, "conv_tc: pair mode needs 128-byte staged rows"); \
+        else if (!obf && cpc == 32) DNB_TC_LAUNCH(ACT, 32, false, ACT2);    \
         else if (!obf && cpc == 16) DNB_TC_LAUNCH(ACT, 16, false, ACT2);    \
         else if (obf && cpc == 64) DNB_TC_LAUNCH(ACT, 64, true, ACT2);      \
         else if (obf && cpc == 32) DNB_TC_LAUNCH(ACT, 32, true, ACT2);      \
@@ -566,12 +672,13 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
     } else {
         // fused shortcut: the two pairs the reference's cfgs use (yolov3: leaky conv, linear shortcut; resnet:
         // linear conv, leaky shortcut) are compile-time, every other pair takes the run-time switches
-        if (a.stage_bufs != 4) DNB_FAIL(DNB_EINVAL, "conv_tc: a fused residual needs four staging buffers");
+        if (a.stage_bufs != (a.pair ? 2 : 4)) DNB_FAIL(DNB_EINVAL, "conv_tc: a fused residual needs four staging buffers (two in pair mode)");
         if (a.ep.activation == DNB_LEAKY && a.ep.activation2 == DNB_LINEAR) DNB_TC_LAUNCH_ACT(DNB_LEAKY, DNB_LINEAR);
         else if (a.ep.activation == DNB_LINEAR && a.ep.activation2 == DNB_LEAKY) DNB_TC_LAUNCH_ACT(DNB_LINEAR, DNB_LEAKY);
         else DNB_TC_LAUNCH_ACT(ACT_GENERIC, ACT_GENERIC);
     }
 #undef DNB_TC_LAUNCH_ACT
+#undef DNB_TC_LAUNCH_PAIR
 #undef DNB_TC_LAUNCH
     DNB_LAUNCH_CHECK("conv_tc");
     return DNB_OK;

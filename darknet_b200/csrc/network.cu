@@ -17,17 +17,21 @@ using namespace dnb;
 
 namespace {
 
-enum LayerKind { L_CONV, L_MAXPOOL, L_UPSAMPLE, L_SHORTCUT, L_ROUTE, L_YOLO, L_AVGPOOL, L_SOFTMAX };
-const char *const kKindNames[] = {"convolutional", "maxpool", "upsample", "shortcut", "route", "yolo", "avgpool", "softmax"};
+enum LayerKind { L_CONV, L_MAXPOOL, L_UPSAMPLE, L_SHORTCUT, L_ROUTE, L_YOLO, L_AVGPOOL, L_SOFTMAX, L_CONNECTED };
+const char *const kKindNames[] = {"convolutional", "maxpool", "upsample", "shortcut", "route", "yolo", "avgpool", "softmax", "connected"};
 
 struct Layer {
     LayerKind kind;
     int c, h, w;                   // input extents
     int out_c, out_h, out_w;
     dnb_tensor out;                // device output: NHWC in the network's storage type (yolo: NCHW f32)
-    // convolutional
+    // convolutional; a connected layer is the 1x1 convolution of a 1x1 map whose channels are the whole input
+    // (height x width x channel pitch of the channels-last tensor it reads), the batch folded into the pixel tile
     dnb_conv_desc cd;
     dnb_conv_plan *plan = nullptr;
+    bool flipped = false;          // convolutional: the file stores the weight matrix transposed (cfg flipped=1)
+    int fc_inputs = 0;             // connected: inputs as the reference counts them (c*h*w of the previous layer)
+    int in_cpitch = 0;             // connected: channel pitch of the tensor it reads
     // maxpool / upsample
     int size = 0, stride = 0, padding = 0;
     float scale = 1.f;
@@ -200,10 +204,22 @@ static int build_network(const char *text, int mode, int batch_override, dnb_net
             if (act < 0) DNB_FAIL(DNB_EINVAL, "cfg layer %d: unknown activation '%s'", index, opt_str(o, "activation", "").c_str());
             L.cd = dnb_conv_desc{net->batch, h, w, c, opt_int(o, "filters", 1), opt_int(o, "groups", 1), size,
                                  opt_int(o, "stride", 1), padding, opt_int(o, "batch_normalize", 0), act, opt_int(o, "xnor", 0)};
-            if (opt_int(o, "flipped", 0)) DNB_FAIL(DNB_EUNSUPPORTED, "cfg layer %d: flipped weights are not on this path", index);
+            L.flipped = opt_int(o, "flipped", 0) != 0;   // parse_convolutional, src/parser.c:199: only the file's weight order differs
             DNB_TRY(dnb_conv_plan_create(&L.cd, mode, &L.plan));
             L.out_c = L.cd.n; L.out_h = L.plan->g.out_h; L.out_w = L.plan->g.out_w;
             L.launches = L.plan->kernel == 3 ? 2 : 1;
+        } else if (type == "connected" || type == "conn") {
+            // parse_connected (src/parser.c:259-268), make_connected_layer (src/connected_layer.c:14-33)
+            L.kind = L_CONNECTED;
+            const int act = parse_activation(opt_str(o, "activation", "logistic"));
+            if (act < 0) DNB_FAIL(DNB_EINVAL, "cfg layer %d: unknown activation '%s'", index, opt_str(o, "activation", "").c_str());
+            const int outputs = opt_int(o, "output", 1);
+            if (outputs < 1) DNB_FAIL(DNB_EINVAL, "cfg layer %d: connected output=%d", index, outputs);
+            L.fc_inputs = c * h * w;
+            L.in_cpitch = round_up(c, 8);
+            L.cd = dnb_conv_desc{net->batch, 1, 1, h * w * L.in_cpitch, outputs, 1, 1, 1, 0, opt_int(o, "batch_normalize", 0), act, 0};
+            DNB_TRY(dnb_conv_plan_create(&L.cd, mode, &L.plan));
+            L.out_c = outputs; L.out_h = 1; L.out_w = 1;
         } else if (type == "maxpool" || type == "max") {
             L.kind = L_MAXPOOL;
             L.stride = opt_int(o, "stride", 1);
@@ -324,7 +340,7 @@ static int build_network(const char *text, int mode, int batch_override, dnb_net
     DNB_CUDA(cudaMallocHost((void **)&net->out_host, (size_t)net->batch * net->outputs * sizeof(float)));
     if (last.kind != L_YOLO) DNB_CUDA(cudaMalloc((void **)&net->out_dev_nchw, (size_t)net->batch * net->outputs * sizeof(float)));
     const Layer &first = net->layers.front();
-    const bool first_reads_nchw = first.kind == L_CONV && (first.plan->kernel == 2 || first.plan->kernel == 3);
+    const bool first_reads_nchw = first.kind == L_CONV && (first.plan->kernel == 2 || first.plan->kernel == 3);   // a connected first layer reads the channels-last copy
     if (!first_reads_nchw) {
         dnb_tensor *t = &net->input_nhwc;
         DNB_TRY(alloc_activation(net, t, net->c, net->h, net->w));
@@ -402,6 +418,25 @@ extern "C" void dnb_free_network(dnb_network *net)
     delete net;
 }
 
+// A connected layer's matrix, [outputs][inputs] with the inputs in the reference's order (channel, row, column of the
+// previous layer's output, src/connected_layer.c:151-160), rearranged for the channels-last tensor the layer reads
+// here: input (ch, y, x) sits at ((y * w + x) * cpitch + ch); padding channels get zero weights.
+static int set_connected_params(dnb_network *net, Layer &L, int index, const float *weights, const float *biases, const float *scales,
+                                const float *mean, const float *var)
+{
+    const Layer *prev = index > 0 ? &net->layers[index - 1] : nullptr;
+    const int c = prev ? prev->out_c : net->c, h = prev ? prev->out_h : net->h, w = prev ? prev->out_w : net->w;
+    const int cp = L.in_cpitch, outputs = L.cd.n;
+    const size_t k = (size_t)h * w * cp;
+    std::vector<float> packed((size_t)outputs * k, 0.f);
+    for (int o = 0; o < outputs; ++o)
+        for (int ch = 0; ch < c; ++ch)
+            for (int y = 0; y < h; ++y)
+                for (int x = 0; x < w; ++x)
+                    packed[(size_t)o * k + ((size_t)y * w + x) * cp + ch] = weights[(size_t)o * L.fc_inputs + ((size_t)ch * h + y) * w + x];
+    return dnb_conv_plan_set_params(L.plan, packed.data(), biases, scales, mean, var);
+}
+
 extern "C" int dnb_load_weights(dnb_network *net, const char *path)
 {
     if (!net || !path) DNB_FAIL(DNB_EINVAL, "load_weights: null argument");
@@ -418,10 +453,13 @@ extern "C" int dnb_load_weights(dnb_network *net, const char *path)
         int seen;
         if (fread(&seen, sizeof(seen), 1, f) != 1) DNB_FAIL(DNB_EIO, "%s: truncated header", path);
     }
-    if (hdr[0] > 1000 || hdr[1] > 1000) DNB_FAIL(DNB_EUNSUPPORTED, "%s: transposed-weights file versions are not on this path", path);
+    // File versions above 1000 store connected-layer matrices as [inputs][outputs] (src/parser.c:1244, 1098-1104);
+    // convolutional layers are not affected by the version.
+    const bool transposed = hdr[0] > 1000 || hdr[1] > 1000;
     int index = 0;
     for (Layer &L : net->layers) {
         if (L.kind == L_CONV) {
+            // load_convolutional_weights (src/parser.c:1164-1215): biases, batchnorm vectors, weights
             const dnb_conv_desc &d = L.cd;
             const size_t nw = (size_t)d.n * (d.c / d.groups) * d.size * d.size;
             std::vector<float> biases(d.n), scales, mean, var, weights(nw);
@@ -434,8 +472,38 @@ extern "C" int dnb_load_weights(dnb_network *net, const char *path)
             }
             ok = ok && fread(weights.data(), sizeof(float), nw, f) == nw;
             if (!ok) DNB_FAIL(DNB_EIO, "%s: file ends inside layer %d (the reference would silently keep its random initialisation)", path, index);
+            if (L.flipped) {
+                // transpose_matrix(l.weights, l.c*l.size*l.size, l.n) (src/parser.c:1206-1208, 1085-1096): the file holds
+                // c*size*size rows of n values; Darknet's layout is n rows of c*size*size values
+                const size_t rows = nw / d.n, cols = d.n;
+                std::vector<float> t(nw);
+                for (size_t x = 0; x < rows; ++x)
+                    for (size_t y = 0; y < cols; ++y) t[y * rows + x] = weights[x * cols + y];
+                weights.swap(t);
+            }
             DNB_TRY(dnb_conv_plan_set_params(L.plan, weights.data(), biases.data(), d.batch_normalize ? scales.data() : nullptr,
                                              d.batch_normalize ? mean.data() : nullptr, d.batch_normalize ? var.data() : nullptr));
+        } else if (L.kind == L_CONNECTED) {
+            // load_connected_weights (src/parser.c:1098-1120): biases, weights, then the batchnorm vectors
+            const int outputs = L.cd.n, inputs = L.fc_inputs;
+            const size_t nw = (size_t)outputs * inputs;
+            std::vector<float> biases(outputs), scales, mean, var, weights(nw);
+            bool ok = fread(biases.data(), sizeof(float), outputs, f) == (size_t)outputs && fread(weights.data(), sizeof(float), nw, f) == nw;
+            if (ok && L.cd.batch_normalize) {
+                scales.resize(outputs); mean.resize(outputs); var.resize(outputs);
+                ok = fread(scales.data(), sizeof(float), outputs, f) == (size_t)outputs &&
+                     fread(mean.data(), sizeof(float), outputs, f) == (size_t)outputs &&
+                     fread(var.data(), sizeof(float), outputs, f) == (size_t)outputs;
+            }
+            if (!ok) DNB_FAIL(DNB_EIO, "%s: file ends inside layer %d", path, index);
+            if (transposed) {
+                std::vector<float> t(nw);   // transpose_matrix(l.weights, l.inputs, l.outputs)
+                for (int x = 0; x < inputs; ++x)
+                    for (int y = 0; y < outputs; ++y) t[(size_t)y * inputs + x] = weights[(size_t)x * outputs + y];
+                weights.swap(t);
+            }
+            DNB_TRY(set_connected_params(net, L, index, weights.data(), biases.data(), L.cd.batch_normalize ? scales.data() : nullptr,
+                                         L.cd.batch_normalize ? mean.data() : nullptr, L.cd.batch_normalize ? var.data() : nullptr));
         }
         ++index;
     }
@@ -451,13 +519,18 @@ extern "C" int dnb_network_set_conv_params(dnb_network *net, int layer, const fl
 {
     if (!net || layer < 0 || layer >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "set_conv_params: bad argument");
     Layer &L = net->layers[layer];
-    if (L.kind != L_CONV) DNB_FAIL(DNB_EINVAL, "set_conv_params: layer %d is not convolutional", layer);
+    if (L.kind != L_CONV && L.kind != L_CONNECTED) DNB_FAIL(DNB_EINVAL, "set_conv_params: layer %d has no parameters", layer);
     if (net->submitted != net->collected) DNB_FAIL(DNB_EINVAL, "set_conv_params: a submitted step is still in flight; collect it first");
-    DNB_TRY(dnb_conv_plan_set_params(L.plan, weights, biases, scales, rolling_mean, rolling_variance));
+    if (L.kind == L_CONNECTED) {
+        if (!weights || !biases) DNB_FAIL(DNB_EINVAL, "set_conv_params: null argument");
+        DNB_TRY(set_connected_params(net, L, layer, weights, biases, scales, rolling_mean, rolling_variance));
+    } else {
+        DNB_TRY(dnb_conv_plan_set_params(L.plan, weights, biases, scales, rolling_mean, rolling_variance));
+    }
     drop_graph(net);   // a captured forward holds the pointers of the parameter tensors just replaced
     if (!L.params_given) { L.params_given = true; ++net->convs_with_params; }
     int convs = 0;
-    for (const Layer &K : net->layers) convs += K.kind == L_CONV;
+    for (const Layer &K : net->layers) convs += K.kind == L_CONV || K.kind == L_CONNECTED;
     if (net->convs_with_params == convs) net->weights_loaded = true;
     return DNB_OK;
 }
@@ -514,6 +587,14 @@ static int forward_layer(dnb_network *net, int i, const float *device_input, cud
             return dnb_conv_shortcut_forward(L.plan, &in, &net->layers[S.from].out, &S.out, S.alpha, S.beta, S.activation, s);
         }
         return dnb_conv_forward(L.plan, &in, &L.out, nullptr, s);
+    case L_CONNECTED: {
+        // forward_connected_layer_gpu (src/connected_layer.c:288-306): the previous layer's whole channels-last output
+        // is one pixel of h*w*cpitch channels per image
+        dnb_tensor flat = in;
+        flat.h = flat.w = 1;
+        flat.c = flat.cpitch = L.cd.c;
+        return dnb_conv_forward(L.plan, &flat, &L.out, nullptr, s);
+    }
     case L_MAXPOOL: return launch_maxpool(&in, &L.out, L.size, L.stride, L.padding, s);
     case L_UPSAMPLE: return launch_upsample(&in, &L.out, L.stride, L.scale, s);
     case L_SHORTCUT:
@@ -720,6 +801,17 @@ extern "C" const char *dnb_network_layer_kernel(const dnb_network *net, int i)
 }
 
 // Images [first, first + count) of layer i's output, NCHW f32, to the host.
+extern "C" int dnb_conv_plan_describe(const dnb_conv_plan *p, char *buf, int len);
+
+extern "C" int dnb_network_layer_describe(const dnb_network *net, int i, char *buf, int len)
+{
+    if (!net || !buf || len < 1 || i < 0 || i >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "layer_describe: bad argument");
+    const Layer &L = net->layers[i];
+    if (L.plan) return dnb_conv_plan_describe(L.plan, buf, len);
+    snprintf(buf, len, "%s", kKindNames[L.kind]);
+    return DNB_OK;
+}
+
 extern "C" int dnb_network_layer_output_images(dnb_network *net, int i, int first, int count, float *host_out)
 {
     if (!net || !host_out || i < 0 || i >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "layer_output: bad argument");
@@ -735,20 +827,25 @@ extern "C" int dnb_network_layer_output_images(dnb_network *net, int i, int firs
         DNB_CUDA(cudaMemcpy(host_out, (const float *)L.out.data + (size_t)first * per_image, elems * sizeof(float), cudaMemcpyDeviceToHost));
         return DNB_OK;
     }
-    if (elems > net->export_elems) {
+    // a run of whole images of a channels-last tensor is itself a channels-last tensor, if it starts on a 128-byte
+    // boundary; where it does not (small maps with odd pitches) the whole layer is converted and the run copied out
+    const size_t image_bytes = (size_t)L.out_h * L.out_w * L.out.cpitch * elem_size(L.out.dtype);
+    const bool aligned = ((size_t)first * image_bytes) % 128 == 0;
+    const int conv_first = aligned ? first : 0, conv_count = aligned ? count : net->batch;
+    const size_t conv_elems = (size_t)conv_count * per_image;
+    if (conv_elems > net->export_elems) {
         cudaFree(net->export_dev);
         net->export_dev = nullptr; net->export_elems = 0;
-        DNB_CUDA(cudaMalloc((void **)&net->export_dev, elems * sizeof(float)));
-        net->export_elems = elems;
+        DNB_CUDA(cudaMalloc((void **)&net->export_dev, conv_elems * sizeof(float)));
+        net->export_elems = conv_elems;
     }
-    // a run of whole images of a channels-last tensor is itself a channels-last tensor
     dnb_tensor in = L.out;
-    in.n = count;
-    in.data = (char *)L.out.data + (size_t)first * L.out_h * L.out_w * L.out.cpitch * elem_size(L.out.dtype);
-    dnb_tensor o{net->export_dev, DNB_NCHW, DNB_F32, count, L.out_c, L.out_h, L.out_w, 0};
+    in.n = conv_count;
+    in.data = (char *)L.out.data + (size_t)conv_first * image_bytes;
+    dnb_tensor o{net->export_dev, DNB_NCHW, DNB_F32, conv_count, L.out_c, L.out_h, L.out_w, 0};
     DNB_TRY(launch_convert(&in, &o, 0, 0, 0, net->stream));
     DNB_CUDA(cudaStreamSynchronize(net->stream));
-    DNB_CUDA(cudaMemcpy(host_out, net->export_dev, elems * sizeof(float), cudaMemcpyDeviceToHost));
+    DNB_CUDA(cudaMemcpy(host_out, net->export_dev + (size_t)(first - conv_first) * per_image, elems * sizeof(float), cudaMemcpyDeviceToHost));
     return DNB_OK;
 }
 
@@ -806,6 +903,8 @@ extern "C" double dnb_network_flops(const dnb_network *net)
     for (const Layer &L : net->layers)
         if (L.kind == L_CONV)
             ops += 2.0 * L.cd.n * L.cd.size * L.cd.size * (L.cd.c / L.cd.groups) * L.out_h * L.out_w;
+        else if (L.kind == L_CONNECTED)
+            ops += 2.0 * L.fc_inputs * L.cd.n;   // examples/darknet.c:91-92
     return ops * net->batch;
 }
 

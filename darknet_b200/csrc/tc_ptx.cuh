@@ -144,6 +144,69 @@ __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// ------------------------------------------------------------------ CTA pairs (cta_group::2)
+// Two CTAs of a cluster of two run one MMA of 256 rows: each holds 128 rows of A and half of B's columns in its own
+// shared memory and its 128 rows of the accumulator in its own TMEM; the even CTA (cluster rank 0) issues the MMAs.
+// Shared-memory addresses of a CTA in a cluster carry its rank from bit 24 up; clearing that bit names the same
+// offset in the even CTA.  No load here is shared between CTAs: each CTA loads its own operands.
+constexpr uint32_t PAIR_LEADER_MASK = 0xFEFFFFFFu;
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// All threads of every CTA of the cluster (release / acquire: barrier initialisations before it are visible after it).
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+}
+// The same barrier in the even CTA of the pair, as a shared::cluster address.
+__device__ __forceinline__ uint32_t leader_bar(uint32_t bar) { return bar & PAIR_LEADER_MASK; }
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar)
+{
+    asm volatile(
+        "{\n\t.reg .b32 rem;\n\t"
+        "mapa.shared::cluster.u32 rem, %0, 0;\n\t"
+        "mbarrier.arrive.shared::cluster.b64 _, [rem];\n\t}"
+        ::"r"(bar) : "memory");
+}
+// Loads of a CTA pair: the data lands in the executing CTA's shared memory, the bytes are counted on the even CTA's barrier.
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(leader_bar(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(leader_bar(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+template <bool IS_BF16>
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    if (IS_BF16) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
+// Arrives on the barrier at this offset in BOTH CTAs of the pair once the MMAs issued so far have retired (an
+// mbarrier arrive, not a load: the only cluster-wide signal in the kernel).
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 

@@ -8,7 +8,8 @@ in the on-disk format Darknet's ``load_weights`` reads (src/parser.c:1218-1306:
 three int32 ``major, minor, revision``, a ``size_t seen``, then per
 convolutional layer ``biases[n]``, and if batch-normalised ``scales[n]``,
 ``rolling_mean[n]``, ``rolling_variance[n]``, then ``weights[n*c/groups*size*size]``,
-src/parser.c:1164-1215).
+src/parser.c:1164-1215; per connected layer ``biases[outputs]``,
+``weights[outputs*inputs]``, then the batchnorm vectors, src/parser.c:1098-1120).
 
 The same file is read by the unmodified reference (the checker) and by this
 library's loader, so both sides always see identical parameters.
@@ -147,6 +148,17 @@ def darknet19_cfg(batch: int = 128, size: int = 224, xnor: bool = True) -> str:
     return s
 
 
+def connected_cfg(batch: int = 4, size: int = 12, hidden: int = 48, classes: int = 10, bn: bool = True) -> str:
+    """A small classifier that ends in connected layers, in the style of the reference's older cfgs
+    (cfg/darknet.cfg's tail, cfg/alexnet.cfg): convolution, maxpool, a connected layer over the whole
+    feature map (its input is the map flattened channel by channel), a second connected layer, softmax."""
+    s = _net(batch, size, size)
+    s += _conv(16, 3) + "\n[maxpool]\nsize=2\nstride=2\n" + _conv(24, 3)
+    s += f"\n[connected]\n{'batch_normalize=1' if bn else ''}\noutput={hidden}\nactivation=leaky\n"
+    s += f"\n[connected]\noutput={classes}\nactivation=linear\n\n[softmax]\ngroups=1\n"
+    return s
+
+
 def single_conv_cfg(batch: int, c: int, h: int, w: int, filters: int, size: int, stride: int = 1,
                     pad: int = 1, bn: bool = True, act: str = "leaky", xnor: bool = False,
                     groups: int = 1) -> str:
@@ -168,12 +180,13 @@ def memory_layers_cfg(batch: int = 64, c: int = 128, size: int = 152) -> str:
 
 @dataclass
 class ConvParams:
-    """Host parameters of one convolutional layer, in Darknet's layouts."""
-    weights: np.ndarray            # [n, c/groups, size, size] fp32
+    """Host parameters of one convolutional or connected layer, in Darknet's layouts."""
+    weights: np.ndarray            # [n, c/groups, size, size] fp32; connected: [outputs, inputs]
     biases: np.ndarray             # [n]
     scales: np.ndarray | None      # [n] (batchnorm gamma) or None
     rolling_mean: np.ndarray | None
     rolling_variance: np.ndarray | None
+    kind: str = "convolutional"    # or "connected" (the two differ in the order of their arrays on disk)
 
 
 @dataclass
@@ -184,66 +197,108 @@ class ConvShape:
     size: int
     groups: int
     batch_normalize: bool
+    kind: str = "convolutional"    # "connected": c is the number of inputs (channels x height x width), size 1
 
 
-def conv_shapes(cfg_text: str) -> list[ConvShape]:
-    """Walk the cfg and return the parameter shape of every convolutional layer,
-    tracking the channel count through maxpool / route / shortcut / upsample the
-    way parse_network_cfg does (src/parser.c:742-889)."""
+def param_shapes(cfg_text: str) -> list[ConvShape]:
+    """Walk the cfg and return the parameter shape of every layer that has parameters (convolutional and
+    connected), in file order, tracking channels and map size through the other layers the way
+    parse_network_cfg does (src/parser.c:742-889)."""
     sections = parse_cfg(cfg_text)
     net = sections[0][1]
-    c = int(net.get("channels", 3))
-    out_c: list[int] = []
+    c, h, w = int(net.get("channels", 3)), int(net.get("height", 0)), int(net.get("width", 0))
+    dims: list[tuple[int, int, int]] = []
     shapes: list[ConvShape] = []
     for idx, (kind, opt) in enumerate(sections[1:]):
         if kind == "convolutional":
-            n = int(opt.get("filters", 1))
-            shapes.append(ConvShape(idx, c, n, int(opt.get("size", 1)), int(opt.get("groups", 1)),
-                                    bool(int(opt.get("batch_normalize", 0)))))
-            c = n
+            n, size, stride = int(opt.get("filters", 1)), int(opt.get("size", 1)), int(opt.get("stride", 1))
+            pad = size // 2 if int(opt.get("pad", 0)) else int(opt.get("padding", 0))
+            shapes.append(ConvShape(idx, c, n, size, int(opt.get("groups", 1)), bool(int(opt.get("batch_normalize", 0)))))
+            c, h, w = n, (h + 2 * pad - size) // stride + 1, (w + 2 * pad - size) // stride + 1
+        elif kind == "connected":
+            n = int(opt.get("output", 1))
+            shapes.append(ConvShape(idx, c * h * w, n, 1, 1, bool(int(opt.get("batch_normalize", 0))), "connected"))
+            c, h, w = n, 1, 1
+        elif kind == "maxpool":
+            stride = int(opt.get("stride", 1))
+            size = int(opt.get("size", stride))
+            pad = int(opt.get("padding", size - 1))
+            h, w = (h + pad - size) // stride + 1, (w + pad - size) // stride + 1
+        elif kind == "upsample":
+            st = int(opt.get("stride", 2))
+            h, w = h * st, w * st
         elif kind == "route":
             ids = [int(t) for t in opt["layers"].split(",")]
-            c = sum(out_c[i if i >= 0 else idx + i] for i in ids)
-        # maxpool, upsample, shortcut, yolo, avgpool, softmax keep the channel count
-        out_c.append(c)
+            ids = [i if i >= 0 else idx + i for i in ids]
+            c = sum(dims[i][0] for i in ids)
+            h, w = dims[ids[0]][1], dims[ids[0]][2]
+        elif kind == "avgpool":
+            h = w = 1
+        # shortcut, yolo, softmax keep the shape
+        dims.append((c, h, w))
     return shapes
 
 
+def conv_shapes(cfg_text: str) -> list[ConvShape]:
+    """The convolutional layers of param_shapes."""
+    return [s for s in param_shapes(cfg_text) if s.kind == "convolutional"]
+
+
 def seeded_params(cfg_text: str, seed: int = 0, pow2_mean_xnor: bool = False) -> list[ConvParams]:
-    """Random parameters for every convolutional layer from a counter-based PRNG
+    """Random parameters for every convolutional and connected layer from a counter-based PRNG
     (Philox), one independent stream per layer: weights He-normal
     N(0, 2/(size^2 * c/groups)), biases N(0, 0.01), batchnorm gamma U(0.9, 1.1),
     rolling_mean N(0, 0.1), rolling_variance U(0.5, 1.5) (second argument of N is
     the variance)."""
     out = []
-    for shp in conv_shapes(cfg_text):
+    for shp in param_shapes(cfg_text):
         rng = np.random.Generator(np.random.Philox(key=[seed, shp.index]))
         fan = shp.size * shp.size * (shp.c // shp.groups)
-        w = rng.standard_normal((shp.n, shp.c // shp.groups, shp.size, shp.size), dtype=np.float32)
+        if shp.kind == "connected":
+            w = rng.standard_normal((shp.n, shp.c), dtype=np.float32)
+        else:
+            w = rng.standard_normal((shp.n, shp.c // shp.groups, shp.size, shp.size), dtype=np.float32)
         w *= np.float32(np.sqrt(2.0 / fan))
         b = (rng.standard_normal(shp.n, dtype=np.float32) * np.float32(0.1))
         if shp.batch_normalize:
             g = rng.uniform(0.9, 1.1, shp.n).astype(np.float32)
             m = (rng.standard_normal(shp.n, dtype=np.float32) * np.float32(np.sqrt(0.1)))
             v = rng.uniform(0.5, 1.5, shp.n).astype(np.float32)
-            out.append(ConvParams(w, b, g, m, v))
+            out.append(ConvParams(w, b, g, m, v, shp.kind))
         else:
-            out.append(ConvParams(w, b, None, None, None))
+            out.append(ConvParams(w, b, None, None, None, shp.kind))
     return out
 
 
-def write_weights(path: str, params: list[ConvParams], seen: int = 0) -> None:
-    """Write a ``.weights`` file: header major=0, minor=2, revision=0 and a
-    64-bit ``seen`` (src/parser.c:1018-1024), then each layer's arrays in load
-    order."""
+def write_weights(path: str, params: list[ConvParams], seen: int = 0, version: tuple[int, int, int] = (0, 2, 0),
+                  flipped: set[int] | frozenset = frozenset()) -> None:
+    """Write a ``.weights`` file: header major, minor, revision and ``seen`` (64-bit from version 0.2 on,
+    32-bit before; src/parser.c:1018-1024, 1234-1241), then each layer's arrays in load order.
+    A major or minor version above 1000 marks a file whose connected-layer matrices are stored
+    [inputs][outputs] (src/parser.c:1244, 1098-1104); ``flipped`` names the positions in ``params`` of
+    convolutions whose cfg section says ``flipped=1`` and whose matrix is stored [c*size*size][n]
+    (src/parser.c:1206-1208)."""
+    major, minor, revision = version
+    transposed = major > 1000 or minor > 1000
     with open(path, "wb") as f:
-        f.write(struct.pack("<iiiQ", 0, 2, 0, seen))
-        for p in params:
+        f.write(struct.pack("<iii", major, minor, revision))
+        f.write(struct.pack("<Q", seen) if (major * 10 + minor) >= 2 and major < 1000 and minor < 1000 else struct.pack("<i", seen))
+        for i, p in enumerate(params):
             f.write(np.ascontiguousarray(p.biases, dtype=np.float32).tobytes())
-            if p.scales is not None:
-                for a in (p.scales, p.rolling_mean, p.rolling_variance):
+            w = np.ascontiguousarray(p.weights, dtype=np.float32)
+            bn = [] if p.scales is None else [p.scales, p.rolling_mean, p.rolling_variance]
+            if p.kind == "connected":
+                if transposed:
+                    w = np.ascontiguousarray(w.T)      # the loader transposes [inputs][outputs] back
+                f.write(w.tobytes())
+                for a in bn:
                     f.write(np.ascontiguousarray(a, dtype=np.float32).tobytes())
-            f.write(np.ascontiguousarray(p.weights, dtype=np.float32).tobytes())
+            else:
+                for a in bn:
+                    f.write(np.ascontiguousarray(a, dtype=np.float32).tobytes())
+                if i in flipped:
+                    w = np.ascontiguousarray(w.reshape(w.shape[0], -1).T)
+                f.write(w.tobytes())
 
 
 def seeded_input(cfg_text: str, seed: int = 0, dist: str = "uniform") -> np.ndarray:

@@ -194,6 +194,13 @@ int dnb_conv_plan_set_diagnostics(dnb_conv_plan *plan, long long wait_limit_cycl
  * "xnor_popc"); static storage. */
 const char *dnb_conv_plan_kernel(const dnb_conv_plan *plan);
 
+/* One line about the plan for logs and tests, written to buf (at most len bytes with the
+ * terminator): the kernel name and, for tensor-core plans after their first forward, the
+ * tiling ("tc_tf32 pair=1 bn=256 tile=8x2x8 tiles=96 stages=6 ctas_per_sm=1 srb=128").
+ * The reference prints a line per layer when it builds the network
+ * (src/convolutional_layer.c:325). */
+int dnb_conv_plan_describe(const dnb_conv_plan *plan, char *buf, int len);
+
 /* ------------------------------------------------------------------ memory-bound layers */
 /* All take tensors of one layout (both NCHW f32, or both NHWC of one dtype). */
 
@@ -246,7 +253,9 @@ typedef struct dnb_network dnb_network;
 
 /* parse_network_cfg (src/parser.c:742-889) for the layer types on this path:
  * [net], [convolutional], [maxpool], [upsample], [shortcut], [route], [yolo],
- * [avgpool], [softmax].  Any other section fails with DNB_EUNSUPPORTED.
+ * [avgpool], [connected], [softmax].  Any other section fails with DNB_EUNSUPPORTED.
+ * A [connected] layer (src/connected_layer.c:288-306) runs on the convolution kernels as
+ * a 1x1 convolution over the flattened input with the batch folded into the pixel tile.
  * batch_override > 0 replaces the cfg's batch/subdivisions (the reference needs
  * an edited cfg for that, src/parser.c:664).  Allocates every layer's output on
  * the current device. */
@@ -255,11 +264,16 @@ int dnb_parse_network_cfg(const char *cfg_path, int mode, int batch_override, dn
 int dnb_parse_network_cfg_text(const char *cfg_text, int mode, int batch_override, dnb_network **net);
 
 /* load_weights (src/parser.c:1308, :1218-1306): reads the .weights file and
- * builds every convolution's derived device tensors. */
+ * builds every convolution's and connected layer's derived device tensors.  Both
+ * header forms (32- and 64-bit `seen`, :1234-1241), files whose version marks
+ * transposed connected-layer matrices (major or minor above 1000, :1244, :1098-1104) and
+ * convolutions declared flipped=1 in the cfg (:1206-1208) are read as the reference
+ * reads them. */
 int dnb_load_weights(dnb_network *net, const char *weights_path);
 
 /* load_weights for a host that already holds the parameters in memory: the arrays the reference's
- * load_convolutional_weights fills (src/parser.c:1164-1215) for convolution `layer`.  Once every convolution
+ * load_convolutional_weights fills (src/parser.c:1164-1215) for convolution `layer`, or load_connected_weights
+ * (src/parser.c:1098-1120; weights [outputs][inputs]) for a connected layer.  Once every such layer
  * of the network has been given its parameters the network is ready to predict. */
 int dnb_network_set_conv_params(dnb_network *net, int layer, const float *weights, const float *biases,
                                 const float *scales, const float *rolling_mean, const float *rolling_variance);
@@ -319,6 +333,8 @@ int dnb_network_outputs(const dnb_network *net);
 int dnb_network_layer_shape(const dnb_network *net, int layer, int *out_c, int *out_h, int *out_w);
 const char *dnb_network_layer_type(const dnb_network *net, int layer);
 const char *dnb_network_layer_kernel(const dnb_network *net, int layer);
+/* dnb_conv_plan_describe for a convolutional layer, the section name for the others. */
+int dnb_network_layer_describe(const dnb_network *net, int layer, char *buf, int len);
 
 /* Copy layer `layer`'s current output to host memory as Darknet lays it out
  * (NCHW f32, batch*outputs floats): what reading l.output after

@@ -262,6 +262,35 @@ void orc_xnor_accumulate(const orc_conv_t *p, const float *input, const float *w
 }
 
 /* ------------------------------------------------------------------------- */
+/* Connected layer: src/connected_layer.c:151-167.  The output is zeroed, then
+ * gemm(0,1,...) = gemm_nt (src/gemm.c:91-106): out[b][o] += sum over i of
+ * input[b][i] * weights[o][i], the products summed in a float register in index
+ * order and added to the output once; then batchnorm (over the outputs, one
+ * value per image: src/batchnorm_layer.c:151-154 with out_h*out_w = 1) or the
+ * bias, then the activation.  The input is the previous layer's output in the
+ * reference's own order (channel, row, column). */
+void orc_connected_forward(int batch, int inputs, int outputs, int batch_normalize, int activation,
+                           const float *input, const float *weights, const float *biases,
+                           const float *scales, const float *rolling_mean, const float *rolling_variance,
+                           float *output)
+{
+    memset(output, 0, sizeof(float) * (size_t)batch * outputs);
+#pragma omp parallel for
+    for (int b = 0; b < batch; ++b) {
+        for (int o = 0; o < outputs; ++o) {
+            float sum = 0;
+            for (int i = 0; i < inputs; ++i) sum += 1.f * input[(size_t)b * inputs + i] * weights[(size_t)o * inputs + i];
+            output[(size_t)b * outputs + o] += sum;
+        }
+    }
+    orc_conv_t p;
+    memset(&p, 0, sizeof(p));
+    p.batch = batch; p.n = outputs; p.batch_normalize = batch_normalize;
+    orc_bn_bias(output, &p, 1, biases, scales, rolling_mean, rolling_variance);
+    orc_activate_array(output, (long)batch * outputs, activation);
+}
+
+/* ------------------------------------------------------------------------- */
 /* Maxpool: src/maxpool_layer.c:21-52 (geometry) and :79-114 (forward).
  * "pad" is the total padding (parser default size-1, src/parser.c:487); the
  * window starts at -pad/2 (C integer division) and taps outside the image are

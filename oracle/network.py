@@ -58,6 +58,7 @@ def lib() -> C.CDLL:
         L.orc_yolo_forward.argtypes = [C.c_void_p] + [C.c_int] * 5 + [C.c_void_p]
         L.orc_avgpool_forward.argtypes = [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p]
         L.orc_softmax_forward.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p]
+        L.orc_connected_forward.argtypes = [C.c_int] * 5 + [C.c_void_p] * 7
         L.orc_im2col.argtypes = [C.c_void_p] + [C.c_int] * 6 + [C.c_void_p]
         L.orc_gemm_nn.argtypes = [C.c_int] * 3 + [C.c_float, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int]
         L.orc_activate_array.argtypes = [C.c_void_p, C.c_long, C.c_int]
@@ -158,6 +159,20 @@ def avgpool_forward(x):
     return out
 
 
+def connected_forward(x, weights, biases, scales=None, mean=None, var=None, *, activation="linear"):
+    """x [B, ...] flattened per image in the reference's order, weights [outputs, inputs]; returns [B, outputs, 1, 1]."""
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(weights, np.float32)
+    B = x.shape[0]
+    outputs, inputs = w.shape
+    assert x[0].size == inputs
+    out = np.empty((B, outputs, 1, 1), np.float32)
+    args = [np.ascontiguousarray(a, np.float32) if a is not None else None for a in (biases, scales, mean, var)]
+    lib().orc_connected_forward(B, inputs, outputs, int(scales is not None), ACT[activation], _p(x), _p(w),
+                                _p(args[0]), _p(args[1]), _p(args[2]), _p(args[3]), _p(out))
+    return out
+
+
 def softmax_forward(x, groups=1, temperature=1.0):
     x = np.ascontiguousarray(x, np.float32)
     out = np.empty_like(x)
@@ -191,6 +206,11 @@ def forward_network(cfg_text: str, params, x: np.ndarray, upto: int | None = Non
             cur = conv_forward(cur, p.weights, p.biases, p.scales, p.rolling_mean, p.rolling_variance,
                                stride=int(opt.get("stride", 1)), pad=padding, groups=int(opt.get("groups", 1)),
                                activation=opt.get("activation", "logistic"), xnor=bool(int(opt.get("xnor", 0))))
+        elif kind == "connected":
+            p = params[pi]
+            pi += 1
+            cur = connected_forward(cur, p.weights, p.biases, p.scales, p.rolling_mean, p.rolling_variance,
+                                    activation=opt.get("activation", "logistic"))
         elif kind == "maxpool":
             stride = int(opt.get("stride", 1))
             size = int(opt.get("size", stride))
@@ -247,10 +267,16 @@ class Reference:
         L.ref_time_predict.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.ref_im2col.argtypes = [C.c_void_p] + [C.c_int] * 6 + [C.c_void_p]
         L.ref_gemm_nn.argtypes = [C.c_int] * 3 + [C.c_void_p] * 3
+        if hasattr(L, "ref_save_weights"):
+            L.ref_save_weights.argtypes = [C.c_void_p, C.c_char_p]
         self.L = L
 
     def load(self, cfg_path: str, weights_path: str | None):
         return self.L.ref_load_network(cfg_path.encode(), (weights_path or "").encode())
+
+    def save_weights(self, net, path: str) -> None:
+        """The reference's own save_weights (src/parser.c:1080-1083) on the loaded network."""
+        self.L.ref_save_weights(net, path.encode())
 
     def predict_all(self, net, x: np.ndarray) -> list[np.ndarray]:
         """network_predict, then a copy of every layer's output buffer."""

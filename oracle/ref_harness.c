@@ -65,6 +65,7 @@ int ref_is_gpu_build(void) { return 0; }
 
 /* network_predict (src/network.c:497-508): returns the last layer's output. */
 float *ref_network_predict(void *h, float *input) { return network_predict((network *)h, input); }
+void ref_save_weights(void *h, char *path) { save_weights((network *)h, path); }
 
 void ref_set_threads(int n) { omp_set_num_threads(n); }
 int ref_max_threads(void) { return omp_get_max_threads(); }

@@ -49,6 +49,8 @@ def cases() -> dict[str, tuple[str, int, int, str]]:
         "conv3x3_xnor": (s(2, 64, 10, 10, 32, 3, xnor=True), 18, 18, "normal"),
         "conv3x3_c256_k512": (s(1, 256, 13, 13, 512, 3), 19, 19, "normal"),
         "conv5x5": (s(1, 8, 11, 11, 8, 5), 20, 20, "normal"),
+        "connected_bn": (synth.connected_cfg(batch=4, size=12, bn=True), 21, 21, "uniform"),
+        "connected_bias": (synth.connected_cfg(batch=3, size=10, hidden=40, classes=7, bn=False), 22, 22, "uniform"),
     }
 
 

@@ -1,0 +1,123 @@
+"""Connected layers and the weight-file variants of the reference's loader, on the GPU.
+
+* [connected] (src/connected_layer.c:151-167, 288-306): a small classifier whose tail is two connected layers, one
+  with batchnorm, every layer against the CPU checker in all three modes; and against the unmodified reference
+  where oracle/_ref is present.
+* load_weights variants (src/parser.c:1218-1306): the 32-bit `seen` header of versions before 0.2, files whose
+  version (major or minor above 1000) marks connected matrices stored [inputs][outputs], convolutions declared
+  flipped=1 (matrix stored [c*size*size][n]); a file written by the reference's own save_weights is read back.
+  Each variant must give the network of the plain file, bit for bit.
+"""
+import os
+
+import numpy as np
+import pytest
+
+import darknet_b200 as dn
+from conftest import parity
+from darknet_b200 import synth
+from oracle import network as orc
+
+pytestmark = pytest.mark.gpu
+TOL = {dn.MODE_FP32: 1e-4, dn.MODE_TF32: 1e-2, dn.MODE_BF16: 6e-2}
+
+
+def build(cfg, wpath, mode):
+    return dn.Network(cfg, wpath, mode, text=True)
+
+
+@pytest.mark.parametrize("mode", [dn.MODE_FP32, dn.MODE_TF32, dn.MODE_BF16])
+@pytest.mark.parametrize("bn", [True, False])
+def test_connected_layers_match_the_checker(mode, bn, tmp_path):
+    cfg = synth.connected_cfg(batch=5, size=12, hidden=48, classes=10, bn=bn)
+    params = synth.seeded_params(cfg, 51)
+    x = synth.seeded_input(cfg, 51)
+    wpath = str(tmp_path / "c.weights")
+    synth.write_weights(wpath, params)
+    want = orc.forward_network(cfg, params, x)
+    net = build(cfg, wpath, mode)
+    out = net.predict(x).copy()
+    assert [net.layer_type(i) for i in range(net.n)].count("connected") == 2
+    for i, w in enumerate(want):
+        parity(net.layer_output(i).reshape(w.shape), w, TOL[mode], f"layer {i} ({net.layer_type(i)}, {net.layer_kernel(i)})")
+    parity(out.reshape(want[-1].shape), want[-1], TOL[mode], "network output")
+    assert abs(float(out[0].sum()) - 1.0) < 1e-3
+    assert net.flops > 0
+
+
+def test_connected_first_layer_and_large_batch(tmp_path):
+    # a connected layer straight on the input image (the flattening order c, h, w matters), batch above one pixel tile
+    cfg = ("[net]\nbatch=150\nsubdivisions=1\nwidth=6\nheight=5\nchannels=3\n"
+           "\n[connected]\noutput=70\nactivation=leaky\n\n[connected]\nbatch_normalize=1\noutput=33\nactivation=logistic\n")
+    params = synth.seeded_params(cfg, 52)
+    x = synth.seeded_input(cfg, 52, "normal")
+    wpath = str(tmp_path / "c.weights")
+    synth.write_weights(wpath, params)
+    want = orc.forward_network(cfg, params, x)
+    net = build(cfg, wpath, dn.MODE_TF32)
+    out = net.predict(x).copy()
+    for i, w in enumerate(want):
+        parity(net.layer_output(i).reshape(w.shape), w, 1e-2, f"layer {i}")
+    parity(out.reshape(want[-1].shape), want[-1], 1e-2, "network output")
+
+
+def test_weight_file_variants_load_the_same_network(tmp_path):
+    cfg = synth.connected_cfg(batch=3, size=12, hidden=40, classes=9, bn=True)
+    flipped_cfg = cfg.replace("filters=24\n", "filters=24\nflipped=1\n")
+    params = synth.seeded_params(cfg, 53)
+    x = synth.seeded_input(cfg, 53)
+    plain = str(tmp_path / "plain.weights")
+    synth.write_weights(plain, params, seen=7)
+    base = build(cfg, plain, dn.MODE_TF32).predict(x).copy()
+    # version 0.1: a 32-bit `seen`
+    old = str(tmp_path / "old.weights")
+    synth.write_weights(old, params, seen=7, version=(0, 1, 0))
+    assert os.path.getsize(old) == os.path.getsize(plain) - 4
+    assert np.array_equal(build(cfg, old, dn.MODE_TF32).predict(x), base)
+    # a version above 1000: connected matrices transposed on disk (and a 32-bit seen)
+    tr = str(tmp_path / "transposed.weights")
+    synth.write_weights(tr, params, seen=7, version=(0, 1001, 0))
+    assert open(tr, "rb").read() != open(old, "rb").read()
+    assert np.array_equal(build(cfg, tr, dn.MODE_TF32).predict(x), base)
+    # flipped=1 on the second convolution: its matrix is transposed on disk
+    fl = str(tmp_path / "flipped.weights")
+    synth.write_weights(fl, params, seen=7, flipped={1})
+    assert open(fl, "rb").read() != open(plain, "rb").read()
+    assert np.array_equal(build(flipped_cfg, fl, dn.MODE_TF32).predict(x), base)
+    # the checker agrees with all of them
+    parity(base.reshape(-1), orc.forward_network(cfg, params, x)[-1].reshape(-1), 1e-2, "against the checker")
+
+
+@pytest.mark.skipif(not orc.Reference.available(), reason="oracle/_ref (the compiled reference) is not built here")
+def test_reads_what_the_reference_saves_and_matches_its_outputs(tmp_path):
+    """The reference loads a transposed-version file and a flipped convolution, runs the network, and writes the
+    weights back with its own save_weights; this library reads the reference's file and reproduces its outputs."""
+    import contextlib
+    cfg = synth.connected_cfg(batch=2, size=12, hidden=32, classes=6, bn=True).replace("filters=24\n", "filters=24\nflipped=1\n")
+    params = synth.seeded_params(cfg, 54)
+    x = synth.seeded_input(cfg, 54)
+    src = str(tmp_path / "src.weights")
+    synth.write_weights(src, params, version=(0, 1001, 0), flipped={1})
+    cpath = str(tmp_path / "n.cfg")
+    open(cpath, "w").write(cfg)
+    R = orc.Reference()
+    devnull = os.open(os.devnull, os.O_WRONLY)
+    saved = os.dup(2)
+    os.dup2(devnull, 2)          # the reference prints its layer table to stderr
+    try:
+        rnet = R.load(cpath, src)
+        ref_out = R.predict_all(rnet, x)
+        back = str(tmp_path / "back.weights")
+        R.save_weights(rnet, back)
+    finally:
+        os.dup2(saved, 2)
+        os.close(devnull)
+    mine = build(cfg, src, dn.MODE_TF32)
+    out = mine.predict(x).copy()
+    for i, w in enumerate(ref_out):
+        parity(mine.layer_output(i).reshape(-1), w.reshape(-1), 1e-2, f"layer {i} against the reference")
+    # save_weights writes version 0.2 with untransposed connected matrices; the flipped convolution is written as it
+    # sits in memory (already transposed back by the loader), so the file is read with flipped=0
+    plain_cfg = cfg.replace("flipped=1\n", "")
+    again = build(plain_cfg, back, dn.MODE_TF32).predict(x).copy()
+    assert np.array_equal(again, out)

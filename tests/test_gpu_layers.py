@@ -371,6 +371,72 @@ def test_conv_tc_halo_mode(name, mode, tol, monkeypatch):
     parity(got_nchw, want, tol)
 
 
+PAIR_CASES = {
+    # shapes with enough tiles of 256 filters for the CTA-pair kernel: (pixel tiles + 1) / 2 * (filters / 256) >= 74
+    "c128_38x38_n512_odd_pixel_tiles": dict(b=8, c=128, h=38, w=38, n=512, size=3),          # 95 pixel tiles: the last pair is half empty
+    "c64_19x19_n1024_batch9": dict(b=9, c=64, h=19, w=19, n=1024, size=3),                    # 45 pixel tiles of 32 x 4 x 1
+    "s2_76_to_38_n512": dict(b=8, c=64, h=76, w=76, n=512, size=3, stride=2),
+    "c64_76x76_n256_one_filter_tile": dict(b=4, c=64, h=76, w=76, n=256, size=3),
+    "logistic_nobn_n256": dict(b=16, c=64, h=40, w=40, n=256, size=3, bn=False, act="logistic"),
+}
+
+
+@pytest.mark.parametrize("name", list(PAIR_CASES))
+@pytest.mark.parametrize("mode,tol", [(dn.MODE_TF32, TOL_TF32), (dn.MODE_BF16, TOL_BF16)])
+def test_conv_tc_cta_pairs(name, mode, tol, monkeypatch):
+    """Layers large enough for the CTA-pair kernel (clusters of two CTAs sharing every MMA, half a weight tile
+    each): against the checker, against the single-CTA kernel, and with Darknet's layout written beside."""
+    case = conv_case(260, **PAIR_CASES[name])
+    want = oracle_conv(case)
+    monkeypatch.setenv("DNB_TC_PAIR", "1")
+    plan, got, _ = run_conv(case, mode, "nhwc", "nhwc")
+    assert "pair=1" in plan.describe(), plan.describe()
+    parity(got, want, tol, name)
+    monkeypatch.setenv("DNB_TC_PAIR", "0")
+    plan0, single, _ = run_conv(case, mode, "nhwc", "nhwc")
+    assert "pair=0" in plan0.describe()
+    parity(got, single, (2e-3 if mode == dn.MODE_TF32 else 1e-2), "pair against single CTA")
+    monkeypatch.setenv("DNB_TC_PAIR", "1")
+    _, got_nchw, got_nhwc = run_conv(case, mode, "nchw", "nchw", both=True)   # Darknet's layout in and out, channels-last beside
+    assert np.array_equal(got_nchw, got_nhwc)
+    parity(got_nchw, want, tol, name)
+
+
+def test_conv_tc_cta_pairs_1x1_when_forced(monkeypatch):
+    case = conv_case(261, b=32, c=512, h=19, w=19, n=512, size=1)
+    monkeypatch.setenv("DNB_TC_PAIR", "2")
+    plan, got, _ = run_conv(case, dn.MODE_TF32, "nhwc", "nhwc")
+    assert "pair=1" in plan.describe(), plan.describe()
+    parity(got, oracle_conv(case), TOL_TF32, "1x1 in pair mode")
+
+
+@pytest.mark.parametrize("mode,tol", [(dn.MODE_TF32, TOL_TF32), (dn.MODE_BF16, TOL_BF16)])
+def test_conv_tc_cta_pairs_with_fused_shortcut(mode, tol, monkeypatch):
+    import ctypes as C
+    monkeypatch.setenv("DNB_TC_PAIR", "1")
+    case = conv_case(262, b=8, c=128, h=38, w=38, n=512, size=3)
+    x, w = case["x"], case["w"]
+    b, c, h, wd = x.shape
+    n = w.shape[0]
+    add = rng(263).standard_normal((b, n, h, wd), dtype=np.float32)
+    store = torch.bfloat16 if mode == dn.MODE_BF16 else torch.float32
+    if mode == dn.MODE_BF16:
+        add = bf16_round(add)
+    want = orc.shortcut_forward(oracle_conv(case), add, 1.0, 1.0, "linear")
+    plan = dn.ConvPlan(b, c, h, wd, n, 3, 1, 1, 1, True, case["act"], False, mode)
+    plan.set_params(w, case["biases"], case["scales"], case["mean"], case["var"])
+    xt, xd = dev_nhwc(x, store)
+    at, ad = dev_nhwc(add, store)
+    yt, yd = empty_nhwc(b, n, h, wd, store)
+    dn.check(dn.lib().dnb_conv_shortcut_forward(plan.handle, C.byref(xd), C.byref(ad), C.byref(yd), 1.0, 1.0, dn.ACTIVATIONS["linear"],
+                                                C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    plan.check_status()
+    assert "pair=1" in plan.describe(), plan.describe()
+    parity(host_from_nhwc(yt, n), want, tol, "pair mode with fused shortcut")
+    assert padding_is_zero(yt, n)
+
+
 def test_conv_tc_all_ones_counts_taps():
     # analytic known answer: ones everywhere -> in-image taps x channels, exact in TF32 and BF16
     C, H, W, N = 16, 9, 10, 16
