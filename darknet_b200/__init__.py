@@ -77,6 +77,7 @@ SIGNATURES = {
     "dnb_parse_network_cfg": (_I, [C.c_char_p, _I, _I, C.POINTER(_P)]),
     "dnb_parse_network_cfg_text": (_I, [C.c_char_p, _I, _I, C.POINTER(_P)]),
     "dnb_load_weights": (_I, [_P, C.c_char_p]),
+    "dnb_load_weights_packed": (_I, [_P, C.c_char_p]),
     "dnb_free_network": (None, [_P]),
     "dnb_network_predict": (_I, [_P, _P, C.POINTER(C.POINTER(_F))]),
     "dnb_network_set_conv_params": (_I, [_P, _I, _P, _P, _P, _P, _P]),

@@ -142,8 +142,10 @@ class Network:
         if weights:
             self.load_weights(weights)
 
-    def load_weights(self, path: str):
-        check(lib().dnb_load_weights(self.handle, path.encode()))
+    def load_weights(self, path: str, packed: bool = False):
+        """load_weights; ``packed``: the file stores its xnor convolutions in the packed-binary layer format."""
+        fn = lib().dnb_load_weights_packed if packed else lib().dnb_load_weights
+        check(fn(self.handle, path.encode()))
 
     n = property(lambda self: lib().dnb_network_num_layers(self.handle))
     batch = property(lambda self: lib().dnb_network_batch(self.handle))

@@ -83,6 +83,7 @@ struct ConvEpilogue {
     int res_cpitch;
     int activation2;
     float alpha, beta;
+    int raw_acc;          // int8 (xnor) tensor-core launches: write the int32 sums themselves into the NCHW output
 };
 
 struct ConvGeom {

@@ -51,7 +51,7 @@ struct alignas(64) TcArgs {
     CUtensorMap tmw;      // weights [taps][n_pad][c_pad], channels innermost
     CUtensorMap tmy;      // NHWC output, written by TMA stores from the staging rows
     CUtensorMap tmr;      // fused residual (same extents and box as tmy), loaded tile by tile in the epilogue
-    int is_bf16;          // 0: kind::tf32 on f32 operands, 1: kind::f16 on bf16 operands
+    int is_bf16;          // operand kind: 0 kind::tf32 on f32 operands, 1 kind::f16 on bf16 operands, 2 kind::i8 on int8 sign tensors (xnor)
     int row_bytes;        // bytes of channels per pipeline stage row: 128, 64 or 32 (= swizzle span)
     int bk;               // channels per stage row (row_bytes / element size)
     int c_blocks;         // ceil(c_pad / bk)
@@ -92,7 +92,7 @@ size_t conv_tc_fixed_smem(int store_row_bytes, int bn, int stage_bufs);
 int conv_tc_max_smem();
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link).
-int encode_tensor_map(CUtensorMap *map, int is_bf16, int rank, void *base, const uint64_t *dims,
+int encode_tensor_map(CUtensorMap *map, int elem_kind /* 0 f32, 1 bf16, 2 bytes */, int rank, void *base, const uint64_t *dims,
                       const uint64_t *strides_bytes /* rank-1 */, const uint32_t *box, int swizzle_bytes);
 
 // ---- conv_xnor.cu : bit-packed popcount GEMM
@@ -111,6 +111,9 @@ struct XnorArgs {
 int launch_conv_xnor(const XnorArgs &a, cudaStream_t s);
 // sign bits of an NHWC (f32/bf16) or NCHW f32 tensor into [b][h][w][cwords]
 int launch_pack_sign_bits(const dnb_tensor *x, uint32_t *bits, int cwords, cudaStream_t s);
+// signs of the same tensors as int8 (+1 where x > 0, else -1; 0 in the padding channels) into [b][h][w][cpad], cpad a
+// multiple of 32: the operand of the tensor-core xnor convolution
+int launch_pack_sign_i8(const dnb_tensor *x, int8_t *out, int cpad, cudaStream_t s);
 
 }  // namespace dnb
 
@@ -136,6 +139,13 @@ struct dnb_conv_plan {
     size_t x_nhwc_bytes;
     uint32_t *x_bits;        // packed input of an xnor plan
     size_t x_bits_bytes;
+    // xnor on the tensor cores (kind::i8): int8 sign tensors instead of packed bits
+    bool xnor_tc;            // this xnor plan runs the tensor-core kernel (DNB_XNOR_TC=0 keeps the popcount kernel)
+    int c_pad_i8;            // input channels rounded up to 32
+    int8_t *w_i8;            // [taps][n_pad][c_pad_i8] signs of the weights
+    float *scale_i8;         // [n_pad] mean|w| * folded batchnorm scale
+    int8_t *x_i8;            // int8 signs of the input, scratch
+    size_t x_i8_bytes;
     int *status;             // device status word of the tensor-core kernel
     bool status_shared;      // the word belongs to a network object (one word for all its plans)
     // tensor-core launch block, rebuilt when the input pointer changes

@@ -14,6 +14,7 @@ using namespace dnb;
 
 enum { K_TC_TF32 = 0, K_TC_BF16 = 1, K_DIRECT = 2, K_XNOR = 3 };
 static const char *const kKernelNames[] = {"tc_tf32", "tc_bf16", "direct_fp32", "xnor_popc"};
+static const char kXnorTcName[] = "xnor_tc";
 
 static float tf32_round_host(float x)
 {
@@ -64,6 +65,7 @@ extern "C" int dnb_conv_plan_create(const dnb_conv_desc *d, int mode, dnb_conv_p
     p->c_pad = round_up(d->c, 8);
     p->npg_pad = round_up(d->n / d->groups, 32);
     p->cwords = (d->c + 31) / 32;
+    p->c_pad_i8 = round_up(d->c, 32);
     if (d->xnor) p->kernel = K_XNOR;
     else if (mode == DNB_MODE_FP32 || d->groups != 1 || d->c < 8) p->kernel = K_DIRECT;
     else p->kernel = mode == DNB_MODE_BF16 ? K_TC_BF16 : K_TC_TF32;
@@ -73,6 +75,12 @@ extern "C" int dnb_conv_plan_create(const dnb_conv_desc *d, int mode, dnb_conv_p
     // RGB first layers of the TF32 / BF16 modes: tensor cores with thread-built im2col rows (DNB_STEM_TC=0 keeps the FP32 kernel)
     const char *stem_env = getenv("DNB_STEM_TC");
     p->stem_tc = p->kernel == K_DIRECT && mode != DNB_MODE_FP32 && !d->xnor && conv_stem_tc_covers(p->g) && !(stem_env && atoi(stem_env) == 0);
+    // xnor layers: int8 sign tensors through the tensor cores (kind::i8, exact int32 sums) unless DNB_XNOR_TC=0 asks
+    // for the bit-packed popcount kernel; strides above 2 have no lattice maps and stay with the popcount kernel
+    {
+        const char *e = getenv("DNB_XNOR_TC");
+        p->xnor_tc = p->kernel == K_XNOR && d->stride <= 2 && !(e && atoi(e) == 0);
+    }
     cudaGetDevice(&p->device);
     *out = p;
     return DNB_OK;
@@ -82,7 +90,7 @@ extern "C" void dnb_conv_plan_destroy(dnb_conv_plan *p)
 {
     if (!p) return;
     cudaFree(p->scale); cudaFree(p->shift); cudaFree(p->w_tc); cudaFree(p->w_direct); cudaFree(p->w_bits);
-    cudaFree(p->w_mean); cudaFree(p->x_nhwc_scratch); cudaFree(p->x_bits);
+    cudaFree(p->w_mean); cudaFree(p->x_nhwc_scratch); cudaFree(p->x_bits); cudaFree(p->w_i8); cudaFree(p->scale_i8); cudaFree(p->x_i8);
     if (!p->status_shared) cudaFree(p->status);
     delete p;
 }
@@ -90,6 +98,7 @@ extern "C" void dnb_conv_plan_destroy(dnb_conv_plan *p)
 extern "C" const char *dnb_conv_plan_kernel(const dnb_conv_plan *p)
 {
     if (!p) return "";
+    if (p->kernel == K_XNOR && p->xnor_tc) return kXnorTcName;
     return p->stem_tc ? "stem_tc_tf32" : kKernelNames[p->kernel];
 }
 
@@ -97,7 +106,7 @@ extern "C" int dnb_conv_plan_describe(const dnb_conv_plan *p, char *buf, int len
 {
     if (!p || !buf || len < 1) DNB_FAIL(DNB_EINVAL, "conv describe: bad argument");
     const TcArgs &a = p->tc;
-    if ((p->kernel == K_TC_TF32 || p->kernel == K_TC_BF16) && p->tc_x_ptr)
+    if ((p->kernel == K_TC_TF32 || p->kernel == K_TC_BF16 || (p->kernel == K_XNOR && p->xnor_tc)) && p->tc_x_ptr)
         snprintf(buf, len, "%s pair=%d halo=%d bn=%d tile=%dx%dx%d tiles=%d stages=%d ctas_per_sm=%d srb=%d", kKernelNames[p->kernel], a.pair, a.halo,
                  a.bn, a.wt, a.ht, a.bt, a.total_tiles, a.stages, a.ctas_per_sm, a.store_row_bytes);
     else
@@ -181,6 +190,19 @@ extern "C" int dnb_conv_plan_set_params(dnb_conv_plan *p, const float *weights, 
         }
         DNB_TRY(upload(&p->w_bits, bits));
         DNB_TRY(upload(&p->w_mean, m));
+        if (p->xnor_tc) {
+            // the same signs as int8 in the tensor-core kernel's weight layout [tap][n_pad][c_pad], zero where padded, and
+            // mean|w| folded into the batchnorm scale: out = act(sum * (mean * s) + shift)
+            std::vector<int8_t> w8((size_t)taps * p->n_pad * p->c_pad_i8, 0);
+            for (int n = 0; n < d.n; ++n)
+                for (int c = 0; c < d.c; ++c)
+                    for (int t = 0; t < taps; ++t)
+                        w8[((size_t)t * p->n_pad + n) * p->c_pad_i8 + c] = weights[((size_t)n * d.c + c) * taps + t] > 0.f ? 1 : -1;
+            std::vector<float> s8(p->n_pad, 0.f);
+            for (int n = 0; n < d.n; ++n) s8[n] = m[n] * s[n];
+            DNB_TRY(upload(&p->w_i8, w8));
+            DNB_TRY(upload(&p->scale_i8, s8));
+        }
     }
     p->params_set = true;
     // The launch block caches a tensor map over the weights just replaced: have the next forward rebuild it.
@@ -219,13 +241,15 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
 {
     TcArgs &a = p->tc;
     const ConvGeom &g = p->g;
-    const bool bf16 = p->kernel == K_TC_BF16;
-    const int es = bf16 ? 2 : 4;
-    a.is_bf16 = bf16;
-    const int cbytes = p->c_pad * es;
+    const bool bf16 = p->kernel == K_TC_BF16, i8 = p->kernel == K_XNOR;
+    const int es = i8 ? 1 : (bf16 ? 2 : 4);
+    const int kind = i8 ? 2 : (bf16 ? 1 : 0);              // element kind of the operands (and of their tensor maps)
+    const int c_pad = i8 ? p->c_pad_i8 : p->c_pad;         // channel pitch of the operand tensors
+    a.is_bf16 = kind;
+    const int cbytes = c_pad * es;
     a.row_bytes = cbytes >= 128 ? 128 : (cbytes >= 64 ? 64 : 32);
     a.bk = a.row_bytes / es;
-    a.c_blocks = (p->c_pad + a.bk - 1) / a.bk;
+    a.c_blocks = (c_pad + a.bk - 1) / a.bk;
     a.taps = g.size * g.size;
     pick_pixel_tile(g, &a.wt, &a.ht, &a.bt);
     // Halo mode (experimental, off unless DNB_TC_HALO is 1 or 2): one activation box per channel block serves all
@@ -238,7 +262,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     {
         const char *e = getenv("DNB_TC_HALO");
         const int knob = e ? atoi(e) : 0;
-        if (knob != 0 && g.size == 3 && g.stride == 1 && g.pad == 1 && a.row_bytes == 128 && g.out_w >= 8 && g.out_h >= 16) {
+        if (knob != 0 && !i8 && g.size == 3 && g.stride == 1 && g.pad == 1 && a.row_bytes == 128 && g.out_w >= 8 && g.out_h >= 16) {
             const double work_h = (double)round_up(g.out_w, 8) * round_up(g.out_h, 16) * g.batch;
             const double work_0 = (double)round_up(g.out_w, a.wt) * round_up(g.out_h, a.ht) * round_up(g.batch, a.bt);
             if (knob == 2 || (a.c_blocks <= 2 && work_h <= 1.08 * work_0)) { a.halo = 1; a.wt = 8; a.ht = 16; a.bt = 1; }
@@ -278,7 +302,9 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     {
         const char *e = getenv("DNB_TC_PAIR");
         const int knob = e ? atoi(e) : 1;
-        const bool legal = !a.halo && a.row_bytes == 128 && g.n % 256 == 0 && (ptiles + 1) / 2 * (g.n / 256) >= sm_count() / 2;
+        // (the pair kernel is built for 128-byte staged rows only: it needs a channels-last output at least that wide)
+        const bool legal = !a.halo && a.row_bytes == 128 && g.n % 256 == 0 && (ptiles + 1) / 2 * (g.n / 256) >= sm_count() / 2 &&
+                           y_nhwc && y_cpitch * (bf16 ? 2 : 4) >= 128;
         if (legal && (knob == 2 || (knob == 1 && g.size >= 3))) {
             a.pair = 1;
             a.bn = 256;
@@ -301,7 +327,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     if (srb < min_srb) srb = min_srb;  // the box may be wider than a narrow tensor: the TMA unit clips it
     if (const char *e = getenv("DNB_TC_SRB")) {   // tuning knob: widest staged row to try (128, 64 or 32)
         const int v = atoi(e);
-        if ((v == 128 || v == 64 || v == 32) && v >= min_srb && v < srb) srb = v;
+        if ((v == 128 || v == 64 || v == 32) && v >= min_srb && v < srb && !a.pair) srb = v;
     }
     const int min_stages = getenv("DNB_TC_MIN_STAGES") ? atoi(getenv("DNB_TC_MIN_STAGES")) : 4;
     // two accumulators of bn columns; TMEM is allocated in powers of two >= 32 columns
@@ -385,29 +411,33 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     for (int ph = 0; ph < s; ++ph)
         for (int pw = 0; pw < s; ++pw) {
             const int hl = (g.h - ph + s - 1) / s, wl = (g.w - pw + s - 1) / s;
-            uint64_t dims[4] = {(uint64_t)p->c_pad, (uint64_t)(wl > 0 ? wl : 1), (uint64_t)(hl > 0 ? hl : 1), (uint64_t)g.batch};
+            uint64_t dims[4] = {(uint64_t)c_pad, (uint64_t)(wl > 0 ? wl : 1), (uint64_t)(hl > 0 ? hl : 1), (uint64_t)g.batch};
             uint64_t strides[3] = {pix_bytes * s, pix_bytes * g.w * s, pix_bytes * g.w * g.h};
             uint32_t box[4] = {(uint32_t)a.bk, (uint32_t)a.wt, (uint32_t)a.ht, (uint32_t)a.bt};
             if (a.halo) { box[1] = (uint32_t)(a.wt + 2); box[2] = (uint32_t)(a.ht + 2); }
             char *base = (char *)x->data + ((size_t)ph * g.w + pw) * pix_bytes;
             if (hl <= 0 || wl <= 0) base = (char *)x->data;  // lattice empty: never addressed in-bounds
-            DNB_TRY(encode_tensor_map(&a.tmx[ph * s + pw], bf16, 4, base, dims, strides, box, a.row_bytes));
+            DNB_TRY(encode_tensor_map(&a.tmx[ph * s + pw], kind, 4, base, dims, strides, box, a.row_bytes));
         }
     {
-        uint64_t dims[3] = {(uint64_t)p->c_pad, (uint64_t)p->n_pad, (uint64_t)a.taps};
-        uint64_t strides[2] = {(uint64_t)p->c_pad * es, (uint64_t)p->c_pad * es * p->n_pad};
+        uint64_t dims[3] = {(uint64_t)c_pad, (uint64_t)p->n_pad, (uint64_t)a.taps};
+        uint64_t strides[2] = {(uint64_t)c_pad * es, (uint64_t)c_pad * es * p->n_pad};
         uint32_t box[3] = {(uint32_t)a.bk, (uint32_t)(a.pair ? a.bn / 2 : a.bn), 1u};
-        DNB_TRY(encode_tensor_map(&a.tmw, bf16, 3, p->w_tc, dims, strides, box, a.row_bytes));
+        DNB_TRY(encode_tensor_map(&a.tmw, kind, 3, i8 ? (void *)p->w_i8 : p->w_tc, dims, strides, box, a.row_bytes));
     }
     if (y_nhwc) {
         const size_t opix = (size_t)y_cpitch * out_es;
-        uint64_t dims[4] = {(uint64_t)y_cpitch, (uint64_t)g.out_w, (uint64_t)g.out_h, (uint64_t)g.batch};
+        // the channel extent is the layer's own (padded to 8), the pitch whatever the tensor has: the output may be a
+        // channel range of a wider tensor (a [route] output), and the boxes must not spill into its neighbour
+        const int y_chan = round_up(g.n, 8) < y_cpitch ? round_up(g.n, 8) : y_cpitch;
+        uint64_t dims[4] = {(uint64_t)y_chan, (uint64_t)g.out_w, (uint64_t)g.out_h, (uint64_t)g.batch};
         uint64_t strides[3] = {opix, opix * g.out_w, opix * g.out_w * g.out_h};
         uint32_t box[4] = {(uint32_t)(srb / out_es), (uint32_t)a.wt, (uint32_t)a.ht, (uint32_t)a.bt};
         DNB_TRY(encode_tensor_map(&a.tmy, bf16, 4, y_nhwc, dims, strides, box, srb));
         if (residual) {
             const size_t rpix = (size_t)res_cpitch * out_es;
-            uint64_t rdims[4] = {(uint64_t)res_cpitch, (uint64_t)g.out_w, (uint64_t)g.out_h, (uint64_t)g.batch};
+            const int r_chan = round_up(g.n, 8) < res_cpitch ? round_up(g.n, 8) : res_cpitch;
+            uint64_t rdims[4] = {(uint64_t)r_chan, (uint64_t)g.out_w, (uint64_t)g.out_h, (uint64_t)g.batch};
             uint64_t rstrides[3] = {rpix, rpix * g.out_w, rpix * g.out_w * g.out_h};
             DNB_TRY(encode_tensor_map(&a.tmr, bf16, 4, const_cast<void *>(residual), rdims, rstrides, box, srb));
         }
@@ -465,7 +495,7 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
         if (o->layout == DNB_NHWC) { y_nhwc = o->data; y_dtype = o->dtype; y_cpitch = o->cpitch; }
         else y_nchw = (float *)o->data;
     }
-    ConvEpilogue ep{p->scale, p->shift, p->d.activation, 0, nullptr, 0, DNB_LINEAR, 1.f, 1.f};
+    ConvEpilogue ep{p->scale, p->shift, p->d.activation, 0, nullptr, 0, DNB_LINEAR, 1.f, 1.f, 0};
     if (res && res->add) {
         if (p->kernel != K_TC_TF32 && p->kernel != K_TC_BF16)
             DNB_FAIL(DNB_EUNSUPPORTED, "conv + shortcut: only tensor-core plans fuse the residual (this plan is %s)", kKernelNames[p->kernel]);
@@ -500,6 +530,35 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
         a.y_nhwc = y_nhwc; a.y_dtype = y_dtype; a.y_cpitch = y_cpitch; a.y_nchw = y_nchw;
         a.g = g; a.ep = ep;
         return launch_conv_direct(a, s);
+    }
+    if (p->kernel == K_XNOR && p->xnor_tc) {
+        // tensor-core xnor: the input's signs as an int8 channels-last tensor (one pass over the input), then the
+        // implicit-GEMM kernel in its int8 kind; out-of-image taps are the TMA unit's zero fill, i.e. they add nothing,
+        // as in the reference, where the padding is applied after the binarisation (src/im2col.c:3-12)
+        const size_t need = (size_t)g.batch * g.h * g.w * p->c_pad_i8;
+        if (need > p->x_i8_bytes) {
+            cudaFree(p->x_i8);
+            p->x_i8 = nullptr; p->x_i8_bytes = 0;
+            DNB_CUDA(cudaMalloc((void **)&p->x_i8, need));
+            p->x_i8_bytes = need;
+            p->tc_x_ptr = nullptr;
+        }
+        DNB_TRY(launch_pack_sign_i8(x, p->x_i8, p->c_pad_i8, s));
+        dnb_tensor xin{p->x_i8, DNB_NHWC, DNB_F32, g.batch, g.c, g.h, g.w, p->c_pad_i8};   // dtype unused: the plan's kind says int8
+        if (y_nhwc && y_dtype != DNB_F32) DNB_FAIL(DNB_EINVAL, "conv: an xnor plan writes channels-last output as f32");
+        float *nchw = acc_out ? reinterpret_cast<float *>(acc_out) : y_nchw;
+        void *nhwc = acc_out ? nullptr : y_nhwc;
+        if (p->tc_x_ptr != xin.data || p->tc_y_ptr != nhwc || p->tc_y_cpitch != (nhwc ? y_cpitch : 0) || !p->status)
+            DNB_TRY(build_tc_args(p, &xin, nhwc, DNB_F32, nhwc ? y_cpitch : 0, nullptr, 0));
+        TcArgs &a = p->tc;
+        a.y_nhwc = nhwc; a.y_dtype = DNB_F32; a.y_cpitch = nhwc ? y_cpitch : 0; a.y_nchw = nchw;
+        ep.scale = p->scale_i8;
+        ep.round_tf32 = 0;
+        ep.raw_acc = acc_out ? 1 : 0;
+        if (acc_out) ep.activation = DNB_LINEAR;
+        a.ep = ep;
+        a.status = p->status;
+        return launch_conv_tc(a, s);
     }
     if (p->kernel == K_XNOR) {
         const size_t need = (size_t)g.batch * g.h * g.w * p->cwords * sizeof(uint32_t);

@@ -247,10 +247,10 @@ conv_stem_tc_kernel(const __grid_constant__ StemTcArgs a)
         if (tid == 0) {
             tc_fence_after();
             const uint64_t da = da0 + (uint64_t)(buf * (ST_A_BYTES >> 4));
-            umma<false>(tmem_base, da, db, idesc, 0u);
-            umma<false>(tmem_base, da + 2, db + 2, idesc, 1u);
-            umma<false>(tmem_base, da + 4, db + 4, idesc, 1u);
-            umma<false>(tmem_base, da + 6, db + 6, idesc, 1u);
+            umma<MMA_TF32>(tmem_base, da, db, idesc, 0u);
+            umma<MMA_TF32>(tmem_base, da + 2, db + 2, idesc, 1u);
+            umma<MMA_TF32>(tmem_base, da + 4, db + 4, idesc, 1u);
+            umma<MMA_TF32>(tmem_base, da + 6, db + 6, idesc, 1u);
             umma_commit(bar0);
         }
         __syncwarp();
@@ -402,10 +402,10 @@ conv_stem_tc_wide_kernel(const __grid_constant__ StemTcArgs a)
             if (tid == 0) {
                 tc_fence_after();
                 const uint64_t da = da0 + (uint64_t)(buf * (ST_A_BYTES >> 4)), db = db0 + kb * b_step;
-                umma<false>(tmem_base, da, db, idesc, kb > 0 ? 1u : 0u);
-                umma<false>(tmem_base, da + 2, db + 2, idesc, 1u);
-                umma<false>(tmem_base, da + 4, db + 4, idesc, 1u);
-                umma<false>(tmem_base, da + 6, db + 6, idesc, 1u);
+                umma<MMA_TF32>(tmem_base, da, db, idesc, kb > 0 ? 1u : 0u);
+                umma<MMA_TF32>(tmem_base, da + 2, db + 2, idesc, 1u);
+                umma<MMA_TF32>(tmem_base, da + 4, db + 4, idesc, 1u);
+                umma<MMA_TF32>(tmem_base, da + 6, db + 6, idesc, 1u);
                 umma_commit(done0 + 8 * buf);
                 if (kb == KB - 1) umma_commit(acc_bar);
             }

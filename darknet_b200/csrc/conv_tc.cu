@@ -86,7 +86,10 @@ __device__ __forceinline__ float act_apply(float x, int runtime_act)
 // adjacent pixel tiles (one per CTA) under one 256-filter tile; each CTA loads its own 128 pixels and HALF of the
 // weight tile, so a third fewer operand bytes cross L2 -> shared memory per MMA and the ring is six slots deep.
 // The even CTA issues the MMAs for both; each CTA drains its own 128 accumulator rows.
-template <int ACT, int CPC, bool OUT_BF16, int ACT2, bool PAIR>
+// I8: operands are int8 sign tensors (+1 / -1, 0 in padding channels and, through the TMA zero fill, outside the
+// image), products accumulate exactly in int32 (kind::i8): the xnor convolution on the tensor cores.  The epilogue
+// converts the integer sums to float and continues as for the other kinds (output f32, OUT_BF16 false).
+template <int ACT, int CPC, bool OUT_BF16, int ACT2, bool PAIR, bool I8 = false>
 __global__ void __launch_bounds__(TC_THREADS)
 conv_tc_kernel(const __grid_constant__ TcArgs a)
 {
@@ -245,9 +248,8 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         // below the 4 x 128 cycles the tensor pipe needs for the slot's MMAs, so everything is in registers:
         // barrier addresses and operand descriptors advance by constants, the accumulator-ready commit
         // sits after the k loop.
-        constexpr bool is_bf16 = OUT_BF16;       // operands and channels-last output share the storage type
-        const uint32_t fmt = is_bf16 ? 1u : 2u;  // BF16 : TF32
-        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bn >> 3) << 17) | (((PAIR ? 256u : 128u) >> 4) << 24);
+        constexpr int is_bf16 = I8 ? MMA_I8 : (OUT_BF16 ? MMA_BF16 : MMA_TF32);   // operand kind of the MMAs
+        const uint32_t idesc = mma_idesc<is_bf16>(PAIR ? 256u : 128u, (uint32_t)bn);
         const int k_steps = row_bytes / 32;      // one MMA consumes 32 bytes of K per row
         const uint64_t da0 = make_smem_desc(ring, row_bytes), db0 = make_smem_desc(ring + a_bytes, row_bytes);
         const uint64_t slot_step = stage_bytes >> 4;   // descriptor address field counts 16-byte units
@@ -349,6 +351,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         void *const y_nhwc = a.y_nhwc;
         float *const y_nchw = a.y_nchw;
         const int runtime_act = a.ep.activation, do_round = a.ep.round_tf32;
+        const bool raw_acc = I8 && a.ep.raw_acc != 0;
         constexpr bool residual = ACT2 != ACT2_NONE;
         // A CTA pair reads the residual with plain 16-byte loads, one staged chunk ahead, instead of TMA tiles into the
         // staging buffers: residual tile loads inside the pair kernel raised an illegal-instruction fault on B200 whose
@@ -474,7 +477,8 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int j = 4 * q + e;
-                        float t = act_apply<ACT>(fmaf(__uint_as_float(r[j]), scv[e], sfv[e]), runtime_act);
+                        const float accv = I8 ? (float)(int)r[j] : __uint_as_float(r[j]);   // int32 sums of an xnor layer are exact in f32 (below 2^24)
+                        float t = act_apply<ACT>(fmaf(accv, scv[e], sfv[e]), runtime_act);
                         if (residual) {
                             float rv = 0.f;
                             {
@@ -494,7 +498,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                         // linear and leaky epilogues produce the zero by themselves; others need the mask
                         constexpr bool self_zero = (ACT == DNB_LINEAR || ACT == DNB_LEAKY) &&
                                                    (ACT2 == ACT2_NONE || ACT2 == DNB_LINEAR || ACT2 == DNB_LEAKY);
-                        r[j] = __float_as_uint((self_zero || j < nvalid) ? t : 0.f);
+                        if (!(I8 && raw_acc)) r[j] = __float_as_uint((self_zero || j < nvalid) ? t : 0.f);   // raw: the integer sums themselves
                     }
                 }
                 const uint32_t buf = chunk_count & buf_mask;
@@ -620,7 +624,7 @@ static int max_pair_clusters(K kernel, size_t smem)
 int launch_conv_tc(const TcArgs &a, cudaStream_t s)
 {
     const size_t smem = conv_tc_smem_bytes(a);
-    const bool obf = a.is_bf16 != 0;
+    const bool obf = a.is_bf16 == 1, i8 = a.is_bf16 == 2;   // int8 operands write f32 output
     const int cpc = a.store_row_bytes / (obf ? 2 : 4);
     if (cpc != 16 && cpc != 32 && cpc != 64) DNB_FAIL(DNB_EINVAL, "conv_tc: staged row of %d bytes", a.store_row_bytes);
     const int slots = sm_count() * a.ctas_per_sm;
@@ -651,6 +655,46 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
         cfg.attrs = attr; cfg.numAttrs = 1;                                                                                      \
         DNB_CUDA(cudaLaunchKernelEx(&cfg, kern, a));                                                                             \
     } while (0)
+#define DNB_TC_LAUNCH_I8(ACT, CPC)                                                                                               \
+    do {                                                                                                                         \
+        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<ACT, CPC, false, ACT2_NONE, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)); \
+        conv_tc_kernel<ACT, CPC, false, ACT2_NONE, false, true><<<grid, TC_THREADS, smem, s>>>(a);                              \
+    } while (0)
+#define DNB_TC_LAUNCH_I8_PAIR(ACT)                                                                                               \
+    do {                                                                                                                         \
+        auto kern = conv_tc_kernel<ACT, 32, false, ACT2_NONE, true, true>;                                                       \
+        DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));                            \
+        const int clusters_max = max_pair_clusters(kern, smem);                                                                  \
+        const int clusters = a.total_tiles < clusters_max ? a.total_tiles : clusters_max;                                        \
+        cudaLaunchConfig_t cfg = {};                                                                                             \
+        cfg.gridDim = dim3(2 * (unsigned)clusters);                                                                              \
+        cfg.blockDim = dim3(TC_THREADS);                                                                                         \
+        cfg.dynamicSmemBytes = smem;                                                                                             \
+        cfg.stream = s;                                                                                                          \
+        cudaLaunchAttribute attr[1];                                                                                             \
+        attr[0].id = cudaLaunchAttributeClusterDimension;                                                                        \
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;                                \
+        cfg.attrs = attr; cfg.numAttrs = 1;                                                                                      \
+        DNB_CUDA(cudaLaunchKernelEx(&cfg, kern, a));                                                                             \
+    } while (0)
+#define DNB_TC_LAUNCH_I8_ACT(ACT)                                           \
+    do {                                                                    \
+        if (a.pair && cpc == 32) DNB_TC_LAUNCH_I8_PAIR(ACT);                \
+        else if (a.pair) DNB_FAIL(DNB_EINVAL, "conv_tc: pair mode needs 128-byte staged rows"); \
+        else if (cpc == 32) DNB_TC_LAUNCH_I8(ACT, 32);                      \
+        else if (cpc == 16) DNB_TC_LAUNCH_I8(ACT, 16);                      \
+        else DNB_FAIL(DNB_EINVAL, "conv_tc: no int8 kernel for %d columns per chunk", cpc); \
+    } while (0)
+    if (i8) {
+        if (a.ep.residual) DNB_FAIL(DNB_EUNSUPPORTED, "conv_tc: the int8 (xnor) kernel fuses no residual");
+        switch (a.ep.activation) {
+        case DNB_LINEAR: DNB_TC_LAUNCH_I8_ACT(DNB_LINEAR); break;
+        case DNB_LEAKY: DNB_TC_LAUNCH_I8_ACT(DNB_LEAKY); break;
+        default: DNB_TC_LAUNCH_I8_ACT(ACT_GENERIC); break;
+        }
+        DNB_LAUNCH_CHECK("conv_tc (int8)");
+        return DNB_OK;
+    }
 #define DNB_TC_LAUNCH_ACT(ACT, ACT2)                                        \
     do {                                                                    \
         if (a.pair && !obf && cpc == 32) DNB_TC_LAUNCH_PAIR(ACT, 32, false, ACT2); \
@@ -680,6 +724,9 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
 #undef DNB_TC_LAUNCH_ACT
 #undef DNB_TC_LAUNCH_PAIR
 #undef DNB_TC_LAUNCH
+#undef DNB_TC_LAUNCH_I8_ACT
+#undef DNB_TC_LAUNCH_I8_PAIR
+#undef DNB_TC_LAUNCH_I8
     DNB_LAUNCH_CHECK("conv_tc");
     return DNB_OK;
 }
@@ -688,7 +735,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-int encode_tensor_map(CUtensorMap *map, int is_bf16, int rank, void *base, const uint64_t *dims,
+int encode_tensor_map(CUtensorMap *map, int elem_kind, int rank, void *base, const uint64_t *dims,
                       const uint64_t *strides_bytes, const uint32_t *box, int swizzle_bytes)
 {
     static EncodeTiledFn fn = nullptr;
@@ -705,7 +752,8 @@ int encode_tensor_map(CUtensorMap *map, int is_bf16, int rank, void *base, const
     for (int i = 0; i + 1 < rank; ++i) st[i] = strides_bytes[i];
     CUtensorMapSwizzle sw = swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                             : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
-    CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, base,
+    const CUtensorMapDataType dt = elem_kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : (elem_kind == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
+    CUresult r = fn(map, dt, (cuuint32_t)rank, base,
                     d, st, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)

@@ -232,6 +232,57 @@ int launch_pack_sign_bits(const dnb_tensor *x, uint32_t *bits, int cwords, cudaS
     return DNB_OK;
 }
 
+// ------------------------------------------------------------------ int8 signs for the tensor-core xnor convolution
+// One thread per (pixel, group of 16 channels): +1 where x > 0, -1 elsewhere (the CPU reference's test, so 0 maps to -1),
+// 0 for channels beyond the layer's (they must add nothing to the sums); 16 bytes written per thread.
+template <typename T, bool NCHW>
+__global__ void __launch_bounds__(256)
+pack_sign_i8_kernel(const T *__restrict__ x, int8_t *__restrict__ out, size_t npix, size_t HW, int C, int Cp_in, int cpad)
+{
+    const int groups = cpad / 16;
+    const size_t total = npix * groups;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        size_t p;
+        int gq;
+        if (NCHW) { p = i % npix; gq = (int)(i / npix); }      // consecutive threads: consecutive pixels of one channel group
+        else { p = i / groups; gq = (int)(i - p * groups); }   // consecutive threads: consecutive groups of one pixel
+        const int c0 = gq * 16;
+        uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const int c = c0 + k;
+            float v = 0.f;
+            bool in = c < C;
+            if (in) {
+                if (NCHW) {
+                    const size_t b = p / HW, hw = p - b * HW;
+                    v = __ldg(reinterpret_cast<const float *>(x) + (b * C + c) * HW + hw);
+                } else if (sizeof(T) == 4) {
+                    v = __ldg(reinterpret_cast<const float *>(x) + p * Cp_in + c);
+                } else {
+                    v = __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(x)[p * Cp_in + c]);
+                }
+            }
+            const uint32_t byte = in ? (v > 0.f ? 0x01u : 0xffu) : 0u;
+            w[k >> 2] |= byte << (8 * (k & 3));
+        }
+        *reinterpret_cast<uint4 *>(out + p * cpad + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+int launch_pack_sign_i8(const dnb_tensor *x, int8_t *out, int cpad, cudaStream_t s)
+{
+    const size_t npix = (size_t)x->n * x->h * x->w, HW = (size_t)x->h * x->w;
+    const size_t total = npix * (cpad / 16);
+    const size_t blocks = (total + 255) / 256, cap = (size_t)sm_count() * 16;
+    const int grid = (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
+    if (x->layout == DNB_NCHW) pack_sign_i8_kernel<float, true><<<grid, 256, 0, s>>>((const float *)x->data, out, npix, HW, x->c, 0, cpad);
+    else if (x->dtype == DNB_F32) pack_sign_i8_kernel<float, false><<<grid, 256, 0, s>>>((const float *)x->data, out, npix, HW, x->c, x->cpitch, cpad);
+    else pack_sign_i8_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>((const __nv_bfloat16 *)x->data, out, npix, HW, x->c, x->cpitch, cpad);
+    DNB_LAUNCH_CHECK("pack_sign_i8");
+    return DNB_OK;
+}
+
 }  // namespace dnb
 
 // ------------------------------------------------------------------ entry point that allocates nothing

@@ -170,25 +170,28 @@ int launch_maxpool(const dnb_tensor *x, const dnb_tensor *y, int size, int strid
 // One output row (b, oh) per block iteration; see maxpool_nhwc_kernel.
 template <typename T>
 __global__ void __launch_bounds__(256)
-upsample_nhwc_kernel(const T *__restrict__ x, T *__restrict__ y, int B, int H, int W, int cvecs, int stride, float scale)
+upsample_nhwc_kernel(const T *__restrict__ x, T *__restrict__ y, int B, int H, int W, int cvecs, int xpitch_vecs, int ypitch_vecs,
+                     int stride, float scale)
 {
+    // cvecs 16-byte vectors of channels per pixel are copied; input and output pixels may be further apart than that
+    // (a tensor that is a channel range of a wider one, e.g. the slice of a [route] output it was placed in)
     using V = Vec16<T>;
     const int OH = H * stride, OW = W * stride;
     const int rows = B * OH, row_vecs = OW * cvecs;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const int b = row / OH, oh = row - b * OH;
-        const uint4 *xrow = reinterpret_cast<const uint4 *>(x) + ((size_t)b * H + oh / stride) * W * cvecs;
-        uint4 *yrow = reinterpret_cast<uint4 *>(y) + (size_t)row * row_vecs;
+        const uint4 *xrow = reinterpret_cast<const uint4 *>(x) + ((size_t)b * H + oh / stride) * W * xpitch_vecs;
+        uint4 *yrow = reinterpret_cast<uint4 *>(y) + (size_t)row * OW * ypitch_vecs;
 #pragma unroll 4
         for (int j = threadIdx.x; j < row_vecs; j += blockDim.x) {
             const int ow = j / cvecs, cv = j - ow * cvecs;
             V v;
-            v.raw = __ldg(xrow + (ow / stride) * cvecs + cv);
+            v.raw = __ldg(xrow + (ow / stride) * xpitch_vecs + cv);
             if (scale != 1.f) {
 #pragma unroll
                 for (int k = 0; k < V::N; ++k) v.v[k] = from_float<T>(scale * to_float<T>(v.v[k]));
             }
-            yrow[j] = v.raw;
+            yrow[ow * ypitch_vecs + cv] = v.raw;
         }
     }
 }
@@ -216,13 +219,16 @@ int launch_upsample(const dnb_tensor *x, const dnb_tensor *y, int stride, float 
         DNB_FAIL(DNB_EINVAL, "upsample: output extents do not match input x%d", stride);
     if (x->layout != y->layout || x->dtype != y->dtype) DNB_FAIL(DNB_EINVAL, "upsample: input and output differ in layout or dtype");
     if (x->layout == DNB_NHWC) {
-        if (x->cpitch != y->cpitch) DNB_FAIL(DNB_EINVAL, "upsample: cpitch differs");
+        // the channels copied per pixel: the narrower of the two pitches (equal pitches: all of them, padding included)
+        const int per = x->dtype == DNB_F32 ? 4 : 8;
+        const int cv = (x->cpitch < y->cpitch ? x->cpitch : y->cpitch) / per;
+        if (cv * per < x->c || x->cpitch % per || y->cpitch % per) DNB_FAIL(DNB_EINVAL, "upsample: channel pitches %d and %d for %d channels", x->cpitch, y->cpitch, x->c);
         if (x->dtype == DNB_F32) {
-            int cv = x->cpitch / 4;
-            upsample_nhwc_kernel<float><<<row_grid(y->n, y->h), 256, 0, s>>>((const float *)x->data, (float *)y->data, x->n, x->h, x->w, cv, stride, scale);
+            upsample_nhwc_kernel<float><<<row_grid(y->n, y->h), 256, 0, s>>>((const float *)x->data, (float *)y->data, x->n, x->h, x->w, cv, x->cpitch / per,
+                                                                            y->cpitch / per, stride, scale);
         } else {
-            int cv = x->cpitch / 8;
-            upsample_nhwc_kernel<__nv_bfloat16><<<row_grid(y->n, y->h), 256, 0, s>>>((const __nv_bfloat16 *)x->data, (__nv_bfloat16 *)y->data, x->n, x->h, x->w, cv, stride, scale);
+            upsample_nhwc_kernel<__nv_bfloat16><<<row_grid(y->n, y->h), 256, 0, s>>>((const __nv_bfloat16 *)x->data, (__nv_bfloat16 *)y->data, x->n, x->h, x->w,
+                                                                                    cv, x->cpitch / per, y->cpitch / per, stride, scale);
         }
     } else {
         if (x->dtype != DNB_F32) DNB_FAIL(DNB_EINVAL, "upsample: NCHW tensors must be f32");
@@ -453,6 +459,10 @@ int launch_route(const dnb_tensor *const *inputs, int count, const dnb_tensor *y
     int coff = 0;
     for (int i = 0; i < count; ++i) {
         const dnb_tensor *t = inputs[i];
+        if (y->layout == DNB_NHWC && t->data == (char *)y->data + (size_t)coff * es && t->cpitch == y->cpitch) {
+            coff += t->c;   // this input IS its channel range of the output (its producer wrote it there): nothing to copy
+            continue;
+        }
         if (y->layout == DNB_NHWC) {
             size_t rows = (size_t)t->n * t->h * t->w;
             DNB_TRY(copy2d(t->data, (char *)y->data + (size_t)coff * es, rows, (size_t)t->c * es, (size_t)t->cpitch * es, (size_t)y->cpitch * es, s));

@@ -53,6 +53,9 @@ struct Layer {
     int launches = 1;
     // a convolution that also performs the [shortcut] layer right after it, and that shortcut layer
     bool fuses_next_shortcut = false, fused_into_prev = false;
+    // the output is a channel range of a later [route] layer's output: its producer writes it in place and the route
+    // has nothing to copy for it (the memory belongs to the route layer)
+    bool out_is_view = false;
 };
 
 typedef std::map<std::string, std::string> Options;
@@ -334,6 +337,47 @@ static int build_network(const char *text, int mode, int batch_override, dnb_net
         cudaFree(C.out.data);      // never written: the convolution stores straight into the shortcut's output
         C.out.data = nullptr;
     }
+    // Zero-copy [route]: where a route input is produced by a layer whose kernel can write a channel range of a wider
+    // channels-last tensor (tensor-core convolutions, with or without a fused shortcut, and upsample), and everything that
+    // reads it can read such a range (convolutions, routes, the yolo head, upsample), the input's tensor BECOMES its
+    // range of the route's output: forward_route_layer_gpu's copies (src/route_layer.c:105-118) disappear.
+    // DNB_ROUTE_ALIAS=0 keeps every layer's own tensor.
+    const bool alias = getenv("DNB_ROUTE_ALIAS") ? atoi(getenv("DNB_ROUTE_ALIAS")) != 0 : true;
+    for (int r = 0; alias && r < (int)net->layers.size(); ++r) {
+        Layer &R = net->layers[r];
+        if (R.kind != L_ROUTE) continue;
+        const size_t es = elem_size(R.out.dtype);
+        int off = 0, copies = 0;
+        for (size_t k = 0; k < R.inputs.size(); ++k) {
+            const int id = R.inputs[k];
+            Layer &P = net->layers[id];
+            const int this_off = off;
+            off += P.out_c;
+            ++copies;
+            const bool last_input = k + 1 == R.inputs.size();
+            if (P.out_is_view || !P.out.data || P.out.layout != DNB_NHWC) continue;
+            if ((size_t)this_off * es % 128 || (!last_input && P.out_c % 8)) continue;
+            bool writer_ok = false;
+            if (P.kind == L_UPSAMPLE) writer_ok = true;
+            if (P.kind == L_CONV && P.plan && (P.plan->kernel == 0 || P.plan->kernel == 1) && !P.plan->stem_tc) writer_ok = true;
+            if (P.kind == L_SHORTCUT && P.fused_into_prev) writer_ok = true;   // written by the convolution before it
+            if (!writer_ok) continue;
+            bool readers_ok = true;
+            for (int j = id + 1; j < (int)net->layers.size() && readers_ok; ++j) {
+                const Layer &C = net->layers[j];
+                const bool reads_as_input = j == id + 1 && C.kind != L_ROUTE && !(C.kind == L_SHORTCUT && C.fused_into_prev);
+                if (reads_as_input && !(C.kind == L_CONV && !C.plan->stem_tc) && C.kind != L_YOLO && C.kind != L_UPSAMPLE) readers_ok = false;
+                if (C.kind == L_SHORTCUT && C.from == id && !C.fused_into_prev) readers_ok = false;   // the stand-alone kernel wants equal pitches
+            }
+            if (!readers_ok) continue;
+            cudaFree(P.out.data);
+            P.out.data = (char *)R.out.data + (size_t)this_off * es;
+            P.out.cpitch = R.out.cpitch;
+            P.out_is_view = true;
+            --copies;
+        }
+        R.launches = copies;
+    }
     const Layer &last = net->layers.back();
     net->outputs = last.out_c * last.out_h * last.out_w;
     DNB_CUDA(cudaMalloc((void **)&net->input_dev, (size_t)net->batch * net->inputs * sizeof(float)));
@@ -394,7 +438,7 @@ extern "C" void dnb_free_network(dnb_network *net)
     if (!net) return;
     for (Layer &L : net->layers) {
         if (L.plan) dnb_conv_plan_destroy(L.plan);
-        cudaFree(L.out.data);
+        if (!L.out_is_view) cudaFree(L.out.data);
         for (float *hp : L.host_slot) if (hp) cudaFreeHost(hp);
         if (L.copied) cudaEventDestroy(L.copied);
     }
@@ -437,7 +481,7 @@ static int set_connected_params(dnb_network *net, Layer &L, int index, const flo
     return dnb_conv_plan_set_params(L.plan, packed.data(), biases, scales, mean, var);
 }
 
-extern "C" int dnb_load_weights(dnb_network *net, const char *path)
+static int load_weights_impl(dnb_network *net, const char *path, bool packed)
 {
     if (!net || !path) DNB_FAIL(DNB_EINVAL, "load_weights: null argument");
     FILE *f = fopen(path, "rb");
@@ -470,7 +514,21 @@ extern "C" int dnb_load_weights(dnb_network *net, const char *path)
                      fread(mean.data(), sizeof(float), d.n, f) == (size_t)d.n &&
                      fread(var.data(), sizeof(float), d.n, f) == (size_t)d.n;
             }
-            ok = ok && fread(weights.data(), sizeof(float), nw, f) == nw;
+            if (ok && packed && d.xnor) {
+                // load_convolutional_weights_binary (src/parser.c:1134-1162): per filter its mean |w| as a float, then one
+                // bit per weight (set: +mean, clear: -mean), eight to a byte, lowest bit first.  The reference stores
+                // size/8 bytes per filter, so a filter whose c*size*size is not a multiple of 8 would lose its tail.
+                const size_t per = nw / d.n;
+                if (per % 8) DNB_FAIL(DNB_EUNSUPPORTED, "%s: layer %d has %zu weights per filter; the packed format holds whole bytes of 8 only", path, index, per);
+                std::vector<unsigned char> bits(per / 8);
+                for (int n = 0; n < d.n && ok; ++n) {
+                    float mean = 0;
+                    ok = fread(&mean, sizeof(float), 1, f) == 1 && fread(bits.data(), 1, per / 8, f) == per / 8;
+                    for (size_t k = 0; ok && k < per; ++k) weights[(size_t)n * per + k] = (bits[k / 8] >> (k % 8)) & 1 ? mean : -mean;
+                }
+            } else {
+                ok = ok && fread(weights.data(), sizeof(float), nw, f) == nw;
+            }
             if (!ok) DNB_FAIL(DNB_EIO, "%s: file ends inside layer %d (the reference would silently keep its random initialisation)", path, index);
             if (L.flipped) {
                 // transpose_matrix(l.weights, l.c*l.size*l.size, l.n) (src/parser.c:1206-1208, 1085-1096): the file holds
@@ -511,6 +569,11 @@ extern "C" int dnb_load_weights(dnb_network *net, const char *path)
     drop_graph(net);   // a captured forward holds the pointers of the parameter tensors just replaced
     return DNB_OK;
 }
+
+extern "C" int dnb_load_weights(dnb_network *net, const char *path) { return load_weights_impl(net, path, false); }
+
+// The same file format with every xnor convolution stored packed (mean |w| and one sign bit per weight).
+extern "C" int dnb_load_weights_packed(dnb_network *net, const char *path) { return load_weights_impl(net, path, true); }
 
 // The same derived tensors from host arrays instead of a file: what a host that has already run the
 // reference's load_weights holds in l.weights, l.biases, l.scales, l.rolling_mean, l.rolling_variance.

@@ -123,15 +123,22 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int row_bytes)
     return d;
 }
 
-// The operand kind is a template parameter on purpose: with a run-time `if` the compiler predicates BOTH
-// tcgen05.mma instructions, and the predicated-off one still occupies the tensor pipe's issue path.
-template <bool IS_BF16>
+// The operand kind is a template parameter on purpose: with a run-time `if` the compiler predicates ALL the
+// tcgen05.mma instructions, and the predicated-off ones still occupy the tensor pipe's issue path.
+// KIND: 0 kind::tf32 (f32 operands), 1 kind::f16 (bf16 operands), 2 kind::i8 (int8 operands, int32 accumulators).
+enum { MMA_TF32 = 0, MMA_BF16 = 1, MMA_I8 = 2 };
+template <int KIND>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
 {
-    if (IS_BF16) {
+    if (KIND == MMA_BF16) {
         asm volatile(
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    } else if (KIND == MMA_I8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
             ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
     } else {
         asm volatile(
@@ -139,6 +146,14 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t 
             "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
             ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
     }
+}
+// Instruction descriptor of a dense K-major x K-major MMA of m rows and n columns: accumulator format (bits 4-5: f32,
+// or s32 for int8), operand formats (bits 7-9 and 10-12: tf32 = 2, bf16 = 1, signed int8 = 1), n / 8 from bit 17, m / 16 from bit 24.
+template <int KIND>
+__device__ __forceinline__ uint32_t mma_idesc(uint32_t m, uint32_t n)
+{
+    const uint32_t cfmt = KIND == MMA_I8 ? 2u : 1u, fmt = KIND == MMA_TF32 ? 2u : 1u;
+    return (cfmt << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
@@ -185,13 +200,18 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(map), "r"(leader_bar(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
-template <bool IS_BF16>
+template <int KIND>
 __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
 {
-    if (IS_BF16) {
+    if (KIND == MMA_BF16) {
         asm volatile(
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    } else if (KIND == MMA_I8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
             ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
     } else {
         asm volatile(

@@ -13,6 +13,7 @@
  *     forward_upsample_layer_gpu        src/upsample_layer.c:88-96
  *     forward_shortcut_layer_gpu        src/shortcut_layer.c:75-80
  *     forward_route_layer_gpu           src/route_layer.c:105-118
+ *     forward_yolo_layer_gpu            src/yolo_layer.c:347-362 (the inference branch: activations, then the pull)
  * Errors follow the reference's convention: print and exit through error() (src/utils.c:253-258).
  */
 #include <stdio.h>
@@ -115,6 +116,23 @@ static void forward_route_layer_b200(layer l, network net)
     if (dnb_route_forward(ptrs, l.n, &y, NULL)) fail("route");
 }
 
+/* forward_yolo_layer_gpu at inference (src/yolo_layer.c:347-362): copy the input, apply the logistic to the x, y,
+ * objectness and class entries of every anchor (2 * batch * anchors launches there, one here), pull the result to
+ * l.output, where get_yolo_detections reads it (src/yolo_layer.c:316-343). */
+static void forward_yolo_layer_b200(layer l, network net)
+{
+    if (net.train && !l.onlyforward) {   /* the training branch (loss on the host) stays the reference's */
+        attached *a = find_attached(net.layers);
+        if (!a || net.index < 0 || net.index >= a->n || !a->original[net.index]) error("darknet_b200: yolo layer called on a network that is not attached");
+        a->original[net.index](l, net);
+        return;
+    }
+    dnb_tensor x = nchw(net.input_gpu, l.batch, l.c, l.h, l.w);
+    dnb_tensor y = nchw(l.output_gpu, l.batch, l.c, l.h, l.w);
+    if (dnb_yolo_forward(&x, &y, l.n, l.classes, NULL)) fail("yolo");
+    cuda_pull_array(l.output_gpu, l.output, (size_t)l.batch * l.outputs);
+}
+
 static int route_is_covered(const network *net, const layer *l)
 {
     if (l->n < 1 || l->n > 16) return 0;
@@ -189,6 +207,8 @@ int b200_attach(network *net, int mode)
             repl = forward_shortcut_layer_b200;
         } else if (l->type == ROUTE && route_is_covered(net, l)) {
             repl = forward_route_layer_b200;
+        } else if (l->type == YOLO && l->c == l->n * (l->classes + 4 + 1) && l->output && l->output_gpu) {
+            repl = forward_yolo_layer_b200;
         }
         if (repl) {
             a->original[i] = l->forward_gpu;

@@ -270,8 +270,23 @@ def seeded_params(cfg_text: str, seed: int = 0, pow2_mean_xnor: bool = False) ->
     return out
 
 
+def packed_filter_bytes(w: np.ndarray) -> bytes:
+    """One convolution's weights [n, ...] in the reference's packed-binary form (save_convolutional_weights_binary,
+    src/parser.c:926-956): per filter the mean |w| (summed in a float in index order, src/convolutional_layer.c:28-41)
+    and size/8 bytes of sign bits, lowest bit first, set where w > 0."""
+    n = w.shape[0]
+    flat = np.ascontiguousarray(w, np.float32).reshape(n, -1)
+    size = flat.shape[1]
+    mean = np.zeros(n, np.float32)
+    for k in range(size):
+        mean += np.abs(flat[:, k])
+    mean = (mean / np.float32(size)).astype(np.float32)
+    bits = np.packbits((flat[:, :size // 8 * 8] > 0).astype(np.uint8), axis=1, bitorder="little")
+    return b"".join(mean[i].tobytes() + bits[i].tobytes() for i in range(n))
+
+
 def write_weights(path: str, params: list[ConvParams], seen: int = 0, version: tuple[int, int, int] = (0, 2, 0),
-                  flipped: set[int] | frozenset = frozenset()) -> None:
+                  flipped: set[int] | frozenset = frozenset(), packed: set[int] | frozenset = frozenset()) -> None:
     """Write a ``.weights`` file: header major, minor, revision and ``seen`` (64-bit from version 0.2 on,
     32-bit before; src/parser.c:1018-1024, 1234-1241), then each layer's arrays in load order.
     A major or minor version above 1000 marks a file whose connected-layer matrices are stored
@@ -296,6 +311,9 @@ def write_weights(path: str, params: list[ConvParams], seen: int = 0, version: t
             else:
                 for a in bn:
                     f.write(np.ascontiguousarray(a, dtype=np.float32).tobytes())
+                if i in packed:       # positions in ``params`` of convolutions stored in the packed-binary form
+                    f.write(packed_filter_bytes(w))
+                    continue
                 if i in flipped:
                     w = np.ascontiguousarray(w.reshape(w.shape[0], -1).T)
                 f.write(w.tobytes())

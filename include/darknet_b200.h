@@ -271,6 +271,14 @@ int dnb_parse_network_cfg_text(const char *cfg_text, int mode, int batch_overrid
  * reads them. */
 int dnb_load_weights(dnb_network *net, const char *weights_path);
 
+/* load_weights for a file in which every convolution with xnor=1 is stored in the reference's packed-binary layer
+ * format (load_convolutional_weights_binary / save_convolutional_weights_binary, src/parser.c:1134-1162, 926-956:
+ * biases and batchnorm vectors as usual, then per filter its mean |w| as a float and one bit per weight, eight to a
+ * byte, lowest bit first; set = +mean).  The reference carries the format but leaves its call sites commented out
+ * (src/parser.c:961, 1167); it is the natural on-disk form of an xnor network, 32 times smaller.  Filters whose
+ * c*size*size is not a multiple of 8 are refused (the reference's size/8 bytes per filter would drop their tail). */
+int dnb_load_weights_packed(dnb_network *net, const char *weights_path);
+
 /* load_weights for a host that already holds the parameters in memory: the arrays the reference's
  * load_convolutional_weights fills (src/parser.c:1164-1215) for convolution `layer`, or load_connected_weights
  * (src/parser.c:1098-1120; weights [outputs][inputs]) for a connected layer.  Once every such layer

@@ -269,6 +269,11 @@ class Reference:
         L.ref_gemm_nn.argtypes = [C.c_int] * 3 + [C.c_void_p] * 3
         if hasattr(L, "ref_save_weights"):
             L.ref_save_weights.argtypes = [C.c_void_p, C.c_char_p]
+        if hasattr(L, "ref_save_conv_binary"):
+            L.ref_save_conv_binary.argtypes = [C.c_void_p, C.c_int, C.c_char_p]
+            L.ref_load_conv_binary.argtypes = [C.c_void_p, C.c_int, C.c_char_p]
+            L.ref_layer_weights.restype = C.POINTER(C.c_float)
+            L.ref_layer_weights.argtypes = [C.c_void_p, C.c_int]
         self.L = L
 
     def load(self, cfg_path: str, weights_path: str | None):

@@ -67,6 +67,30 @@ int ref_is_gpu_build(void) { return 0; }
 float *ref_network_predict(void *h, float *input) { return network_predict((network *)h, input); }
 void ref_save_weights(void *h, char *path) { save_weights((network *)h, path); }
 
+/* The reference's packed-binary layer writer and reader (src/parser.c:926-956, 1134-1162), which its own
+ * save_weights / load_weights leave commented out: layer i of the network to / from a file of its own. */
+void save_convolutional_weights_binary(layer l, FILE *fp);
+void load_convolutional_weights_binary(layer l, FILE *fp);
+int ref_save_conv_binary(void *h, int i, const char *path)
+{
+    network *net = (network *)h;
+    FILE *fp = fopen(path, "wb");
+    if (!fp || i < 0 || i >= net->n || net->layers[i].type != CONVOLUTIONAL || !net->layers[i].binary_weights) { if (fp) fclose(fp); return -1; }
+    save_convolutional_weights_binary(net->layers[i], fp);
+    fclose(fp);
+    return 0;
+}
+int ref_load_conv_binary(void *h, int i, const char *path)
+{
+    network *net = (network *)h;
+    FILE *fp = fopen(path, "rb");
+    if (!fp || i < 0 || i >= net->n || net->layers[i].type != CONVOLUTIONAL) { if (fp) fclose(fp); return -1; }
+    load_convolutional_weights_binary(net->layers[i], fp);
+    fclose(fp);
+    return 0;
+}
+float *ref_layer_weights(void *h, int i) { return ((network *)h)->layers[i].weights; }
+
 void ref_set_threads(int n) { omp_set_num_threads(n); }
 int ref_max_threads(void) { return omp_get_max_threads(); }
 

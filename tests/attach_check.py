@@ -50,7 +50,7 @@ def main():
     stock = ref.predict_all(net, x)
     res = {"layers": len(kinds), "stock_vs_cpu": worst(stock)}
     res["attached"] = ref.attach(net, mode)
-    res["coverable"] = sum(k in ("convolutional", "maxpool", "upsample", "shortcut", "route") for k in kinds)
+    res["coverable"] = sum(k in ("convolutional", "maxpool", "upsample", "shortcut", "route", "yolo") for k in kinds)
     ours = ref.predict_all(net, x)
     res["attached_vs_cpu"] = worst(ours)
     res["attached_vs_stock_last"] = rel_to_max(ours[-1], stock[-1])

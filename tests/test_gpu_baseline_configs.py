@@ -99,7 +99,9 @@ def test_resnet50_224_batch_256(tmp_path):
     net.close()
 
 
-def test_xnor_darknet19_224_batch_128(tmp_path):
+@pytest.mark.parametrize("kernel", ["xnor_tc", "xnor_popc"])
+def test_xnor_darknet19_224_batch_128(kernel, tmp_path, monkeypatch):
+    monkeypatch.setenv("DNB_XNOR_TC", "1" if kernel == "xnor_tc" else "0")
     B = 128
     gen = lambda b: synth.darknet19_cfg(batch=b, size=224, xnor=True)   # noqa: E731
     cfg = gen(B)
@@ -124,7 +126,7 @@ def test_xnor_darknet19_224_batch_128(tmp_path):
         n, size, stride = int(opt["filters"]), int(opt["size"]), int(opt["stride"])
         plan = dn.ConvPlan(B, c, h, w, n, size, stride, size // 2, 1, True, opt["activation"], True)
         plan.set_params(p.weights, p.biases, p.scales, p.rolling_mean, p.rolling_variance)
-        assert plan.kernel.startswith("xnor")
+        assert plan.kernel == kernel
         xt, xd = dev_nchw(xin)
         acc = torch.full((B, n, plan.out_h, plan.out_w), -12345, dtype=torch.int32, device="cuda")
         plan.xnor_accumulate(xd, acc)
@@ -149,7 +151,7 @@ def test_xnor_darknet19_224_batch_128(tmp_path):
     synth.write_weights(wpath, params)
     net = dn.Network(cfg, wpath, dn.MODE_TF32, text=True)
     out = net.predict(x).copy()
-    assert [net.layer_kernel(i) for i in range(net.n)].count("xnor_popc") + [net.layer_kernel(i) for i in range(net.n)].count("xnor_tc") == 17
+    assert sum(net.layer_kernel(i).startswith("xnor_") for i in range(net.n)) == 17
     first = net.layer_output_images(0, src[1], 1)
     parity(first, want[src[1]][0], 1e-3, "xnor darknet19-224 b128 first layer (TF32 stem)")
     net.close()

@@ -121,3 +121,45 @@ def test_reads_what_the_reference_saves_and_matches_its_outputs(tmp_path):
     plain_cfg = cfg.replace("flipped=1\n", "")
     again = build(plain_cfg, back, dn.MODE_TF32).predict(x).copy()
     assert np.array_equal(again, out)
+
+
+def test_packed_binary_weights_load_the_same_xnor_network(tmp_path):
+    """dnb_load_weights_packed: every xnor convolution stored as mean |w| + sign bits (32 times smaller) gives, bit for
+    bit, the network that the ordinary file with those layers' weights replaced by +-mean gives."""
+    cfg = synth.darknet19_cfg(batch=2, size=64, xnor=True)
+    params = synth.seeded_params(cfg, 55)
+    x = synth.seeded_input(cfg, 55)
+    xnor_pos = {i for i, (k, o) in enumerate([s for s in synth.parse_cfg(cfg)[1:] if s[0] == "convolutional"]) if int(o.get("xnor", 0))}
+    assert len(xnor_pos) == 17
+    packed = str(tmp_path / "packed.weights")
+    synth.write_weights(packed, params, packed=xnor_pos)
+    expanded = []
+    for i, p in enumerate(params):
+        if i in xnor_pos:
+            flat = p.weights.reshape(p.weights.shape[0], -1)
+            rec = 4 + flat.shape[1] // 8
+            raw = synth.packed_filter_bytes(p.weights)
+            means = np.frombuffer(b"".join(raw[f * rec: f * rec + 4] for f in range(flat.shape[0])), np.float32)
+            w = np.where(flat > 0, means[:, None], -means[:, None]).astype(np.float32).reshape(p.weights.shape)
+            expanded.append(synth.ConvParams(w, p.biases, p.scales, p.rolling_mean, p.rolling_variance))
+        else:
+            expanded.append(p)
+    plain = str(tmp_path / "plain.weights")
+    synth.write_weights(plain, expanded)
+    assert os.path.getsize(packed) < os.path.getsize(plain) / 8
+    a = dn.Network(cfg, None, dn.MODE_TF32, text=True)
+    a.load_weights(packed, packed=True)
+    b = build(cfg, plain, dn.MODE_TF32)
+    out_a, out_b = a.predict(x).copy(), b.predict(x).copy()
+    assert np.array_equal(out_a, out_b)
+    for i in range(a.n):
+        assert np.array_equal(a.layer_output(i), b.layer_output(i)), f"layer {i}"
+    # a layer whose filters are not whole bytes of bits is refused, as the reference's size/8 would drop its tail
+    odd = synth.single_conv_cfg(1, 3, 8, 8, 8, 3, xnor=True)
+    op = synth.seeded_params(odd, 56)
+    bad = str(tmp_path / "odd.weights")
+    synth.write_weights(bad, op, packed={0})
+    n = dn.Network(odd, None, dn.MODE_TF32, text=True)
+    with pytest.raises(dn.DarknetB200Error) as e:
+        n.load_weights(bad, packed=True)
+    assert e.value.status == dn.EUNSUPPORTED

@@ -75,6 +75,51 @@ def test_upsample(shape, stride, layout):
     assert np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_producers_write_into_a_channel_range_of_a_wider_tensor(dtype):
+    """What the zero-copy [route] relies on: upsample and the tensor-core convolution write a tensor that is a channel
+    range of a wider channels-last tensor (own channel count, the wider tensor's pitch) without touching its
+    neighbours, and route skips an input that already is its range of the output."""
+    g = rng(40)
+    b, h, w = 2, 9, 11
+    x = g.standard_normal((b, 32, h, w), dtype=np.float32)
+    other = g.standard_normal((b, 64, 2 * h, 2 * w), dtype=np.float32)
+    if dtype == torch.bfloat16:
+        x, other = bf16_round(x), bf16_round(other)
+    es = 2 if dtype == torch.bfloat16 else 4
+    wide = torch.full((b, 2 * h, 2 * w, 96), 7.0, dtype=dtype, device="cuda")     # [upsampled 32 | other 64]
+    up_view = dn.Tensor(wide.data_ptr(), dn.NHWC, dn.BF16 if dtype == torch.bfloat16 else dn.F32, b, 32, 2 * h, 2 * w, 96)
+    ot_view = dn.Tensor(wide.data_ptr() + 32 * es, dn.NHWC, up_view.dtype, b, 64, 2 * h, 2 * w, 96)
+    xt, xd = dev_nhwc(x, dtype)
+    dn.upsample(xd, up_view, 2)
+    torch.cuda.synchronize()
+    assert np.array_equal(wide[..., :32].permute(0, 3, 1, 2).float().cpu().numpy(), orc.upsample_forward(x, 2))
+    assert bool((wide[..., 32:] == 7.0).all().item())                             # the neighbour's channels are untouched
+    # a convolution writes the other range
+    case = conv_case(41, b=b, c=16, h=2 * h, w=2 * w, n=64, size=3)
+    mode = dn.MODE_BF16 if dtype == torch.bfloat16 else dn.MODE_TF32
+    plan = dn.ConvPlan(b, 16, 2 * h, 2 * w, 64, 3, 1, 1, 1, True, "leaky", False, mode)
+    plan.set_params(case["w"], case["biases"], case["scales"], case["mean"], case["var"])
+    ct, cd = dev_nhwc(case["x"], dtype)
+    plan.forward(cd, ot_view)
+    torch.cuda.synchronize()
+    plan.check_status()
+    conv_out = wide[..., 32:].permute(0, 3, 1, 2).float().cpu().numpy()
+    parity(conv_out, oracle_conv(case), TOL_BF16 if dtype == torch.bfloat16 else TOL_TF32, "convolution into a channel range")
+    assert np.array_equal(wide[..., :32].permute(0, 3, 1, 2).float().cpu().numpy(), orc.upsample_forward(x, 2))
+    # route over the two ranges of its own output copies nothing and leaves the tensor as it is
+    before = wide.clone()
+    y_all = dn.Tensor(wide.data_ptr(), dn.NHWC, up_view.dtype, b, 96, 2 * h, 2 * w, 96)
+    dn.route([up_view, ot_view], y_all)
+    torch.cuda.synchronize()
+    assert torch.equal(wide, before)
+    # and the same route into a separate tensor copies both ranges
+    yt, yd = empty_nhwc(b, 96, 2 * h, 2 * w, dtype)
+    dn.route([up_view, ot_view], yd)
+    torch.cuda.synchronize()
+    assert torch.equal(yt, wide)
+
+
 @pytest.mark.parametrize("xs,adds,act", [
     ((2, 64, 19, 19), (2, 64, 19, 19), "linear"),     # YOLOv3 residual
     ((2, 256, 14, 14), (2, 64, 14, 14), "leaky"),     # ResNet: add has fewer channels
@@ -453,6 +498,9 @@ def test_conv_tc_all_ones_counts_taps():
 
 XNOR_CASES = {
     "3x3_c64": dict(b=2, c=64, h=10, w=10, n=32, size=3),
+    "3x3_c32_one_mma_per_tap": dict(b=3, c=32, h=20, w=20, n=64, size=3),
+    "3x3_c512_n1024_pairs": dict(b=16, c=512, h=7, w=7, n=1024, size=3),       # K = 4608; enough tiles for CTA pairs
+    "1x1_c1024_n512": dict(b=8, c=1024, h=7, w=7, n=512, size=1),
     "3x3_c40_ragged_word": dict(b=2, c=40, h=6, w=7, n=9, size=3),
     "1x1_c128": dict(b=2, c=128, h=7, w=7, n=64, size=1),
     "3x3_c1024": dict(b=1, c=1024, h=7, w=7, n=70, size=3),
@@ -462,7 +510,11 @@ XNOR_CASES = {
 
 @pytest.mark.parametrize("name", list(XNOR_CASES))
 @pytest.mark.parametrize("in_layout", ["nchw", "nhwc"])
-def test_conv_xnor(name, in_layout):
+@pytest.mark.parametrize("kernel", ["xnor_tc", "xnor_popc"])
+def test_conv_xnor(name, in_layout, kernel, monkeypatch):
+    """Both xnor kernels, the int8 tensor-core one (default) and the bit-packed popcount one (DNB_XNOR_TC=0): integer
+    sums bit for bit against the checker, layer outputs within 1e-5."""
+    monkeypatch.setenv("DNB_XNOR_TC", "1" if kernel == "xnor_tc" else "0")
     case = conv_case(400, **XNOR_CASES[name])
     x, w = case["x"], case["w"]
     x.reshape(-1)[::7] = 0.0   # exact zeros binarise to -1 (the CPU reference tests x > 0)
@@ -470,7 +522,7 @@ def test_conv_xnor(name, in_layout):
     n = w.shape[0]
     plan = dn.ConvPlan(b, c, h, wd, n, w.shape[2], case["stride"], case["pad"], 1, True, case["act"], True, dn.MODE_TF32)
     plan.set_params(w, case["biases"], case["scales"], case["mean"], case["var"])
-    assert plan.kernel == "xnor_popc"
+    assert plan.kernel == (kernel if case["stride"] <= 2 else "xnor_popc")
     xt, xd = dev_nchw(x) if in_layout == "nchw" else dev_nhwc(x)
     acc = torch.full((b, n, plan.out_h, plan.out_w), -12345, dtype=torch.int32, device="cuda")
     plan.xnor_accumulate(xd, acc)

@@ -240,5 +240,5 @@ def test_xnor_network_teacher_forced(tmp_path):
         parity(yt.cpu().numpy(), want[i], 1e-5, f"layer {i}")
     net = build(cfg, params, tmp_path, dn.MODE_TF32)
     net.predict(x)
-    assert [net.layer_kernel(i) for i in range(net.n)].count("xnor_popc") == 17
+    assert sum(net.layer_kernel(i).startswith("xnor_") for i in range(net.n)) == 17
     parity(net.layer_output(0), want[0], 1e-3)   # fp32 stem, stored rounded to TF32 for the next layer

@@ -135,3 +135,51 @@ def test_oracle_matches_reference_live(seed):
     R.L.ref_gemm_nn(7, 20, 45, A.ctypes.data, col_r.ctypes.data, Cr.ctypes.data)
     orc.lib().orc_gemm_nn(7, 20, 45, 1.0, A.ctypes.data, 45, col_m.ctypes.data, 20, Cm.ctypes.data, 20)
     assert np.array_equal(Cr, Cm)
+
+
+@pytest.mark.skipif(not orc.Reference.available() or not hasattr(orc.Reference().L, "ref_save_conv_binary"),
+                    reason="oracle/_ref (the compiled reference) is not built here")
+def test_packed_binary_layer_format_matches_the_reference(tmp_path):
+    """The reference's dormant packed-binary layer format (src/parser.c:926-956, 1134-1162), driven through its own
+    writer and reader: the writer of darknet_b200.synth produces the reference's bytes (sign bits exactly; the
+    per-filter mean to the last bits, the stock -Ofast build vectorises that sum), and the reference's reader
+    expands a file written here into the +-mean weights the loader of the CUDA library builds."""
+    import ctypes as C
+    import contextlib
+    cfg = synth.single_conv_cfg(2, 16, 6, 6, 12, 3, xnor=True)
+    params = synth.seeded_params(cfg, 77)
+    p = params[0]
+    d = str(tmp_path)
+    open(d + "/n.cfg", "w").write(cfg)
+    synth.write_weights(d + "/n.weights", params)
+    R = orc.Reference()
+    devnull = os.open(os.devnull, os.O_WRONLY)
+    saved = os.dup(2)
+    os.dup2(devnull, 2)
+    try:
+        net = R.load(d + "/n.cfg", d + "/n.weights")
+    finally:
+        os.dup2(saved, 2)
+        os.close(devnull)
+    assert R.L.ref_save_conv_binary(net, 0, (d + "/layer.bin").encode()) == 0
+    ref_bytes = open(d + "/layer.bin", "rb").read()
+    n, per = 12, 16 * 9
+    head = b"".join(np.ascontiguousarray(a, np.float32).tobytes() for a in (p.biases, p.scales, p.rolling_mean, p.rolling_variance))
+    mine = head + synth.packed_filter_bytes(p.weights)
+    assert len(ref_bytes) == len(mine) == len(head) + n * (4 + per // 8)
+    assert ref_bytes[:len(head)] == mine[:len(head)]
+    rec = 4 + per // 8
+    for f in range(n):
+        a = ref_bytes[len(head) + f * rec: len(head) + (f + 1) * rec]
+        b = mine[len(head) + f * rec: len(head) + (f + 1) * rec]
+        assert a[4:] == b[4:], f"filter {f}: sign bits"
+        ma, mb = np.frombuffer(a[:4], np.float32)[0], np.frombuffer(b[:4], np.float32)[0]
+        assert abs(ma - mb) <= 1e-6 * abs(mb), f"filter {f}: mean"   # a few units in the last place: the reference build reassociates the sum
+    # the reference's reader on the bytes written here
+    open(d + "/mine.bin", "wb").write(mine)
+    assert R.L.ref_load_conv_binary(net, 0, (d + "/mine.bin").encode()) == 0
+    got = np.ctypeslib.as_array(R.L.ref_layer_weights(net, 0), shape=(n, per)).copy()
+    flat = p.weights.reshape(n, per)
+    means = np.frombuffer(b"".join(mine[len(head) + f * rec: len(head) + f * rec + 4] for f in range(n)), np.float32)
+    want = np.where(flat > 0, means[:, None], -means[:, None]).astype(np.float32)
+    assert np.array_equal(got, want)
