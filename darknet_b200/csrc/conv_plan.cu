@@ -7,6 +7,8 @@
 
 #include <vector>
 
+#include <cuda_bf16.h>
+
 #include "common.h"
 #include "conv.h"
 
@@ -15,27 +17,6 @@ using namespace dnb;
 enum { K_TC_TF32 = 0, K_TC_BF16 = 1, K_DIRECT = 2, K_XNOR = 3 };
 static const char *const kKernelNames[] = {"tc_tf32", "tc_bf16", "direct_fp32", "xnor_popc"};
 static const char kXnorTcName[] = "xnor_tc";
-
-static float tf32_round_host(float x)
-{
-    // nearest TF32, ties away from zero (the device uses cvt.rna.tf32.f32)
-    uint32_t u;
-    memcpy(&u, &x, 4);
-    if ((u & 0x7f800000u) == 0x7f800000u) return x;
-    u += 0x1000u;
-    u &= ~0x1fffu;
-    memcpy(&x, &u, 4);
-    return x;
-}
-
-static uint16_t bf16_round_host(float x)
-{
-    uint32_t u;
-    memcpy(&u, &x, 4);
-    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);  // NaN
-    u += 0x7fffu + ((u >> 16) & 1);  // round to nearest even
-    return (uint16_t)(u >> 16);
-}
 
 extern "C" int dnb_conv_plan_create(const dnb_conv_desc *d, int mode, dnb_conv_plan **out)
 {
@@ -123,14 +104,120 @@ static int upload(T **dst, const std::vector<T> &src)
     return DNB_OK;
 }
 
+// ------------------------------------------------------------------ derived parameter tensors, built on the device
+// One host-to-device copy of the layer's weights as Darknet holds them ([n][c/groups][size][size]) and one kernel per
+// derived tensor: transposition into the kernels' layouts, rounding to the storage type, sign extraction.
+namespace {
+
+// tensor-core layout [tap][n_pad][c_pad], zero where padded; T = float (rounded to TF32-nearest) or bf16
+template <typename T>
+__global__ void repack_tc_kernel(const float *__restrict__ w, T *__restrict__ out, int n, int c, int taps, int n_pad, int c_pad)
+{
+    const size_t total = (size_t)taps * n_pad * c_pad;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int cc = (int)(i % c_pad);
+        const size_t r = i / c_pad;
+        const int f = (int)(r % n_pad), t = (int)(r / n_pad);
+        float v = 0.f;
+        if (f < n && cc < c) v = __ldg(w + ((size_t)f * c + cc) * taps + t);
+        if (sizeof(T) == 4) {
+            // nearest TF32, ties away from zero (what cvt.rna.tf32.f32 computes); infinities and NaNs pass through
+            uint32_t u = __float_as_uint(v);
+            if ((u & 0x7f800000u) != 0x7f800000u) u = (u + 0x1000u) & ~0x1fffu;
+            reinterpret_cast<float *>(out)[i] = __uint_as_float(u);
+        } else {
+            reinterpret_cast<__nv_bfloat16 *>(out)[i] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+// CUDA-core layout [groups][K][npg_pad], K = c/groups * size * size, filters innermost
+__global__ void repack_direct_kernel(const float *__restrict__ w, float *__restrict__ out, int groups, int npg, size_t K, int npg_pad)
+{
+    const size_t total = (size_t)groups * K * npg_pad;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int f = (int)(i % npg_pad);
+        const size_t r = i / npg_pad;
+        const size_t k = r % K;
+        const int g = (int)(r / K);
+        out[i] = f < npg ? __ldg(w + ((size_t)(g * npg + f)) * K + k) : 0.f;
+    }
+}
+
+// xnor: per filter the mean |w|, summed in a float in index order as binarize_weights does (src/convolutional_layer.c:28-41):
+// one thread per filter, so the order of the additions is the reference's
+__global__ void xnor_mean_kernel(const float *__restrict__ w, float *__restrict__ mean, int n, size_t K)
+{
+    const int f = blockIdx.x * blockDim.x + threadIdx.x;
+    if (f >= n) return;
+    float acc = 0.f;
+    for (size_t k = 0; k < K; ++k) acc += fabsf(__ldg(w + (size_t)f * K + k));
+    mean[f] = acc / (float)K;
+}
+
+// xnor: sign bits [n][taps][cwords] (bit c % 32 of word c / 32 set where w > 0), one thread per word
+__global__ void xnor_bits_kernel(const float *__restrict__ w, uint32_t *__restrict__ bits, int n, int c, int taps, int cwords)
+{
+    const size_t total = (size_t)n * taps * cwords;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int wd = (int)(i % cwords);
+        const size_t r = i / cwords;
+        const int t = (int)(r % taps), f = (int)(r / taps);
+        uint32_t word = 0;
+        for (int k = 0; k < 32; ++k) {
+            const int cc = wd * 32 + k;
+            if (cc < c && __ldg(w + ((size_t)f * c + cc) * taps + t) > 0.f) word |= 1u << k;
+        }
+        bits[i] = word;
+    }
+}
+
+// xnor on the tensor cores: signs as int8 in the tensor-core weight layout [tap][n_pad][c_pad], zero where padded
+__global__ void xnor_i8_kernel(const float *__restrict__ w, int8_t *__restrict__ out, int n, int c, int taps, int n_pad, int c_pad)
+{
+    const size_t total = (size_t)taps * n_pad * c_pad;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int cc = (int)(i % c_pad);
+        const size_t r = i / c_pad;
+        const int f = (int)(r % n_pad), t = (int)(r / n_pad);
+        int8_t v = 0;
+        if (f < n && cc < c) v = __ldg(w + ((size_t)f * c + cc) * taps + t) > 0.f ? 1 : -1;
+        out[i] = v;
+    }
+}
+
+// mean|w| folded into the batchnorm scale of the tensor-core xnor kernel
+__global__ void scale_times_mean_kernel(const float *__restrict__ scale, const float *__restrict__ mean, float *__restrict__ out, int n, int n_pad)
+{
+    const int f = blockIdx.x * blockDim.x + threadIdx.x;
+    if (f < n_pad) out[f] = f < n ? mean[f] * scale[f] : 0.f;
+}
+
+int grid_of(size_t total)
+{
+    const size_t blocks = (total + 255) / 256, cap = (size_t)sm_count() * 16;
+    return (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
+}
+
+template <typename T>
+int device_alloc(T **dst, size_t count)
+{
+    if (*dst) { cudaFree(*dst); *dst = nullptr; }
+    DNB_CUDA(cudaMalloc((void **)dst, count * sizeof(T)));
+    return DNB_OK;
+}
+
+}  // namespace
+
 extern "C" int dnb_conv_plan_set_params(dnb_conv_plan *p, const float *weights, const float *biases, const float *scales,
                                         const float *mean, const float *var)
 {
     if (!p || !weights || !biases) DNB_FAIL(DNB_EINVAL, "conv params: null argument");
     const dnb_conv_desc &d = p->d;
     if (d.batch_normalize && (!scales || !mean || !var)) DNB_FAIL(DNB_EINVAL, "conv params: batch_normalize layer needs scales, rolling_mean, rolling_variance");
+    DNB_TRY(check_current_device(p->device, "conv params"));
     const int cpg = d.c / d.groups, npg = d.n / d.groups, taps = d.size * d.size;
-    const size_t K = (size_t)cpg * taps;
+    const size_t K = (size_t)cpg * taps, nw = (size_t)d.n * K;
 
     // Folded inference batchnorm.  The CPU reference computes
     // ((x - mean) / (sqrt(var) + 1e-6f)) * scale + bias (src/blas.c:147-158,
@@ -149,61 +236,43 @@ extern "C" int dnb_conv_plan_set_params(dnb_conv_plan *p, const float *weights, 
     DNB_TRY(upload(&p->scale, s));
     DNB_TRY(upload(&p->shift, b));
 
+    // the weights as Darknet holds them, once; every derived tensor is built from this copy on the device
+    float *raw = nullptr;
+    DNB_CUDA(cudaMalloc((void **)&raw, nw * sizeof(float)));
+    struct Raw { float *p; ~Raw() { cudaFree(p); } } raw_guard{raw};
+    DNB_CUDA(cudaMemcpy(raw, weights, nw * sizeof(float), cudaMemcpyHostToDevice));
+
     if (p->kernel == K_TC_TF32) {
-        std::vector<float> w((size_t)taps * p->n_pad * p->c_pad, 0.f);
-        for (int n = 0; n < d.n; ++n)
-            for (int c = 0; c < d.c; ++c)
-                for (int t = 0; t < taps; ++t)
-                    w[((size_t)t * p->n_pad + n) * p->c_pad + c] = tf32_round_host(weights[((size_t)n * d.c + c) * taps + t]);
+        const size_t total = (size_t)taps * p->n_pad * p->c_pad;
         float *dev = (float *)p->w_tc;
-        DNB_TRY(upload(&dev, w));
+        DNB_TRY(device_alloc(&dev, total));
         p->w_tc = dev;
+        repack_tc_kernel<float><<<grid_of(total), 256>>>(raw, dev, d.n, d.c, taps, p->n_pad, p->c_pad);
     } else if (p->kernel == K_TC_BF16) {
-        std::vector<uint16_t> w((size_t)taps * p->n_pad * p->c_pad, 0);
-        for (int n = 0; n < d.n; ++n)
-            for (int c = 0; c < d.c; ++c)
-                for (int t = 0; t < taps; ++t)
-                    w[((size_t)t * p->n_pad + n) * p->c_pad + c] = bf16_round_host(weights[((size_t)n * d.c + c) * taps + t]);
-        uint16_t *dev = (uint16_t *)p->w_tc;
-        DNB_TRY(upload(&dev, w));
+        const size_t total = (size_t)taps * p->n_pad * p->c_pad;
+        __nv_bfloat16 *dev = (__nv_bfloat16 *)p->w_tc;
+        DNB_TRY(device_alloc(&dev, total));
         p->w_tc = dev;
+        repack_tc_kernel<__nv_bfloat16><<<grid_of(total), 256>>>(raw, dev, d.n, d.c, taps, p->n_pad, p->c_pad);
     } else if (p->kernel == K_DIRECT) {
-        std::vector<float> w((size_t)d.groups * K * p->npg_pad, 0.f);
-        for (int g = 0; g < d.groups; ++g)
-            for (int f = 0; f < npg; ++f)
-                for (size_t k = 0; k < K; ++k)
-                    w[((size_t)g * K + k) * p->npg_pad + f] = weights[((size_t)(g * npg + f)) * K + k];
-        DNB_TRY(upload(&p->w_direct, w));
+        const size_t total = (size_t)d.groups * K * p->npg_pad;
+        DNB_TRY(device_alloc(&p->w_direct, total));
+        repack_direct_kernel<<<grid_of(total), 256>>>(raw, p->w_direct, d.groups, npg, K, p->npg_pad);
     } else {
-        // sign bits (w > 0) and the per-filter mean |w|, accumulated in a float in
-        // index order as binarize_weights does (src/convolutional_layer.c:28-41)
-        std::vector<uint32_t> bits((size_t)d.n * taps * p->cwords, 0u);
-        std::vector<float> m(d.n);
-        for (int n = 0; n < d.n; ++n) {
-            float acc = 0.f;
-            for (size_t k = 0; k < K; ++k) acc += fabsf(weights[(size_t)n * K + k]);
-            m[n] = acc / (float)K;
-            for (int c = 0; c < d.c; ++c)
-                for (int t = 0; t < taps; ++t)
-                    if (weights[((size_t)n * d.c + c) * taps + t] > 0.f)
-                        bits[((size_t)n * taps + t) * p->cwords + c / 32] |= 1u << (c % 32);
-        }
-        DNB_TRY(upload(&p->w_bits, bits));
-        DNB_TRY(upload(&p->w_mean, m));
+        DNB_TRY(device_alloc(&p->w_bits, (size_t)d.n * taps * p->cwords));
+        DNB_TRY(device_alloc(&p->w_mean, (size_t)d.n));
+        xnor_bits_kernel<<<grid_of((size_t)d.n * taps * p->cwords), 256>>>(raw, p->w_bits, d.n, d.c, taps, p->cwords);
+        xnor_mean_kernel<<<(d.n + 127) / 128, 128>>>(raw, p->w_mean, d.n, K);
         if (p->xnor_tc) {
-            // the same signs as int8 in the tensor-core kernel's weight layout [tap][n_pad][c_pad], zero where padded, and
-            // mean|w| folded into the batchnorm scale: out = act(sum * (mean * s) + shift)
-            std::vector<int8_t> w8((size_t)taps * p->n_pad * p->c_pad_i8, 0);
-            for (int n = 0; n < d.n; ++n)
-                for (int c = 0; c < d.c; ++c)
-                    for (int t = 0; t < taps; ++t)
-                        w8[((size_t)t * p->n_pad + n) * p->c_pad_i8 + c] = weights[((size_t)n * d.c + c) * taps + t] > 0.f ? 1 : -1;
-            std::vector<float> s8(p->n_pad, 0.f);
-            for (int n = 0; n < d.n; ++n) s8[n] = m[n] * s[n];
-            DNB_TRY(upload(&p->w_i8, w8));
-            DNB_TRY(upload(&p->scale_i8, s8));
+            const size_t total = (size_t)taps * p->n_pad * p->c_pad_i8;
+            DNB_TRY(device_alloc(&p->w_i8, total));
+            DNB_TRY(device_alloc(&p->scale_i8, (size_t)p->n_pad));
+            xnor_i8_kernel<<<grid_of(total), 256>>>(raw, p->w_i8, d.n, d.c, taps, p->n_pad, p->c_pad_i8);
+            scale_times_mean_kernel<<<(p->n_pad + 127) / 128, 128>>>(p->scale, p->w_mean, p->scale_i8, d.n, p->n_pad);
         }
     }
+    DNB_LAUNCH_CHECK("weight repack");
+    DNB_CUDA(cudaDeviceSynchronize());   // the staging copy is released on return
     p->params_set = true;
     // The launch block caches a tensor map over the weights just replaced: have the next forward rebuild it.
     p->tc_x_ptr = p->tc_y_ptr = p->tc_res_ptr = nullptr;
@@ -303,8 +372,13 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
         const char *e = getenv("DNB_TC_PAIR");
         const int knob = e ? atoi(e) : 1;
         // (the pair kernel is built for 128-byte staged rows only: it needs a channels-last output at least that wide)
-        const bool legal = !a.halo && a.row_bytes == 128 && g.n % 256 == 0 && (ptiles + 1) / 2 * (g.n / 256) >= sm_count() / 2 &&
-                           y_nhwc && y_cpitch * (bf16 ? 2 : 4) >= 128;
+        // Enough pair tiles to occupy every pair of SMs; or, for long K loops (small batches of the 19x19 and 38x38
+        // layers), at least half of them: a pair's six-deep ring of 32 KB slots keeps its tensor pipes fed where two
+        // single CTAs per SM with two or three slots each starve on load latency, which outweighs the idle SMs.
+        const int pair_tiles = (ptiles + 1) / 2 * (g.n / 256), clusters = sm_count() / 2;
+        const int k_iters_p = g.size * g.size * a.c_blocks;
+        const bool enough = pair_tiles >= clusters || (k_iters_p >= 64 && 2 * pair_tiles >= clusters);
+        const bool legal = !a.halo && a.row_bytes == 128 && g.n % 256 == 0 && enough && y_nhwc && y_cpitch * (bf16 ? 2 : 4) >= 128;
         if (legal && (knob == 2 || (knob == 1 && g.size >= 3))) {
             a.pair = 1;
             a.bn = 256;

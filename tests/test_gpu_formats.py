@@ -68,22 +68,29 @@ def test_weight_file_variants_load_the_same_network(tmp_path):
     x = synth.seeded_input(cfg, 53)
     plain = str(tmp_path / "plain.weights")
     synth.write_weights(plain, params, seen=7)
-    base = build(cfg, plain, dn.MODE_TF32).predict(x).copy()
+
+    def run(c, w):
+        net = build(c, w, dn.MODE_TF32)       # predict() returns memory the network owns: copy before the network goes
+        out = net.predict(x).copy()
+        net.close()
+        return out
+
+    base = run(cfg, plain)
     # version 0.1: a 32-bit `seen`
     old = str(tmp_path / "old.weights")
     synth.write_weights(old, params, seen=7, version=(0, 1, 0))
     assert os.path.getsize(old) == os.path.getsize(plain) - 4
-    assert np.array_equal(build(cfg, old, dn.MODE_TF32).predict(x), base)
+    assert np.array_equal(run(cfg, old), base)
     # a version above 1000: connected matrices transposed on disk (and a 32-bit seen)
     tr = str(tmp_path / "transposed.weights")
     synth.write_weights(tr, params, seen=7, version=(0, 1001, 0))
     assert open(tr, "rb").read() != open(old, "rb").read()
-    assert np.array_equal(build(cfg, tr, dn.MODE_TF32).predict(x), base)
+    assert np.array_equal(run(cfg, tr), base)
     # flipped=1 on the second convolution: its matrix is transposed on disk
     fl = str(tmp_path / "flipped.weights")
     synth.write_weights(fl, params, seen=7, flipped={1})
     assert open(fl, "rb").read() != open(plain, "rb").read()
-    assert np.array_equal(build(flipped_cfg, fl, dn.MODE_TF32).predict(x), base)
+    assert np.array_equal(run(flipped_cfg, fl), base)
     # the checker agrees with all of them
     parity(base.reshape(-1), orc.forward_network(cfg, params, x)[-1].reshape(-1), 1e-2, "against the checker")
 
@@ -119,7 +126,8 @@ def test_reads_what_the_reference_saves_and_matches_its_outputs(tmp_path):
     # save_weights writes version 0.2 with untransposed connected matrices; the flipped convolution is written as it
     # sits in memory (already transposed back by the loader), so the file is read with flipped=0
     plain_cfg = cfg.replace("flipped=1\n", "")
-    again = build(plain_cfg, back, dn.MODE_TF32).predict(x).copy()
+    net2 = build(plain_cfg, back, dn.MODE_TF32)
+    again = net2.predict(x).copy()
     assert np.array_equal(again, out)
 
 

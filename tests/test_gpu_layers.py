@@ -82,19 +82,19 @@ def test_producers_write_into_a_channel_range_of_a_wider_tensor(dtype):
     neighbours, and route skips an input that already is its range of the output."""
     g = rng(40)
     b, h, w = 2, 9, 11
-    x = g.standard_normal((b, 32, h, w), dtype=np.float32)
+    x = g.standard_normal((b, 64, h, w), dtype=np.float32)
     other = g.standard_normal((b, 64, 2 * h, 2 * w), dtype=np.float32)
     if dtype == torch.bfloat16:
         x, other = bf16_round(x), bf16_round(other)
     es = 2 if dtype == torch.bfloat16 else 4
-    wide = torch.full((b, 2 * h, 2 * w, 96), 7.0, dtype=dtype, device="cuda")     # [upsampled 32 | other 64]
-    up_view = dn.Tensor(wide.data_ptr(), dn.NHWC, dn.BF16 if dtype == torch.bfloat16 else dn.F32, b, 32, 2 * h, 2 * w, 96)
-    ot_view = dn.Tensor(wide.data_ptr() + 32 * es, dn.NHWC, up_view.dtype, b, 64, 2 * h, 2 * w, 96)
+    wide = torch.full((b, 2 * h, 2 * w, 128), 7.0, dtype=dtype, device="cuda")    # [upsampled 64 | other 64]; ranges start on 128-byte boundaries
+    up_view = dn.Tensor(wide.data_ptr(), dn.NHWC, dn.BF16 if dtype == torch.bfloat16 else dn.F32, b, 64, 2 * h, 2 * w, 128)
+    ot_view = dn.Tensor(wide.data_ptr() + 64 * es, dn.NHWC, up_view.dtype, b, 64, 2 * h, 2 * w, 128)
     xt, xd = dev_nhwc(x, dtype)
     dn.upsample(xd, up_view, 2)
     torch.cuda.synchronize()
-    assert np.array_equal(wide[..., :32].permute(0, 3, 1, 2).float().cpu().numpy(), orc.upsample_forward(x, 2))
-    assert bool((wide[..., 32:] == 7.0).all().item())                             # the neighbour's channels are untouched
+    assert np.array_equal(wide[..., :64].permute(0, 3, 1, 2).float().cpu().numpy(), orc.upsample_forward(x, 2))
+    assert bool((wide[..., 64:] == 7.0).all().item())                             # the neighbour's channels are untouched
     # a convolution writes the other range
     case = conv_case(41, b=b, c=16, h=2 * h, w=2 * w, n=64, size=3)
     mode = dn.MODE_BF16 if dtype == torch.bfloat16 else dn.MODE_TF32
@@ -104,17 +104,17 @@ def test_producers_write_into_a_channel_range_of_a_wider_tensor(dtype):
     plan.forward(cd, ot_view)
     torch.cuda.synchronize()
     plan.check_status()
-    conv_out = wide[..., 32:].permute(0, 3, 1, 2).float().cpu().numpy()
+    conv_out = wide[..., 64:].permute(0, 3, 1, 2).float().cpu().numpy()
     parity(conv_out, oracle_conv(case), TOL_BF16 if dtype == torch.bfloat16 else TOL_TF32, "convolution into a channel range")
-    assert np.array_equal(wide[..., :32].permute(0, 3, 1, 2).float().cpu().numpy(), orc.upsample_forward(x, 2))
+    assert np.array_equal(wide[..., :64].permute(0, 3, 1, 2).float().cpu().numpy(), orc.upsample_forward(x, 2))
     # route over the two ranges of its own output copies nothing and leaves the tensor as it is
     before = wide.clone()
-    y_all = dn.Tensor(wide.data_ptr(), dn.NHWC, up_view.dtype, b, 96, 2 * h, 2 * w, 96)
+    y_all = dn.Tensor(wide.data_ptr(), dn.NHWC, up_view.dtype, b, 128, 2 * h, 2 * w, 128)
     dn.route([up_view, ot_view], y_all)
     torch.cuda.synchronize()
     assert torch.equal(wide, before)
     # and the same route into a separate tensor copies both ranges
-    yt, yd = empty_nhwc(b, 96, 2 * h, 2 * w, dtype)
+    yt, yd = empty_nhwc(b, 128, 2 * h, 2 * w, dtype)
     dn.route([up_view, ot_view], yd)
     torch.cuda.synchronize()
     assert torch.equal(yt, wide)

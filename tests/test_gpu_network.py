@@ -90,7 +90,7 @@ def test_network_device_forward_equals_predict(tmp_path):
     assert np.array_equal(a, b)
     ms = net.profile(xd)
     assert ms.shape == (net.n,) and (ms >= 0).all()
-    assert net.launches >= net.n and net.flops > 0
+    assert 0 < net.launches <= net.n + 1 and net.flops > 0   # a route whose inputs sit in place launches nothing
 
 
 @pytest.mark.parametrize("name", ["tiny64", "resnet50_32"])
