@@ -149,6 +149,10 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     __syncthreads();
     if (PAIR) cluster_sync_all();   // the other CTA's barriers are initialised before anything is signalled across the pair
     tc_fence_after();
+    // Everything above touched only this CTA's shared memory and TMEM: it may run while the previous layer's kernel is
+    // still draining.  From here on the previous layer's output is read and buffers it may still read are written.
+    grid_dependency_wait();
+    launch_dependents();   // this grid is persistent and fully resident: the next layer's CTAs take SMs only as ours leave
     const uint32_t tmem_base = sh->tmem_base;
 
     // Kernel parameters live in the constant bank, and every asm statement below is a compiler memory
@@ -621,68 +625,75 @@ static int max_pair_clusters(K kernel, size_t smem)
     return n;
 }
 
+// DNB_PDL=0 launches every kernel plainly (no overlap of a kernel's set-up with the tail of the kernel before it).
+static bool pdl_enabled()
+{
+    static int v = -1;
+    if (v < 0) { const char *e = getenv("DNB_PDL"); v = e ? (atoi(e) != 0) : 1; }
+    return v != 0;
+}
+
+// One launch.  Single CTAs: one CTA per SM slot (or per tile, if fewer).  Pair mode: clusters of two CTAs, as many as are
+// resident at once (or pair tiles, if fewer).  Either way the grid is one wave of persistent CTAs.  Every launch carries
+// the programmatic-stream-serialization attribute: the kernel's set-up overlaps the tail of the kernel before it in the
+// stream, and the kernel itself waits for that kernel before it touches global memory.
+template <typename K>
+static int launch_one(K kern, const TcArgs &a, size_t smem, cudaStream_t s)
+{
+    // the opt-in for large dynamic shared memory is per kernel symbol and cheap, so it is set on every launch
+    DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, conv_tc_max_smem()));
+    unsigned grid;
+    if (a.pair) {
+        const int clusters_max = max_pair_clusters(kern, smem);
+        grid = 2u * (unsigned)(a.total_tiles < clusters_max ? a.total_tiles : clusters_max);
+    } else {
+        const int slots = sm_count() * a.ctas_per_sm;
+        grid = (unsigned)(a.total_tiles < slots ? a.total_tiles : slots);
+    }
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    attrs[1].id = cudaLaunchAttributeClusterDimension;
+    attrs[1].val.clusterDim.x = 2; attrs[1].val.clusterDim.y = 1; attrs[1].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cfg.attrs = attrs;
+    cfg.numAttrs = a.pair ? 2 : 1;
+    DNB_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
+    return DNB_OK;
+}
+
 int launch_conv_tc(const TcArgs &a, cudaStream_t s)
 {
     const size_t smem = conv_tc_smem_bytes(a);
     const bool obf = a.is_bf16 == 1, i8 = a.is_bf16 == 2;   // int8 operands write f32 output
     const int cpc = a.store_row_bytes / (obf ? 2 : 4);
     if (cpc != 16 && cpc != 32 && cpc != 64) DNB_FAIL(DNB_EINVAL, "conv_tc: staged row of %d bytes", a.store_row_bytes);
-    const int slots = sm_count() * a.ctas_per_sm;
-    const int grid = a.total_tiles < slots ? a.total_tiles : slots;
-    const int max_smem = conv_tc_max_smem();
-    // one instantiation per (activation, columns per staged chunk, output type); the opt-in for large
-    // dynamic shared memory is per kernel symbol and cheap, so it is set on every launch
-#define DNB_TC_LAUNCH(ACT, CPC, OBF, ACT2)                                                                                       \
-    do {                                                                                                                         \
-        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<ACT, CPC, OBF, ACT2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)); \
-        conv_tc_kernel<ACT, CPC, OBF, ACT2, false><<<grid, TC_THREADS, smem, s>>>(a);                                           \
+    if (a.pair && !((!obf && cpc == 32) || (obf && cpc == 64))) DNB_FAIL(DNB_EINVAL, "conv_tc: pair mode needs 128-byte staged rows");
+    // one instantiation per (activation, columns per staged chunk, output type, fused shortcut, pair mode, operand kind)
+#define DNB_TC_GO(ACT, CPC, OBF, ACT2, I8)                                                          \
+    do {                                                                                            \
+        if (a.pair) DNB_TRY(launch_one(conv_tc_kernel<ACT, CPC, OBF, ACT2, true, I8>, a, smem, s)); \
+        else DNB_TRY(launch_one(conv_tc_kernel<ACT, CPC, OBF, ACT2, false, I8>, a, smem, s));       \
     } while (0)
-    // pair mode: clusters of two CTAs, one CTA per SM, as many clusters as are resident at once (or pair tiles, if fewer)
-#define DNB_TC_LAUNCH_PAIR(ACT, CPC, OBF, ACT2)                                                                                  \
-    do {                                                                                                                         \
-        auto kern = conv_tc_kernel<ACT, CPC, OBF, ACT2, true>;                                                                   \
-        DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));                            \
-        const int clusters_max = max_pair_clusters(kern, smem);                                                                  \
-        const int clusters = a.total_tiles < clusters_max ? a.total_tiles : clusters_max;                                        \
-        cudaLaunchConfig_t cfg = {};                                                                                             \
-        cfg.gridDim = dim3(2 * (unsigned)clusters);                                                                              \
-        cfg.blockDim = dim3(TC_THREADS);                                                                                         \
-        cfg.dynamicSmemBytes = smem;                                                                                             \
-        cfg.stream = s;                                                                                                          \
-        cudaLaunchAttribute attr[1];                                                                                             \
-        attr[0].id = cudaLaunchAttributeClusterDimension;                                                                        \
-        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;                                \
-        cfg.attrs = attr; cfg.numAttrs = 1;                                                                                      \
-        DNB_CUDA(cudaLaunchKernelEx(&cfg, kern, a));                                                                             \
+    // pair-mode kernels exist for 128-byte staged rows only, so the narrower variants are instantiated without it
+#define DNB_TC_GO_SINGLE(ACT, CPC, OBF, ACT2, I8) DNB_TRY(launch_one(conv_tc_kernel<ACT, CPC, OBF, ACT2, false, I8>, a, smem, s))
+#define DNB_TC_LAUNCH_ACT(ACT, ACT2)                                            \
+    do {                                                                        \
+        if (!obf && cpc == 32) DNB_TC_GO(ACT, 32, false, ACT2, false);          \
+        else if (!obf && cpc == 16) DNB_TC_GO_SINGLE(ACT, 16, false, ACT2, false); \
+        else if (obf && cpc == 64) DNB_TC_GO(ACT, 64, true, ACT2, false);       \
+        else if (obf && cpc == 32) DNB_TC_GO_SINGLE(ACT, 32, true, ACT2, false); \
+        else if (obf && cpc == 16) DNB_TC_GO_SINGLE(ACT, 16, true, ACT2, false); \
+        else DNB_FAIL(DNB_EINVAL, "conv_tc: no kernel for %d columns per chunk", cpc); \
     } while (0)
-#define DNB_TC_LAUNCH_I8(ACT, CPC)                                                                                               \
-    do {                                                                                                                         \
-        DNB_CUDA(cudaFuncSetAttribute(conv_tc_kernel<ACT, CPC, false, ACT2_NONE, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)); \
-        conv_tc_kernel<ACT, CPC, false, ACT2_NONE, false, true><<<grid, TC_THREADS, smem, s>>>(a);                              \
-    } while (0)
-#define DNB_TC_LAUNCH_I8_PAIR(ACT)                                                                                               \
-    do {                                                                                                                         \
-        auto kern = conv_tc_kernel<ACT, 32, false, ACT2_NONE, true, true>;                                                       \
-        DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));                            \
-        const int clusters_max = max_pair_clusters(kern, smem);                                                                  \
-        const int clusters = a.total_tiles < clusters_max ? a.total_tiles : clusters_max;                                        \
-        cudaLaunchConfig_t cfg = {};                                                                                             \
-        cfg.gridDim = dim3(2 * (unsigned)clusters);                                                                              \
-        cfg.blockDim = dim3(TC_THREADS);                                                                                         \
-        cfg.dynamicSmemBytes = smem;                                                                                             \
-        cfg.stream = s;                                                                                                          \
-        cudaLaunchAttribute attr[1];                                                                                             \
-        attr[0].id = cudaLaunchAttributeClusterDimension;                                                                        \
-        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;                                \
-        cfg.attrs = attr; cfg.numAttrs = 1;                                                                                      \
-        DNB_CUDA(cudaLaunchKernelEx(&cfg, kern, a));                                                                             \
-    } while (0)
-#define DNB_TC_LAUNCH_I8_ACT(ACT)                                           \
-    do {                                                                    \
-        if (a.pair && cpc == 32) DNB_TC_LAUNCH_I8_PAIR(ACT);                \
-        else if (a.pair) DNB_FAIL(DNB_EINVAL, "conv_tc: pair mode needs 128-byte staged rows"); \
-        else if (cpc == 32) DNB_TC_LAUNCH_I8(ACT, 32);                      \
-        else if (cpc == 16) DNB_TC_LAUNCH_I8(ACT, 16);                      \
+#define DNB_TC_LAUNCH_I8_ACT(ACT)                                               \
+    do {                                                                        \
+        if (cpc == 32) DNB_TC_GO(ACT, 32, false, ACT2_NONE, true);              \
+        else if (cpc == 16) DNB_TC_GO_SINGLE(ACT, 16, false, ACT2_NONE, true);  \
         else DNB_FAIL(DNB_EINVAL, "conv_tc: no int8 kernel for %d columns per chunk", cpc); \
     } while (0)
     if (i8) {
@@ -692,22 +703,7 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
         case DNB_LEAKY: DNB_TC_LAUNCH_I8_ACT(DNB_LEAKY); break;
         default: DNB_TC_LAUNCH_I8_ACT(ACT_GENERIC); break;
         }
-        DNB_LAUNCH_CHECK("conv_tc (int8)");
-        return DNB_OK;
-    }
-#define DNB_TC_LAUNCH_ACT(ACT, ACT2)                                        \
-    do {                                                                    \
-        if (a.pair && !obf && cpc == 32) DNB_TC_LAUNCH_PAIR(ACT, 32, false, ACT2); \
-        else if (a.pair && obf && cpc == 64) DNB_TC_LAUNCH_PAIR(ACT, 64, true, ACT2); \
-        else if (a.pair) DNB_FAIL(DNB_EINVAL, "conv_tc: pair mode needs 128-byte staged rows"); \
-        else if (!obf && cpc == 32) DNB_TC_LAUNCH(ACT, 32, false, ACT2);    \
-        else if (!obf && cpc == 16) DNB_TC_LAUNCH(ACT, 16, false, ACT2);    \
-        else if (obf && cpc == 64) DNB_TC_LAUNCH(ACT, 64, true, ACT2);      \
-        else if (obf && cpc == 32) DNB_TC_LAUNCH(ACT, 32, true, ACT2);      \
-        else if (obf && cpc == 16) DNB_TC_LAUNCH(ACT, 16, true, ACT2);      \
-        else DNB_FAIL(DNB_EINVAL, "conv_tc: no kernel for %d columns per chunk", cpc); \
-    } while (0)
-    if (!a.ep.residual) {
+    } else if (!a.ep.residual) {
         switch (a.ep.activation) {
         case DNB_LINEAR: DNB_TC_LAUNCH_ACT(DNB_LINEAR, ACT2_NONE); break;
         case DNB_LEAKY: DNB_TC_LAUNCH_ACT(DNB_LEAKY, ACT2_NONE); break;
@@ -721,12 +717,10 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
         else if (a.ep.activation == DNB_LINEAR && a.ep.activation2 == DNB_LEAKY) DNB_TC_LAUNCH_ACT(DNB_LINEAR, DNB_LEAKY);
         else DNB_TC_LAUNCH_ACT(ACT_GENERIC, ACT_GENERIC);
     }
-#undef DNB_TC_LAUNCH_ACT
-#undef DNB_TC_LAUNCH_PAIR
-#undef DNB_TC_LAUNCH
 #undef DNB_TC_LAUNCH_I8_ACT
-#undef DNB_TC_LAUNCH_I8_PAIR
-#undef DNB_TC_LAUNCH_I8
+#undef DNB_TC_LAUNCH_ACT
+#undef DNB_TC_GO_SINGLE
+#undef DNB_TC_GO
     DNB_LAUNCH_CHECK("conv_tc");
     return DNB_OK;
 }

@@ -159,6 +159,15 @@ __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before it in the
+// stream is still draining: its CTAs take SMs as they free up and run their set-up (barriers, TMEM, tensor-map
+// fetch); grid_dependency_wait() then holds them until the previous kernel has finished and its writes are visible.
+// Nothing a previous kernel wrote may be read, and nothing it may still read may be written, before that wait.
+// launch_dependents() lets the kernel after this one be scheduled the same way.  Both are no-ops in a plain launch.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ------------------------------------------------------------------ CTA pairs (cta_group::2)
 // Two CTAs of a cluster of two run one MMA of 256 rows: each holds 128 rows of A and half of B's columns in its own
 // shared memory and its 128 rows of the accumulator in its own TMEM; the even CTA (cluster rank 0) issues the MMAs.
