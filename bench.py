@@ -71,6 +71,10 @@ def workload_cfg(name: str, batch: int, size: int) -> tuple[str, str, str]:
         return synth.single_conv_cfg(batch, 256, 52, 52, 512, 3), "conv3x3_256_512_52_images_per_s", "isolated 3x3 conv 256->512 at 52x52"
     if name == "conv1x1":
         return synth.single_conv_cfg(batch, 512, 52, 52, 256, 1), "conv1x1_512_256_52_images_per_s", "isolated 1x1 conv 512->256 at 52x52"
+    if name.startswith("block:"):   # block:C,HW: one residual block of darknet-53 (3x3 C->C, 1x1 C->C/2, 3x3 C/2->C, shortcut), for profiling
+        c, hw = [int(t) for t in name[6:].split(",")]
+        cfg = (synth._net(batch, hw, hw, c) + synth._conv(c, 3) + synth._conv(c // 2, 1) + synth._conv(c, 3) + synth._shortcut(-3))
+        return cfg, f"block_{c}_{hw}_images_per_s", f"darknet-53 residual block, {c} channels at {hw}x{hw}"
     if name.startswith("conv:"):   # conv:C,HW,N,SIZE[,STRIDE]: any single layer, for profiling (batchnorm + leaky)
         v = [int(t) for t in name[5:].split(",")]
         c, hw, n, k = v[:4]
@@ -95,8 +99,8 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=64, help="images per GPU per step")
     ap.add_argument("--size", type=int, default=0, help="input width = height (default: 608 yolov3, 416 tiny, 224 classifiers)")
     ap.add_argument("--workload", default="yolov3",
-                    help="yolov3 (the headline), yolov3-tiny, resnet50, darknet19-xnor, conv3x3, conv1x1, memlayers, or conv:C,HW,N,SIZE[,STRIDE] "
-                         "for one convolutional layer of that shape")
+                    help="yolov3 (the headline), yolov3-tiny, resnet50, darknet19-xnor, conv3x3, conv1x1, memlayers, conv:C,HW,N,SIZE[,STRIDE] "
+                         "for one convolutional layer of that shape, or block:C,HW for one darknet-53 residual block")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: --batch images on every GPU; strong: --batch images split over the GPUs")
     ap.add_argument("--cpu-sample", type=int, default=4, help="images of the CPU-baseline sample (0 = skip)")
@@ -410,10 +414,29 @@ def roofline_of(net, cfg: str, per_gpu: int, mean_ms, mode: str, workload: str, 
             words += float(per_gpu) * sh.n * sh.size * sh.size * ((sh.c + 31) // 32) * h * w
         x_ms = float(mean_ms[xn].sum())
         rate = words / (x_ms / 1000.0) / 1e12
-        roofline = {"kernel": "conv_xnor_kernel", "bound": "popc issue", "achieved": rate, "unit": "T word-popcounts/s", "peak": None, "frac": None,
-                    "binary_tops": rate * 64.0, "traffic": None, "launches_per_step": int(xn.sum()), "ms_per_step": x_ms,
-                    "share_of_step": x_ms / float(mean_ms.sum()),
-                    "what": "bit-packed xnor + popcount GEMM on the integer pipe; binary_tops counts 2 x 32 binary operations per word"}
+        if any(kn == "xnor_tc" for kn in kernels):
+            # int8 sign tensors through the tensor cores (kind::i8): the integer sums cost a few per cent of the int8 tensor
+            # rate; what bounds the layer is the fp32 activations around it.  Algorithmic bytes per layer: fp32 input read
+            # once by the sign pass, int8 signs written and read once, fp32 output written, the int8 weights once.
+            bytes_ = 0.0
+            for i in np.nonzero(xn)[0]:
+                c, h, w = net.layer_shape(int(i))
+                sh = shapes[int(i)]
+                stride = int(sections[int(i)][1].get("stride", 1))
+                in_e = float(per_gpu) * sh.c * (h * stride) * (w * stride)
+                bytes_ += 4.0 * in_e + 2.0 * in_e + 4.0 * per_gpu * sh.n * h * w + sh.n * sh.c * sh.size * sh.size
+            gbs = bytes_ / (x_ms / 1000.0) / 1e9
+            ops = 2.0 * 32.0 * words   # multiply-adds of +-1 values, two operations each
+            roofline = {"kernel": "conv_tc_kernel (int8 kind) + pack_sign_i8_kernel", "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": gbs / peaks["hbm_gbs"], "traffic": None, "launches_per_step": 2 * int(xn.sum()), "ms_per_step": x_ms,
+                        "share_of_step": x_ms / float(mean_ms.sum()), "integer_tops": ops / (x_ms / 1000.0) / 1e12,
+                        "peak_source": f"{peaks['source']}: STREAM-style copy",
+                        "what": "xnor layers as int8 sign tensors on tcgen05 (exact int32 sums); bytes = fp32 input + int8 signs written and read + fp32 output + int8 weights"}
+        else:
+            roofline = {"kernel": "conv_xnor_kernel", "bound": "popc issue", "achieved": rate, "unit": "T word-popcounts/s", "peak": None, "frac": None,
+                        "binary_tops": rate * 64.0, "traffic": None, "launches_per_step": int(xn.sum()), "ms_per_step": x_ms,
+                        "share_of_step": x_ms / float(mean_ms.sum()),
+                        "what": "bit-packed xnor + popcount GEMM on the integer pipe; binary_tops counts 2 x 32 binary operations per word"}
     return roofline, flops, kinds, kernels
 
 
@@ -481,7 +504,7 @@ def run_b200(args):
     if world > 1:
         dist.barrier()
     net = dn.Network(cfg, os.path.join(wdir, "net.weights"), mode, text=True)
-    x_host = torch.from_numpy(synth.seeded_input(cfg, rank, "normal" if args.workload.startswith("conv") else "uniform")).pin_memory()
+    x_host = torch.from_numpy(synth.seeded_input(cfg, rank, "normal" if args.workload.startswith(("conv", "block")) else "uniform")).pin_memory()
     x_dev = x_host.cuda()
     stream = torch.cuda.current_stream()
 
