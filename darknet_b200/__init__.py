@@ -60,6 +60,7 @@ SIGNATURES = {
     "dnb_conv_forward": (_I, [_P, _TP, _TP, _TP, _P]),
     "dnb_conv_xnor_accumulate": (_I, [_P, _TP, _P, _P]),
     "dnb_conv_shortcut_forward": (_I, [_P, _TP, _TP, _TP, _F, _F, _I, _P]),
+    "dnb_conv_yolo_forward": (_I, [_P, _TP, _TP, _I, _I, _P]),
     "dnb_conv_plan_check_status": (_I, [_P]),
     "dnb_conv_xnor_forward_static": (_I, [C.POINTER(ConvDesc), _TP, _P, _P, _P, _P, _TP, _P]),
     "dnb_conv_plan_set_diagnostics": (_I, [_P, C.c_longlong, _I]),

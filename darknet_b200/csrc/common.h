@@ -84,6 +84,9 @@ struct ConvEpilogue {
     int activation2;
     float alpha, beta;
     int raw_acc;          // int8 (xnor) tensor-core launches: write the int32 sums themselves into the NCHW output
+    // fused [yolo] head (tensor-core kernel only): > 0 = entries per anchor (5 + classes); the logistic is applied to
+    // every output channel but the w and h entries of each anchor (ch % entries == 2 or 3), after the activation
+    int yolo_entries;
 };
 
 struct ConvGeom {

@@ -156,6 +156,7 @@ struct dnb_conv_plan {
     const void *tc_res_ptr;  // fused residual the load map was built for (NULL: none)
     int tc_res_cpitch;
     int tc_y_cpitch, tc_y_dtype;
+    int tc_nchw_out;         // the cached launch block was built for a launch that also writes Darknet's layout
     int device;
     long long wait_limit;    // bound of the kernels' waits in cycles (0: the default, about one second)
     int debug_bits;          // OR-ed into the launch block's debug field (dnb_conv_plan_set_diagnostics)

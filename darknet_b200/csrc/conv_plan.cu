@@ -292,24 +292,48 @@ extern "C" int dnb_conv_plan_set_diagnostics(dnb_conv_plan *p, long long wait_li
 }
 
 // ------------------------------------------------------------------ tensor-core launch block
-static void pick_pixel_tile(const ConvGeom &g, int *wt, int *ht, int *bt)
+// Relative cost of writing NCHW output in runs of `run` contiguous pixels (tuning knob DNB_TC_NCHW_PENALTY scales it;
+// 0 = the tile that suits channels-last output).
+static double nchw_run_penalty(int run)
+{
+    static double scale = -1.0;
+    if (scale < 0.0) { const char *e = getenv("DNB_TC_NCHW_PENALTY"); scale = e ? atof(e) : 1.0; }
+    const double base = run >= 32 ? 0.0 : run >= 16 ? 0.03 : run >= 8 ? 0.10 : run >= 4 ? 0.5 : run >= 2 ? 1.0 : 2.0;
+    return scale * base;
+}
+
+static void pick_pixel_tile(const ConvGeom &g, bool nchw_out, int *wt, int *ht, int *bt)
 {
     // wt*ht*bt == 128, powers of two; least padded work, then widest rows.
+    // A launch that writes Darknet's layout stores, per filter plane, one run of wt pixels per tile row: runs shorter
+    // than a 32-byte sector make every store a partial-sector write, which costs far more than the padded work of a
+    // wider tile (measured on the 255-filter heads of YOLOv3-608, batch 64: 4-pixel runs 2.0 ms, see nchw_run_penalty).
     double best = 1e300;
     for (int w = 1; w <= 128; w *= 2)
         for (int h = 1; w * h <= 128; h *= 2) {
             const int b = 128 / (w * h);
             const double work = (double)round_up(g.out_w, w) * round_up(g.out_h, h) * round_up(g.batch, b);
-            const double score = work * (1.0 + 1e-6 * (128 - w) + 1e-7 * (128 - h));
+            double score = work * (1.0 + 1e-6 * (128 - w) + 1e-7 * (128 - h));
+            if (nchw_out) score *= 1.0 + nchw_run_penalty(w < g.out_w ? w : g.out_w);
             if (score < best) { best = score; *wt = w; *ht = h; *bt = b; }
         }
 }
 
 static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, int y_dtype, int y_cpitch,
-                         const void *residual, int res_cpitch)
+                         const void *residual, int res_cpitch, bool nchw_out)
 {
     TcArgs &a = p->tc;
-    const ConvGeom &g = p->g;
+    // A 1x1 convolution (stride 1, no padding) does not care which pixels are neighbours: with Darknet's layout among
+    // the outputs, the h x w plane is treated as one row of h*w pixels, so that a tile is a run of up to 128 contiguous
+    // pixels of every filter plane (and of the channels-last input) instead of a wt x ht patch.  DNB_TC_FLAT=0: never.
+    ConvGeom g = p->g;
+    {
+        const char *e = getenv("DNB_TC_FLAT");
+        if (nchw_out && g.size == 1 && g.stride == 1 && g.pad == 0 && !(e && atoi(e) == 0)) {
+            g.w = g.out_w = g.w * g.h;
+            g.h = g.out_h = 1;
+        }
+    }
     const bool bf16 = p->kernel == K_TC_BF16, i8 = p->kernel == K_XNOR;
     const int es = i8 ? 1 : (bf16 ? 2 : 4);
     const int kind = i8 ? 2 : (bf16 ? 1 : 0);              // element kind of the operands (and of their tensor maps)
@@ -320,7 +344,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     a.bk = a.row_bytes / es;
     a.c_blocks = (c_pad + a.bk - 1) / a.bk;
     a.taps = g.size * g.size;
-    pick_pixel_tile(g, &a.wt, &a.ht, &a.bt);
+    pick_pixel_tile(g, nchw_out, &a.wt, &a.ht, &a.bt);
     // Halo mode (experimental, off unless DNB_TC_HALO is 1 or 2): one activation box per channel block serves all
     // nine taps of a 3x3 stride-1 layer, which cuts the bytes that cross L2 -> shared memory by 2.3x on the
     // 32- and 64-channel layers of large maps.  Measured on YOLOv3-608 batch 64 it does not pay yet: the 8 x 16
@@ -361,6 +385,13 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     a.n_tiles = (p->n_pad + a.bn - 1) / a.bn;
     while (ptiles * a.n_tiles < sm_count() && a.bn >= 128 && a.bn % 128 == 0) {  // too few tiles to fill the SMs
         a.bn /= 2;
+        a.n_tiles = (p->n_pad + a.bn - 1) / a.bn;
+    }
+    // A launch that writes Darknet's layout spends a store per output element in its epilogue; behind a short K loop
+    // (the 1x1 heads of YOLOv3) that is the whole run time, and the four epilogue warps of one CTA per SM issue it
+    // slowly: 128-filter tiles leave TMEM for a second CTA, i.e. eight epilogue warps.
+    if (nchw_out && a.bn == 256 && g.size * g.size * a.c_blocks <= 16) {
+        a.bn = 128;
         a.n_tiles = (p->n_pad + a.bn - 1) / a.bn;
     }
     // CTA pairs (cta_group::2): for layers whose filters come in whole tiles of 256 and whose K loop is long enough to
@@ -525,6 +556,7 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     p->tc_y_dtype = y_dtype;
     p->tc_res_ptr = residual;
     p->tc_res_cpitch = res_cpitch;
+    p->tc_nchw_out = nchw_out ? 1 : 0;
     return DNB_OK;
 }
 
@@ -552,6 +584,7 @@ struct Residual {
     const dnb_tensor *add = nullptr;
     float alpha = 1.f, beta = 1.f;
     int activation = DNB_LINEAR;
+    int yolo_entries = 0;   // instead of a residual: the [yolo] layer's activations, entries per anchor
 };
 
 static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_tensor *y, const dnb_tensor *y2,
@@ -571,7 +604,12 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
         if (o->layout == DNB_NHWC) { y_nhwc = o->data; y_dtype = o->dtype; y_cpitch = o->cpitch; }
         else y_nchw = (float *)o->data;
     }
-    ConvEpilogue ep{p->scale, p->shift, p->d.activation, 0, nullptr, 0, DNB_LINEAR, 1.f, 1.f, 0};
+    ConvEpilogue ep{p->scale, p->shift, p->d.activation, 0, nullptr, 0, DNB_LINEAR, 1.f, 1.f, 0, 0};
+    if (res && res->yolo_entries > 0) {
+        if (p->kernel != K_TC_TF32 && p->kernel != K_TC_BF16)
+            DNB_FAIL(DNB_EUNSUPPORTED, "conv + yolo: only tensor-core plans fuse the yolo activations (this plan is %s)", kKernelNames[p->kernel]);
+        ep.yolo_entries = res->yolo_entries;
+    }
     if (res && res->add) {
         if (p->kernel != K_TC_TF32 && p->kernel != K_TC_BF16)
             DNB_FAIL(DNB_EUNSUPPORTED, "conv + shortcut: only tensor-core plans fuse the residual (this plan is %s)", kKernelNames[p->kernel]);
@@ -624,8 +662,8 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
         if (y_nhwc && y_dtype != DNB_F32) DNB_FAIL(DNB_EINVAL, "conv: an xnor plan writes channels-last output as f32");
         float *nchw = acc_out ? reinterpret_cast<float *>(acc_out) : y_nchw;
         void *nhwc = acc_out ? nullptr : y_nhwc;
-        if (p->tc_x_ptr != xin.data || p->tc_y_ptr != nhwc || p->tc_y_cpitch != (nhwc ? y_cpitch : 0) || !p->status)
-            DNB_TRY(build_tc_args(p, &xin, nhwc, DNB_F32, nhwc ? y_cpitch : 0, nullptr, 0));
+        if (p->tc_x_ptr != xin.data || p->tc_y_ptr != nhwc || p->tc_y_cpitch != (nhwc ? y_cpitch : 0) || !p->status || p->tc_nchw_out != (nchw ? 1 : 0))
+            DNB_TRY(build_tc_args(p, &xin, nhwc, DNB_F32, nhwc ? y_cpitch : 0, nullptr, 0, nchw != nullptr));
         TcArgs &a = p->tc;
         a.y_nhwc = nhwc; a.y_dtype = DNB_F32; a.y_cpitch = nhwc ? y_cpitch : 0; a.y_nchw = nchw;
         ep.scale = p->scale_i8;
@@ -671,8 +709,9 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
     if (y_nhwc && y_dtype != want)
         DNB_FAIL(DNB_EINVAL, "conv: a %s plan writes channels-last output as %s", kKernelNames[p->kernel], want == DNB_BF16 ? "bf16" : "f32");
     if (p->tc_x_ptr != xin.data || p->tc_x_cpitch != xin.cpitch || p->tc_y_ptr != y_nhwc || p->tc_y_cpitch != y_cpitch ||
-        p->tc_y_dtype != y_dtype || !p->status || p->tc_res_ptr != ep.residual || p->tc_res_cpitch != ep.res_cpitch)
-        DNB_TRY(build_tc_args(p, &xin, y_nhwc, y_dtype, y_cpitch, ep.residual, ep.res_cpitch));
+        p->tc_y_dtype != y_dtype || !p->status || p->tc_res_ptr != ep.residual || p->tc_res_cpitch != ep.res_cpitch ||
+        p->tc_nchw_out != (y_nchw ? 1 : 0))
+        DNB_TRY(build_tc_args(p, &xin, y_nhwc, y_dtype, y_cpitch, ep.residual, ep.res_cpitch, y_nchw != nullptr));
     TcArgs &a = p->tc;
     a.y_nhwc = y_nhwc; a.y_dtype = y_dtype; a.y_cpitch = y_cpitch; a.y_nchw = y_nchw;
     a.ep = ep;
@@ -703,6 +742,23 @@ extern "C" int dnb_conv_shortcut_forward(dnb_conv_plan *p, const dnb_tensor *x, 
         DNB_FAIL(DNB_EUNSUPPORTED, "conv + shortcut: the residual must have the output's extents (other shapes: dnb_shortcut_forward)");
     Residual r;
     r.add = add; r.alpha = alpha; r.beta = beta; r.activation = activation2;
+    return conv_forward_impl(p, x, y, nullptr, nullptr, (cudaStream_t)stream, &r);
+}
+
+// Convolution followed by the [yolo] layer that reads it, one launch: forward_yolo_layer_gpu at inference copies
+// its input and applies the logistic to the x, y, objectness and class entries of every anchor
+// (src/yolo_layer.c:347-357); here the convolution's epilogue does that and writes the [yolo] layer's NCHW output.
+extern "C" int dnb_conv_yolo_forward(dnb_conv_plan *p, const dnb_tensor *x, const dnb_tensor *y, int anchors, int classes, void *stream)
+{
+    if (!p) DNB_FAIL(DNB_EINVAL, "conv + yolo: null plan");
+    DNB_TRY(check_conv_io(p, x, y, nullptr));
+    if (anchors < 1 || classes < 0 || p->g.n != anchors * (classes + 5))
+        DNB_FAIL(DNB_EINVAL, "conv + yolo: %d filters are not %d anchors of %d entries", p->g.n, anchors, classes + 5);
+    if (y->layout != DNB_NCHW || y->dtype != DNB_F32) DNB_FAIL(DNB_EINVAL, "conv + yolo: the output is Darknet's layout (NCHW f32)");
+    if (p->d.activation != DNB_LINEAR) DNB_FAIL(DNB_EUNSUPPORTED, "conv + yolo: the convolution's own activation must be linear (as in every yolo cfg)");
+    if (p->g.n % 256 == 0) DNB_FAIL(DNB_EUNSUPPORTED, "conv + yolo: %d filters (whole tiles of 256 may run as CTA pairs, which have no yolo epilogue)", p->g.n);
+    Residual r;
+    r.yolo_entries = classes + 5;
     return conv_forward_impl(p, x, y, nullptr, nullptr, (cudaStream_t)stream, &r);
 }
 

@@ -64,13 +64,13 @@ struct TcShared {
 };
 
 enum { WAIT_EMPTY = 101, WAIT_FULL = 102, WAIT_ACC_EMPTY = 103, WAIT_ACC_FULL = 104, WAIT_RESIDUAL = 105, BAD_SMEM_BASE = 106 };
-enum { ACT_GENERIC = -1, ACT2_NONE = -2 };   // ACT2_NONE: no fused residual
+enum { ACT_GENERIC = -1, ACT2_NONE = -2, ACT_YOLO = -3 };   // ACT2_NONE: no fused residual; ACT_YOLO: linear, then the [yolo] layer's per-entry logistic
 
 
 template <int ACT>
 __device__ __forceinline__ float act_apply(float x, int runtime_act)
 {
-    if (ACT == DNB_LINEAR) return x;
+    if (ACT == DNB_LINEAR || ACT == ACT_YOLO) return x;
     if (ACT == DNB_LEAKY) return fmaxf(x, 0.1f * x);   // x > 0 ? x : 0.1x
     return activate_call(x, runtime_act);   // the 14-way switch, out of line
 }
@@ -356,6 +356,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         float *const y_nchw = a.y_nchw;
         const int runtime_act = a.ep.activation, do_round = a.ep.round_tf32;
         const bool raw_acc = I8 && a.ep.raw_acc != 0;
+        const int yolo_entries = ACT == ACT_YOLO ? a.ep.yolo_entries : 1;   // fused [yolo] head: a kernel variant of its own
         constexpr bool residual = ACT2 != ACT2_NONE;
         // A CTA pair reads the residual with plain 16-byte loads, one staged chunk ahead, instead of TMA tiles into the
         // staging buffers: residual tile loads inside the pair kernel raised an illegal-instruction fault on B200 whose
@@ -472,6 +473,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 // scale / shift copies are zero beyond the layer's filters and padded by 64 entries
                 const int nl0 = nt * bn + c0;                 // first filter of this chunk
                 const int nvalid = min(bn - c0, g.n - nl0);   // columns of this chunk that are real filters
+                int yolo_entry = ACT == ACT_YOLO ? nl0 % yolo_entries : 0;   // entry (x, y, w, h, objectness, classes...) of the chunk's first column
                 const float4 *sc4 = reinterpret_cast<const float4 *>(s_scale + c0);
                 const float4 *sf4 = reinterpret_cast<const float4 *>(s_shift + c0);
 #pragma unroll
@@ -483,6 +485,13 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                         const int j = 4 * q + e;
                         const float accv = I8 ? (float)(int)r[j] : __uint_as_float(r[j]);   // int32 sums of an xnor layer are exact in f32 (below 2^24)
                         float t = act_apply<ACT>(fmaf(accv, scv[e], sfv[e]), runtime_act);
+                        if (ACT == ACT_YOLO) {
+                            // forward_yolo_layer_gpu's activations (src/yolo_layer.c:351-357): logistic on x, y, objectness, classes.
+                            // The entry index is the same for the whole warp (it depends on the column only); the epilogue has
+                            // four warps to hide its latencies with, so the fast exponential and division are used (2 ulp).
+                            if (yolo_entry < 2 || yolo_entry >= 4) t = __fdividef(1.f, 1.f + __expf(-t));
+                            if (++yolo_entry == yolo_entries) yolo_entry = 0;
+                        }
                         if (residual) {
                             float rv = 0.f;
                             {
@@ -544,15 +553,18 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                     }
                 }
                 if (y_nchw && pix_ok) {
-                    // Darknet-layout copy: this thread's pixel, one filter plane per staged column, read
-                    // back from the staged row (a rolled loop: registers cannot be indexed dynamically)
+                    // Darknet-layout copy: this thread's pixel, one filter plane per column, straight from the registers
+                    // (a warp's 32 pixels are wt-long runs of each plane).  BF16 plans write what the channels-last
+                    // copy holds: the value rounded to bf16.
                     float *dst = y_nchw + ((size_t)b * g.n + nl0) * plane + (size_t)oh * g.out_w + ow;
                     const int cols = min(CPC, g.n - nl0);
-                    for (int j = 0; j < cols; ++j) {
-                        float v;
-                        if (!out_bf16) v = *reinterpret_cast<const float *>(row + ((((j >> 2) ^ q_xor) << 4) | ((j & 3) << 2)));
-                        else v = __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(row + ((((j >> 3) ^ q_xor) << 4) | ((j & 7) << 1))));
-                        dst[(size_t)j * plane] = v;
+#pragma unroll
+                    for (int j = 0; j < CPC; ++j) {
+                        if (j < cols) {
+                            float v = __uint_as_float(r[j]);
+                            if (out_bf16) v = __bfloat162float(__float2bfloat16_rn(v));
+                            dst[(size_t)j * plane] = v;
+                        }
                     }
                 }
                 ++chunk_count;
@@ -690,6 +702,17 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
         else if (obf && cpc == 16) DNB_TC_GO_SINGLE(ACT, 16, true, ACT2, false); \
         else DNB_FAIL(DNB_EINVAL, "conv_tc: no kernel for %d columns per chunk", cpc); \
     } while (0)
+    // (a yolo head's filters are anchors * (classes + 5), never whole tiles of 256: no pair variant)
+#define DNB_TC_LAUNCH_ACT_SINGLE(ACT, ACT2)                                     \
+    do {                                                                        \
+        if (a.pair) DNB_FAIL(DNB_EINVAL, "conv_tc: no pair variant of this epilogue"); \
+        if (!obf && cpc == 32) DNB_TC_GO_SINGLE(ACT, 32, false, ACT2, false);   \
+        else if (!obf && cpc == 16) DNB_TC_GO_SINGLE(ACT, 16, false, ACT2, false); \
+        else if (obf && cpc == 64) DNB_TC_GO_SINGLE(ACT, 64, true, ACT2, false); \
+        else if (obf && cpc == 32) DNB_TC_GO_SINGLE(ACT, 32, true, ACT2, false); \
+        else if (obf && cpc == 16) DNB_TC_GO_SINGLE(ACT, 16, true, ACT2, false); \
+        else DNB_FAIL(DNB_EINVAL, "conv_tc: no kernel for %d columns per chunk", cpc); \
+    } while (0)
 #define DNB_TC_LAUNCH_I8_ACT(ACT)                                               \
     do {                                                                        \
         if (cpc == 32) DNB_TC_GO(ACT, 32, false, ACT2_NONE, true);              \
@@ -697,27 +720,31 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
         else DNB_FAIL(DNB_EINVAL, "conv_tc: no int8 kernel for %d columns per chunk", cpc); \
     } while (0)
     if (i8) {
-        if (a.ep.residual) DNB_FAIL(DNB_EUNSUPPORTED, "conv_tc: the int8 (xnor) kernel fuses no residual");
+        if (a.ep.residual || a.ep.yolo_entries) DNB_FAIL(DNB_EUNSUPPORTED, "conv_tc: the int8 (xnor) kernel fuses neither a residual nor a yolo head");
         switch (a.ep.activation) {
         case DNB_LINEAR: DNB_TC_LAUNCH_I8_ACT(DNB_LINEAR); break;
         case DNB_LEAKY: DNB_TC_LAUNCH_I8_ACT(DNB_LEAKY); break;
         default: DNB_TC_LAUNCH_I8_ACT(ACT_GENERIC); break;
         }
     } else if (!a.ep.residual) {
-        switch (a.ep.activation) {
+        if (a.ep.yolo_entries > 0 && a.ep.activation != DNB_LINEAR) DNB_FAIL(DNB_EUNSUPPORTED, "conv_tc: a fused yolo head follows a linear convolution");
+        switch (a.ep.yolo_entries > 0 ? (int)ACT_YOLO : a.ep.activation) {
         case DNB_LINEAR: DNB_TC_LAUNCH_ACT(DNB_LINEAR, ACT2_NONE); break;
         case DNB_LEAKY: DNB_TC_LAUNCH_ACT(DNB_LEAKY, ACT2_NONE); break;
+        case ACT_YOLO: DNB_TC_LAUNCH_ACT_SINGLE(ACT_YOLO, ACT2_NONE); break;
         default: DNB_TC_LAUNCH_ACT(ACT_GENERIC, ACT2_NONE); break;
         }
     } else {
         // fused shortcut: the two pairs the reference's cfgs use (yolov3: leaky conv, linear shortcut; resnet:
         // linear conv, leaky shortcut) are compile-time, every other pair takes the run-time switches
+        if (a.ep.yolo_entries) DNB_FAIL(DNB_EUNSUPPORTED, "conv_tc: a residual and a yolo head in one launch");
         if (a.stage_bufs != (a.pair ? 2 : 4)) DNB_FAIL(DNB_EINVAL, "conv_tc: a fused residual needs four staging buffers (two in pair mode)");
         if (a.ep.activation == DNB_LEAKY && a.ep.activation2 == DNB_LINEAR) DNB_TC_LAUNCH_ACT(DNB_LEAKY, DNB_LINEAR);
         else if (a.ep.activation == DNB_LINEAR && a.ep.activation2 == DNB_LEAKY) DNB_TC_LAUNCH_ACT(DNB_LINEAR, DNB_LEAKY);
         else DNB_TC_LAUNCH_ACT(ACT_GENERIC, ACT_GENERIC);
     }
 #undef DNB_TC_LAUNCH_I8_ACT
+#undef DNB_TC_LAUNCH_ACT_SINGLE
 #undef DNB_TC_LAUNCH_ACT
 #undef DNB_TC_GO_SINGLE
 #undef DNB_TC_GO

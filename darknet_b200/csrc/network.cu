@@ -53,6 +53,8 @@ struct Layer {
     int launches = 1;
     // a convolution that also performs the [shortcut] layer right after it, and that shortcut layer
     bool fuses_next_shortcut = false, fused_into_prev = false;
+    // a convolution that also performs the [yolo] layer right after it (that layer is then fused_into_prev too)
+    bool fuses_next_yolo = false;
     // the output is a channel range of a later [route] layer's output: its producer writes it in place and the route
     // has nothing to copy for it (the memory belongs to the route layer)
     bool out_is_view = false;
@@ -337,6 +339,29 @@ static int build_network(const char *text, int mode, int batch_override, dnb_net
         cudaFree(C.out.data);      // never written: the convolution stores straight into the shortcut's output
         C.out.data = nullptr;
     }
+    // Fuse "convolution, then [yolo]" when nothing else reads the convolution's output: the epilogue applies the yolo
+    // layer's logistic per entry and writes that layer's NCHW output; the channels-last copy of the raw predictions
+    // and the pass that transposed it (forward_yolo_layer_gpu, src/yolo_layer.c:347-357) disappear.
+    // DNB_FUSE_YOLO=0 keeps the two layers separate.
+    const bool fuse_yolo = getenv("DNB_FUSE_YOLO") ? atoi(getenv("DNB_FUSE_YOLO")) != 0 : true;
+    for (int i = 0; fuse_yolo && i + 1 < (int)net->layers.size(); ++i) {
+        Layer &C = net->layers[i], &Y = net->layers[i + 1];
+        if (C.kind != L_CONV || !C.plan || (C.plan->kernel != 0 && C.plan->kernel != 1) || C.plan->stem_tc || Y.kind != L_YOLO) continue;
+        if (C.plan->d.activation != DNB_LINEAR || C.plan->g.n % 256 == 0) continue;   // the fused epilogue is built for the linear heads every yolo cfg has (and not for CTA pairs)
+        bool read_elsewhere = false;
+        for (int j = i + 2; j < (int)net->layers.size(); ++j) {
+            const Layer &L = net->layers[j];
+            if (L.kind == L_SHORTCUT && L.from == i) read_elsewhere = true;
+            if (L.kind == L_ROUTE)
+                for (int id : L.inputs) if (id == i) read_elsewhere = true;
+        }
+        if (read_elsewhere) continue;
+        C.fuses_next_yolo = true;
+        Y.fused_into_prev = true;
+        Y.launches = 0;
+        cudaFree(C.out.data);      // never written: the convolution stores straight into the yolo layer's output
+        C.out.data = nullptr;
+    }
     // Zero-copy [route]: where a route input is produced by a layer whose kernel can write a channel range of a wider
     // channels-last tensor (tensor-core convolutions, with or without a fused shortcut, and upsample), and everything that
     // reads it can read such a range (convolutions, routes, the yolo head, upsample), the input's tensor BECOMES its
@@ -603,7 +628,7 @@ extern "C" int dnb_network_export_layer(dnb_network *net, int layer, float *devi
 {
     if (!net || !device_nchw || layer < 0 || layer >= (int)net->layers.size()) DNB_FAIL(DNB_EINVAL, "export_layer: bad argument");
     Layer &L = net->layers[layer];
-    if (!L.out.data) DNB_FAIL(DNB_EUNSUPPORTED, "layer %d is fused into the shortcut layer %d and has no output of its own", layer, layer + 1);
+    if (!L.out.data) DNB_FAIL(DNB_EUNSUPPORTED, "layer %d is fused into layer %d and has no output of its own", layer, layer + 1);
     cudaStream_t s = (cudaStream_t)stream;
     if (L.out.layout == DNB_NCHW) {
         DNB_CUDA(cudaMemcpyAsync(device_nchw, L.out.data, tensor_elems(&L.out) * sizeof(float), cudaMemcpyDeviceToDevice, s));
@@ -649,6 +674,10 @@ static int forward_layer(dnb_network *net, int i, const float *device_input, cud
             Layer &S = net->layers[i + 1];
             return dnb_conv_shortcut_forward(L.plan, &in, &net->layers[S.from].out, &S.out, S.alpha, S.beta, S.activation, s);
         }
+        if (L.fuses_next_yolo) {
+            Layer &Y = net->layers[i + 1];
+            return dnb_conv_yolo_forward(L.plan, &in, &Y.out, Y.anchors, Y.classes, s);
+        }
         return dnb_conv_forward(L.plan, &in, &L.out, nullptr, s);
     case L_CONNECTED: {
         // forward_connected_layer_gpu (src/connected_layer.c:288-306): the previous layer's whole channels-last output
@@ -668,7 +697,9 @@ static int forward_layer(dnb_network *net, int i, const float *device_input, cud
         for (int id : L.inputs) ins.push_back(&net->layers[id].out);
         return launch_route(ins.data(), (int)ins.size(), &L.out, s);
     }
-    case L_YOLO: return launch_convert(&in, &L.out, 0, L.anchors, L.classes, s);
+    case L_YOLO:
+        if (L.fused_into_prev) return DNB_OK;   // done by the convolution before it
+        return launch_convert(&in, &L.out, 0, L.anchors, L.classes, s);
     case L_AVGPOOL: return launch_avgpool(&in, &L.out, s);
     case L_SOFTMAX: return launch_softmax(&in, &L.out, L.groups, L.temperature, s);
     }
@@ -882,7 +913,7 @@ extern "C" int dnb_network_layer_output_images(dnb_network *net, int i, int firs
     Layer &L = net->layers[i];
     if (net->submitted != net->collected) DNB_FAIL(DNB_EINVAL, "layer_output: a submitted step is still in flight; collect it first");
     if (!L.out.data)
-        DNB_FAIL(DNB_EUNSUPPORTED, "layer %d is fused into the shortcut layer %d and has no output of its own (DNB_FUSE_SHORTCUT=0 keeps it)", i, i + 1);
+        DNB_FAIL(DNB_EUNSUPPORTED, "layer %d is fused into layer %d and has no output of its own (DNB_FUSE_SHORTCUT=0 / DNB_FUSE_YOLO=0 keep it)", i, i + 1);
     const size_t per_image = (size_t)L.out_c * L.out_h * L.out_w;
     const size_t elems = (size_t)count * per_image;
     DNB_CUDA(cudaDeviceSynchronize());  // the forward may have run on any stream

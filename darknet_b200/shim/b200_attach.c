@@ -148,7 +148,7 @@ static int route_is_covered(const network *net, const layer *l)
  * [yolo] layer's l.output and the last layer's, are page-locked in place while the network is attached. */
 static void pin_outputs(attached *a, network *net)
 {
-    a->pinned = calloc(net->n, 1);
+    a->pinned = calloc((size_t)net->n, 1);
     for (int i = 0; i < net->n; ++i) {
         layer *l = &net->layers[i];
         if ((l->type != YOLO && i != net->n - 1) || !l->output) continue;
@@ -179,8 +179,8 @@ int b200_attach(network *net, int mode)
     attached *a = calloc(1, sizeof *a);
     a->layers = net->layers;
     a->n = net->n;
-    a->plans = calloc(net->n, sizeof *a->plans);
-    a->original = calloc(net->n, sizeof *a->original);
+    a->plans = calloc((size_t)net->n, sizeof *a->plans);
+    a->original = calloc((size_t)net->n, sizeof *a->original);
     int count = 0;
     for (int i = 0; i < net->n; ++i) {
         layer *l = &net->layers[i];
@@ -218,7 +218,7 @@ int b200_attach(network *net, int mode)
     }
     /* inference only from here to b200_detach: forward_network_gpu zero-fills every layer's delta before calling
      * it (src/network.c:775-777), 30 GB per YOLOv3-608 batch of 64; with the pointers set aside it has nothing to clear */
-    a->saved_delta = calloc(net->n, sizeof *a->saved_delta);
+    a->saved_delta = calloc((size_t)net->n, sizeof *a->saved_delta);
     for (int i = 0; i < net->n; ++i) {
         a->saved_delta[i] = net->layers[i].delta_gpu;
         net->layers[i].delta_gpu = NULL;
@@ -319,6 +319,7 @@ static void forward_yolo_pull_b200(layer l, network net)
 int b200_attach_network(network *net, int mode)
 {
     if (!net || net->n < 1 || find_attached(net->layers)) return -1;
+    const size_t count = (size_t)net->n;
     char *cfg = cfg_from_structs(net);
     if (!cfg) return -1;
     dnb_network *whole = NULL;
@@ -335,9 +336,9 @@ int b200_attach_network(network *net, int mode)
     attached *a = calloc(1, sizeof *a);
     a->layers = net->layers;
     a->n = net->n;
-    a->plans = calloc(net->n, sizeof *a->plans);
-    a->original = calloc(net->n, sizeof *a->original);
-    a->saved_delta = calloc(net->n, sizeof *a->saved_delta);
+    a->plans = calloc(count, sizeof *a->plans);
+    a->original = calloc(count, sizeof *a->original);
+    a->saved_delta = calloc(count, sizeof *a->saved_delta);
     a->whole = whole;
     for (int i = 0; i < net->n; ++i) {
         layer *l = &net->layers[i];

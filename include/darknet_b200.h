@@ -140,6 +140,17 @@ int dnb_conv_forward(dnb_conv_plan *plan, const dnb_tensor *x, const dnb_tensor 
 int dnb_conv_shortcut_forward(dnb_conv_plan *plan, const dnb_tensor *x, const dnb_tensor *add,
                               const dnb_tensor *y, float alpha, float beta, int activation2, void *stream);
 
+/* A convolution and the [yolo] layer that follows it in one launch.  At inference
+ * forward_yolo_layer_gpu (src/yolo_layer.c:347-357) copies its input and applies the
+ * logistic to the x, y, objectness and class entries of every anchor, i.e. to every
+ * channel ch with ch % (classes + 5) not 2 or 3; here the convolution's epilogue does
+ * that after the layer's own activation and writes y, the [yolo] layer's output
+ * (NCHW f32, anchors * (classes + 5) channels = the plan's filters).  Tensor-core plans
+ * only; x channels-last in the plan's storage type.  The network object uses it wherever
+ * nothing else reads the convolution's own output. */
+int dnb_conv_yolo_forward(dnb_conv_plan *plan, const dnb_tensor *x, const dnb_tensor *y,
+                          int anchors, int classes, void *stream);
+
 /* Integer accumulators of an xnor plan, before scale/batchnorm/activation:
  * acc[b][n][oh][ow] (NCHW int32) = sum over in-bounds taps of sign(w)*sign(x).
  * What binarize + im2col + gemm produce in the reference

@@ -48,7 +48,7 @@ def compare_layers(net, want_by_image, tol, name):
             try:
                 got = net.layer_output_images(i, img, 1)
             except dn.DarknetB200Error as e:
-                assert e.status == dn.EUNSUPPORTED   # a convolution whose shortcut was fused has no output of its own
+                assert e.status == dn.EUNSUPPORTED   # a convolution fused with the shortcut or yolo layer after it has no output of its own
                 continue
             parity(got, wnt.reshape(got.shape), tol, f"{name} image {img} layer {i} ({net.layer_kernel(i)})")
             checked += 1
@@ -73,7 +73,7 @@ def test_yolov3_608_batch_64(yolov3_b64, mode, tol):
     net = dn.Network(cfg, wpath, mode, text=True)
     out = net.predict(x)
     checked = compare_layers(net, want, tol, f"yolov3-608 b64 mode {mode}")
-    assert checked >= 3 * (107 - 23)
+    assert checked >= 3 * (107 - 23 - 3)
     heads = [i for i in range(net.n) if net.layer_type(i) == "yolo"]
     for img, w in want.items():
         for i in heads:

@@ -88,11 +88,11 @@ def test_yolov3_608_one_image_every_layer(tmp_path):
         try:
             got = net.layer_output(i)
         except dn.DarknetB200Error:
-            continue                                        # a convolution whose shortcut was fused has no output of its own
+            continue                                        # a convolution fused with the shortcut or yolo layer after it has no output of its own
         e = parity(got, wnt, TOL_TF32, f"layer {i}")
         worst = max(worst, e)
         checked += 1
-    assert checked >= 107 - 23
+    assert checked >= 107 - 23 - 3
     print(f"yolov3-608: {checked} layer outputs checked, worst rel error {worst:.3g}")
     # a batch of two: each image's heads equal the single-image run, bit for bit
     cfg2 = synth.yolov3_cfg(batch=2, size=608)

@@ -482,6 +482,43 @@ def test_conv_tc_cta_pairs_with_fused_shortcut(mode, tol, monkeypatch):
     assert padding_is_zero(yt, n)
 
 
+@pytest.mark.parametrize("mode,tol", [(dn.MODE_TF32, TOL_TF32), (dn.MODE_BF16, TOL_BF16)])
+@pytest.mark.parametrize("shape", [dict(b=2, c=256, h=19, w=19, anchors=3, classes=80),      # YOLOv3's heads: 255 filters
+                                   dict(b=3, c=64, h=13, w=11, anchors=2, classes=1),        # 12 filters, ragged tiles
+                                   dict(b=1, c=128, h=8, w=8, anchors=5, classes=20)])       # 125 filters
+def test_conv_with_fused_yolo_head(shape, mode, tol):
+    """Convolution + the [yolo] layer after it in one launch against the checker's convolution followed by its
+    yolo layer (src/yolo_layer.c:347-357: logistic on every entry but w and h of each anchor)."""
+    import ctypes as C
+    anchors, classes = shape["anchors"], shape["classes"]
+    n = anchors * (classes + 5)
+    case = conv_case(270 + n, b=shape["b"], c=shape["c"], h=shape["h"], w=shape["w"], n=n, size=1, bn=False, act="linear")
+    x = case["x"]
+    b, c, h, wd = x.shape
+    store = torch.bfloat16 if mode == dn.MODE_BF16 else torch.float32
+    want = orc.yolo_forward(oracle_conv(case), anchors, classes)
+    plan = dn.ConvPlan(b, c, h, wd, n, 1, 1, 0, 1, False, "linear", False, mode)
+    plan.set_params(case["w"], case["biases"], None, None, None)
+    xt, xd = dev_nhwc(x, store)
+    yt, yd = empty_nchw(b, n, h, wd)
+    yt.fill_(float("nan"))
+    dn.check(dn.lib().dnb_conv_yolo_forward(plan.handle, C.byref(xd), C.byref(yd), anchors, classes,
+                                            C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    plan.check_status()
+    got = yt.cpu().numpy()
+    assert np.isfinite(got).all()
+    parity(got, want, tol, f"fused yolo head, {n} filters")
+    # the w and h entries are the raw predictions, everything else went through the logistic
+    raw = got.reshape(b, anchors, classes + 5, h, wd)
+    assert ((raw[:, :, [0, 1]] > 0) & (raw[:, :, [0, 1]] < 1)).all() and ((raw[:, :, 4:] > 0) & (raw[:, :, 4:] < 1)).all()
+    assert (raw[:, :, 2:4] < 0).any()
+    # wrong anchor count for the plan's filters
+    with pytest.raises(dn.DarknetB200Error) as e:
+        dn.check(dn.lib().dnb_conv_yolo_forward(plan.handle, C.byref(xd), C.byref(yd), anchors + 1, classes, None))
+    assert e.value.status == dn.EINVAL
+
+
 def test_conv_tc_all_ones_counts_taps():
     # analytic known answer: ones everywhere -> in-image taps x channels, exact in TF32 and BF16
     C, H, W, N = 16, 9, 10, 16

@@ -39,8 +39,9 @@ def build(cfg, params, tmp_path, mode):
 @pytest.mark.parametrize("fuse", [0, 1])
 def test_network_matches_oracle_and_golden(name, mode, fuse, tmp_path, golden, monkeypatch):
     # fuse=0: every layer separate, every layer's output checked; fuse=1 (the default): convolutions absorb the
-    # shortcut layer after them, their own outputs do not exist and are skipped
+    # shortcut or yolo layer after them, their own outputs do not exist and are skipped
     monkeypatch.setenv("DNB_FUSE_SHORTCUT", str(fuse))
+    monkeypatch.setenv("DNB_FUSE_YOLO", str(fuse))
     cfg, pseed, iseed, dist = CASES[name]
     params = synth.seeded_params(cfg, pseed)
     x = synth.seeded_input(cfg, iseed, dist)
@@ -55,7 +56,7 @@ def test_network_matches_oracle_and_golden(name, mode, fuse, tmp_path, golden, m
         try:
             got = net.layer_output(i)
         except dn.DarknetB200Error as e:
-            assert fuse and e.status == dn.EUNSUPPORTED and kinds[i] == "convolutional" and kinds[i + 1] == "shortcut"
+            assert fuse and e.status == dn.EUNSUPPORTED and kinds[i] == "convolutional" and kinds[i + 1] in ("shortcut", "yolo")
             skipped += 1
             continue
         assert got.shape == w.shape or got.size == w.size
@@ -70,8 +71,8 @@ def test_network_matches_oracle_and_golden(name, mode, fuse, tmp_path, golden, m
     for i, k in enumerate(kinds):
         if k == "yolo":
             parity(net.yolo_output(i), want[i], TOL[mode])
-    if fuse and mode != dn.MODE_FP32 and "shortcut" in kinds:
-        assert skipped > 0, "no convolution was fused with its shortcut"
+    if fuse and mode != dn.MODE_FP32 and ("shortcut" in kinds or "yolo" in kinds):
+        assert skipped > 0, "no convolution was fused with the shortcut or yolo layer after it"
     if not fuse:
         assert skipped == 0
     print(f"{name} mode {mode} fuse {fuse}: worst per-layer rel error {worst:.3g}, {skipped} fused layers")
