@@ -83,6 +83,10 @@ struct alignas(64) TcArgs {
     int y_dtype, y_cpitch;
     float *y_nchw;
     int *status;          // device word: 0, or the code of the wait that expired
+    // split-K (layers with fewer tiles than SMs and a long K loop): total_tiles counts (output tile, K range) pairs
+    int splits;           // K ranges per output tile; 1 = off
+    void *split_scratch;  // [output tile][range][128 rows][bn] raw accumulators (f32, or int32 of the int8 kind)
+    int *split_counters;  // [output tile] ranges delivered so far; zero between launches
     ConvGeom g;
     ConvEpilogue ep;
 };
@@ -156,8 +160,15 @@ struct dnb_conv_plan {
     const void *tc_res_ptr;  // fused residual the load map was built for (NULL: none)
     int tc_res_cpitch;
     int tc_y_cpitch, tc_y_dtype;
+    void *split_scratch;     // split-K partial sums and counters of the cached launch block (owned by the plan)
+    size_t split_scratch_bytes;
+    int *split_counters;
+    int split_counters_n;
     int tc_nchw_out;         // the cached launch block was built for a launch that also writes Darknet's layout
     int device;
     long long wait_limit;    // bound of the kernels' waits in cycles (0: the default, about one second)
     int debug_bits;          // OR-ed into the launch block's debug field (dnb_conv_plan_set_diagnostics)
 };
+
+// zero the split-K counters a timed-out launch may have left part-way (on `s`; a null plan or one without counters: nothing)
+void conv_plan_reset_after_abort(dnb_conv_plan *p, cudaStream_t s = nullptr);

@@ -72,6 +72,7 @@ extern "C" void dnb_conv_plan_destroy(dnb_conv_plan *p)
     if (!p) return;
     cudaFree(p->scale); cudaFree(p->shift); cudaFree(p->w_tc); cudaFree(p->w_direct); cudaFree(p->w_bits);
     cudaFree(p->w_mean); cudaFree(p->x_nhwc_scratch); cudaFree(p->x_bits); cudaFree(p->w_i8); cudaFree(p->scale_i8); cudaFree(p->x_i8);
+    cudaFree(p->split_scratch); cudaFree(p->split_counters);
     if (!p->status_shared) cudaFree(p->status);
     delete p;
 }
@@ -88,8 +89,8 @@ extern "C" int dnb_conv_plan_describe(const dnb_conv_plan *p, char *buf, int len
     if (!p || !buf || len < 1) DNB_FAIL(DNB_EINVAL, "conv describe: bad argument");
     const TcArgs &a = p->tc;
     if ((p->kernel == K_TC_TF32 || p->kernel == K_TC_BF16 || (p->kernel == K_XNOR && p->xnor_tc)) && p->tc_x_ptr)
-        snprintf(buf, len, "%s pair=%d halo=%d bn=%d tile=%dx%dx%d tiles=%d stages=%d ctas_per_sm=%d srb=%d", kKernelNames[p->kernel], a.pair, a.halo,
-                 a.bn, a.wt, a.ht, a.bt, a.total_tiles, a.stages, a.ctas_per_sm, a.store_row_bytes);
+        snprintf(buf, len, "%s pair=%d halo=%d bn=%d tile=%dx%dx%d tiles=%d stages=%d ctas_per_sm=%d srb=%d splits=%d", kKernelNames[p->kernel], a.pair, a.halo,
+                 a.bn, a.wt, a.ht, a.bt, a.total_tiles, a.stages, a.ctas_per_sm, a.store_row_bytes, a.splits);
     else
         snprintf(buf, len, "%s", dnb_conv_plan_kernel(p));
     return DNB_OK;
@@ -410,7 +411,9 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
         // single CTAs per SM with two or three slots each starve on load latency, which outweighs the idle SMs.
         const int pair_tiles = (ptiles + 1) / 2 * (g.n / 256), clusters = sm_count() / 2;
         const int k_iters_p = g.size * g.size * a.c_blocks;
-        const bool enough = pair_tiles >= clusters || (k_iters_p >= 64 && 2 * pair_tiles >= clusters);
+        // (with split-K, below, a sixteenth of them is enough: every pair tile becomes up to eight)
+        const bool split_ok = !(getenv("DNB_TC_SPLITK") && atoi(getenv("DNB_TC_SPLITK")) == 0) && !i8;
+        const bool enough = pair_tiles >= clusters || (k_iters_p >= 64 && (2 * pair_tiles >= clusters || (split_ok && 16 * pair_tiles >= clusters)));
         const bool legal = !a.halo && a.row_bytes == 128 && g.n % 256 == 0 && enough && y_nhwc && y_cpitch * (bf16 ? 2 : 4) >= 128;
         if (legal && (knob == 2 || (knob == 1 && (g.size >= 3 || k_iters_p >= 16)))) {
             a.pair = 1;
@@ -504,6 +507,59 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     if (stages < 2) DNB_FAIL(DNB_ECUDA, "conv: %d bytes of shared memory are too few for the operand ring", max_smem);
     a.stages = stages;
     a.store_row_bytes = srb;
+    // Split-K: a layer with fewer tiles than the GPU has room for and a long K loop (the 19x19 and 38x38 layers at
+    // small batches) cuts every tile's K loop into `splits` ranges that run as separate tiles; see the kernel.
+    // The cost model counts waves of tiles, in units of one K-loop iteration (about 0.3 us): a tile cut into S ranges
+    // costs K/S iterations plus the partial sums' trip through L2: one dump (about 10 units) and, in the CTA that
+    // finishes the tile, S dependent rounds of loads per staged chunk (about 16 units per range; measured on the 19x19
+    // layers of YOLOv3 at one image: 61 us unsplit, 46 us with eight ranges).  Only long K loops on a mostly empty GPU
+    // qualify: batches of one or two images.
+    // DNB_TC_SPLITK: 0 never, N > 1 forces N ranges wherever the variant exists (tests).
+    a.splits = 1;
+    a.split_scratch = nullptr;
+    a.split_counters = nullptr;
+    {
+        const char *e = getenv("DNB_TC_SPLITK");
+        const int knob = e ? atoi(e) : -1;
+        const int k_iters = g.size * g.size * a.c_blocks, cpc = srb / out_es;
+        const bool legal = knob != 0 && !a.halo && !i8 && srb == 128 && a.bn % cpc == 0 && (!residual || a.pair) && k_iters >= 4;
+        if (legal) {
+            const int slots = a.pair ? sm_count() / 2 : sm_count() * a.ctas_per_sm;
+            const int T = a.total_tiles;
+            int best_s = 1;
+            double best = (double)((T + slots - 1) / slots);
+            best *= k_iters;
+            const double alone_units = best;
+            for (int S = 2; S <= 8 && k_iters / S >= 8; ++S) {
+                const double cost = (double)(((long long)T * S + slots - 1) / slots) * ((double)k_iters / S + 10.0 + 16.0 * S);
+                if (cost < best) { best = cost; best_s = S; }
+            }
+            if (best > 0.85 * alone_units) best_s = 1;   // not worth the extra traffic
+            if (knob > 1) best_s = knob < k_iters / 2 ? knob : k_iters / 2;
+            if (best_s > 8) best_s = 8;
+            a.splits = best_s > 1 ? best_s : 1;
+        }
+        if (a.splits > 1) {
+            const int out_tiles = (a.pair ? (ptiles + 1) / 2 * 2 : ptiles) * a.n_tiles;
+            const size_t need = (size_t)out_tiles * a.splits * 128 * a.bn * sizeof(float);
+            if (need > p->split_scratch_bytes) {
+                cudaFree(p->split_scratch);
+                p->split_scratch = nullptr; p->split_scratch_bytes = 0;
+                DNB_CUDA(cudaMalloc(&p->split_scratch, need));
+                p->split_scratch_bytes = need;
+            }
+            if (out_tiles > p->split_counters_n) {
+                cudaFree(p->split_counters);
+                p->split_counters = nullptr; p->split_counters_n = 0;
+                DNB_CUDA(cudaMalloc((void **)&p->split_counters, (size_t)out_tiles * sizeof(int)));
+                DNB_CUDA(cudaMemset(p->split_counters, 0, (size_t)out_tiles * sizeof(int)));
+                p->split_counters_n = out_tiles;
+            }
+            a.split_scratch = p->split_scratch;
+            a.split_counters = p->split_counters;
+            a.total_tiles *= a.splits;
+        }
+    }
     a.g = g;
     if (!p->status) {
         DNB_CUDA(cudaMalloc((void **)&p->status, sizeof(int)));
@@ -616,8 +672,10 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
         ep.residual = res->add->data; ep.res_cpitch = res->add->cpitch; ep.activation2 = res->activation;
         ep.alpha = res->alpha; ep.beta = res->beta;
     }
-    // f32 channels-last results of a TF32 network feed the next tensor-core layer: round them once here
-    ep.round_tf32 = (p->mode == DNB_MODE_TF32 && y_nhwc && y_dtype == DNB_F32 && !y_nchw) ? 1 : 0;
+    // f32 channels-last results of a TF32 network feed the next tensor-core layer: round them once here (the tensor
+    // core would truncate them instead, a bias that adds up over a network's depth).  A copy in Darknet's layout
+    // written by the same launch holds the same rounded values.
+    ep.round_tf32 = (p->mode == DNB_MODE_TF32 && y_nhwc && y_dtype == DNB_F32) ? 1 : 0;
 
     if (p->kernel == K_DIRECT && p->stem_tc && x->dtype == DNB_F32 && y_nhwc && !y_nchw && y_cpitch == g.n) {
         StemTcArgs a;
@@ -772,6 +830,12 @@ extern "C" int dnb_conv_xnor_accumulate(dnb_conv_plan *p, const dnb_tensor *x, i
     return conv_forward_impl(p, x, nullptr, nullptr, acc, (cudaStream_t)stream);
 }
 
+// A launch that gave up on a wait may have left split-K counters part-way: zero them before the plan runs again.
+void conv_plan_reset_after_abort(dnb_conv_plan *p, cudaStream_t s)
+{
+    if (p && p->split_counters) cudaMemsetAsync(p->split_counters, 0, (size_t)p->split_counters_n * sizeof(int), s);
+}
+
 // Device status word of the tensor-core kernel: 0, or the code of the bounded
 // wait that expired (DNB_ETIMEOUT is returned to the caller in that case).
 extern "C" int dnb_conv_plan_check_status(dnb_conv_plan *p)
@@ -781,6 +845,7 @@ extern "C" int dnb_conv_plan_check_status(dnb_conv_plan *p)
     DNB_CUDA(cudaMemcpy(&v, p->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (v) {
         cudaMemset(p->status, 0, sizeof(int));
+        conv_plan_reset_after_abort(p);
         DNB_FAIL(DNB_ETIMEOUT, "conv: a device-side wait expired (code %d: 101 ring slot free, 102 operands landed, 103 accumulator free, 104 accumulator ready, 105 residual tile, 106 shared memory window not 1024-byte aligned)", v);
     }
     return DNB_OK;

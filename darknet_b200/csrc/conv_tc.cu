@@ -61,6 +61,7 @@ struct TcShared {
     uint64_t res_full[MAX_RES_BUFS];   // residual tile landed in its staging buffer
     uint32_t tmem_base;
     int abort_flag;
+    int split_last;                    // split-K: this CTA delivered the last partial sum of the tile it is finishing
 };
 
 enum { WAIT_EMPTY = 101, WAIT_FULL = 102, WAIT_ACC_EMPTY = 103, WAIT_ACC_FULL = 104, WAIT_RESIDUAL = 105, BAD_SMEM_BASE = 106 };
@@ -89,7 +90,13 @@ __device__ __forceinline__ float act_apply(float x, int runtime_act)
 // I8: operands are int8 sign tensors (+1 / -1, 0 in padding channels and, through the TMA zero fill, outside the
 // image), products accumulate exactly in int32 (kind::i8): the xnor convolution on the tensor cores.  The epilogue
 // converts the integer sums to float and continues as for the other kinds (output f32, OUT_BF16 false).
-template <int ACT, int CPC, bool OUT_BF16, int ACT2, bool PAIR, bool I8 = false>
+// SPLIT: the K loop (taps x channel blocks) of every output tile is cut into a.splits consecutive ranges that run as
+// separate tiles, on different CTAs at the same time: for layers with fewer tiles than SMs and a long K loop (small
+// batches of the 19x19 and 38x38 layers).  Every range's CTA writes its raw accumulators to a scratch tensor in
+// global memory (L2), then adds one to the tile's counter; the CTA that finds the counter at splits - 1 is the last
+// one, sums all ranges in their fixed order (so the result does not depend on who came last) and runs the normal
+// epilogue.  Nobody waits for anybody: no spin, no deadlock.  The last CTA resets the counter for the next launch.
+template <int ACT, int CPC, bool OUT_BF16, int ACT2, bool PAIR, bool I8 = false, bool SPLIT = false>
 __global__ void __launch_bounds__(TC_THREADS)
 conv_tc_kernel(const __grid_constant__ TcArgs a)
 {
@@ -169,6 +176,10 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
     // tile past the batch: its loads are zero-filled, its stores are skipped.
     auto pixel_tile = [&](int tile) { return PAIR ? 2 * (tile / n_tiles) + (int)cta_rank : tile / n_tiles; };
     const long long wait_limit = a.wait_limit;
+    const int splits = SPLIT ? a.splits : 1;
+    // tile index -> (output tile, K range); the ranges of one output tile are consecutive tile indices, i.e. they
+    // run on neighbouring CTAs at the same time
+    auto k_begin = [&](int split) { return SPLIT ? (int)((long long)split * k_iters / splits) : 0; };
 
     if (warp == 0) {
         // ---------------- TMA producer: one thread runs the loop, the other lanes wait at the __syncwarp
@@ -211,39 +222,43 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             }
         } else
         for (int tile = first_tile; lane == 0 && tile < total_tiles && ok; tile += grid_stride) {
-            const int nt = tile % n_tiles, pt = pixel_tile(tile);
+            const int base = SPLIT ? tile / splits : tile, split = SPLIT ? tile - base * splits : 0;
+            const int nt = base % n_tiles, pt = pixel_tile(base);
             const int ow0 = (pt % tiles_w) * wt;
             const int oh0 = ((pt / tiles_w) % tiles_h) * ht;
             const int b0 = (pt / ptiles_wh) * bt;
             const int n0 = nt * bn + (PAIR ? (int)cta_rank * (bn >> 1) : 0);   // a pair's CTAs load one half of the filter tile each
-            int kh = 0, kw = 0;
-            for (int tap = 0; tap < taps && ok; ++tap) {
+            const int k0 = k_begin(split), k1 = SPLIT ? k_begin(split + 1) : k_iters;
+            int tap = k0 / c_blocks, cb = k0 - tap * c_blocks;
+            int kh = tap / ksize, kw = tap - kh * ksize;
+            for (int ki = k0; ki < k1; ++ki) {
                 // input row = oh*stride + kh - pad = stride*(oh + q) + parity
                 const int dh = kh - cpad, dw = kw - cpad;
                 int ph = 0, qh = dh, pw = 0, qw = dw;
                 if (cstride == 2) { ph = dh & 1; qh = (dh - ph) >> 1; pw = dw & 1; qw = (dw - pw) >> 1; }
                 const CUtensorMap *mx = maps + (ph * cstride + pw);
-                for (int cb = 0; cb < c_blocks; ++cb) {
-                    ok = mbar_wait_thread(empty0 + 8 * stage, phase ^ 1, abort_flag, status, WAIT_EMPTY, wait_limit);
-                    if (!ok) break;
-                    // wait-expiry test (debug bit 32): the last operand load of this CTA's first tile is never
-                    // requested, so the MMA role's wait for it runs out and the CTA takes the abort path
-                    if (withhold && tile == first_tile && tap == taps - 1 && cb == c_blocks - 1) { ok = false; break; }
-                    const uint32_t bar = full0 + 8 * stage;
-                    const uint32_t sa = ring + stage * stage_bytes;
-                    if (PAIR) {
-                        // one barrier, in the even CTA, counts the bytes of both CTAs' loads of this slot
-                        if (leader) mbar_expect_tx(bar, 2u * tx_bytes);
-                        tma_load_4d_pair(sa, mx, bar, cb * bk, ow0 + qw, oh0 + qh, b0);
-                        tma_load_3d_pair(sa + a_bytes, wmap, bar, cb * bk, n0, tap);
-                    } else {
-                        mbar_expect_tx(bar, tx_bytes);
-                        tma_load_4d(sa, mx, bar, cb * bk, ow0 + qw, oh0 + qh, b0);
-                        tma_load_3d(sa + a_bytes, wmap, bar, cb * bk, n0, tap);
-                    }
-                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                ok = mbar_wait_thread(empty0 + 8 * stage, phase ^ 1, abort_flag, status, WAIT_EMPTY, wait_limit);
+                if (!ok) break;
+                // wait-expiry test (debug bit 32): the last operand load of this CTA's first tile is never
+                // requested, so the MMA role's wait for it runs out and the CTA takes the abort path
+                if (withhold && tile == first_tile && ki == k1 - 1) { ok = false; break; }
+                const uint32_t bar = full0 + 8 * stage;
+                const uint32_t sa = ring + stage * stage_bytes;
+                if (PAIR) {
+                    // one barrier, in the even CTA, counts the bytes of both CTAs' loads of this slot
+                    if (leader) mbar_expect_tx(bar, 2u * tx_bytes);
+                    tma_load_4d_pair(sa, mx, bar, cb * bk, ow0 + qw, oh0 + qh, b0);
+                    tma_load_3d_pair(sa + a_bytes, wmap, bar, cb * bk, n0, tap);
+                } else {
+                    mbar_expect_tx(bar, tx_bytes);
+                    tma_load_4d(sa, mx, bar, cb * bk, ow0 + qw, oh0 + qh, b0);
+                    tma_load_3d(sa + a_bytes, wmap, bar, cb * bk, n0, tap);
                 }
-                if (++kw == ksize) { kw = 0; ++kh; }
+                if (++stage == stages) { stage = 0; phase ^= 1; }
+                if (++cb == c_blocks) {
+                    cb = 0; ++tap;
+                    if (++kw == ksize) { kw = 0; ++kh; }
+                }
             }
         }
         __syncwarp();
@@ -318,7 +333,9 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * acc_stride;
-            for (int ki = 0; ki < k_iters; ++ki) {
+            const int split = SPLIT ? tile % splits : 0;
+            const int kn = SPLIT ? k_begin(split + 1) - k_begin(split) : k_iters;   // this tile's share of the K loop
+            for (int ki = 0; ki < kn; ++ki) {
                 ok = mbar_wait_thread(full0 + 8 * stage, phase, abort_flag, status, WAIT_FULL, wait_limit);
                 if (!ok) break;
                 tc_fence_after();
@@ -405,7 +422,8 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         for (int tile = first_tile; tile < total_tiles; tile += grid_stride, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            const int nt = tile % n_tiles, pt = pixel_tile(tile);
+            const int base = SPLIT ? tile / splits : tile, split = SPLIT ? tile - base * splits : 0;
+            const int nt = base % n_tiles, pt = pixel_tile(base);
             const int ow0 = (pt % tiles_w) * wt, oh0 = ((pt / tiles_w) % tiles_h) * ht, b0 = (pt / ptiles_wh) * bt;
             const int ow = ow0 + wl, oh = oh0 + hl, b = b0 + bl;
             const bool pix_ok = ow < g.out_w && oh < g.out_h && b < g.batch;
@@ -425,6 +443,41 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             if (*abort_flag) break;
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * acc_stride;
+            // split-K: this pixel's row of every range's partial sums, [range][128 rows][bn columns] per output tile
+            // layout [range][group of 4 columns][128 rows][4]: the 32 rows of a warp are 512 contiguous bytes
+            const uint4 *split_rows = nullptr;
+            if (SPLIT) {
+                uint4 *tile_rows = reinterpret_cast<uint4 *>(a.split_scratch) + ((size_t)(pt * n_tiles + nt) * splits) * 32 * bn + m;
+                uint4 *mine = tile_rows + (size_t)split * 32 * bn;
+#pragma unroll 1
+                for (int c0 = 0; c0 < bn; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(t_row + c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) __stcg(mine + (size_t)(c0 / 4 + q) * 128, make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+                }
+                __threadfence();          // the partial sums are visible device-wide before the counter moves
+                epilogue_bar();
+                if (store_thread) {
+                    int *counter = a.split_counters + (pt * n_tiles + nt);
+                    const int last = atomicAdd(counter, 1) == splits - 1;
+                    if (last) *counter = 0;   // every range has arrived: ready for the next launch
+                    sh->split_last = last;
+                }
+                epilogue_bar();
+                const bool last = *reinterpret_cast<volatile int *>(&sh->split_last) != 0;
+                if (!last) {              // another CTA finishes this tile
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (PAIR) mbar_arrive_leader(smem_u32(&sh->acc_empty[acc])); else mbar_arrive(smem_u32(&sh->acc_empty[acc]));
+                    }
+                    continue;
+                }
+                __threadfence();
+                split_rows = tile_rows;
+            }
             // One staged chunk of CPC columns per iteration: CPC/16 TMEM loads in flight, one wait, the
             // arithmetic, the staged row, the store.  The loop is deliberately NOT unrolled: its body has to
             // stay resident in the instruction cache next to the MMA warp's loop.
@@ -441,16 +494,51 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
 #pragma unroll 1
             for (int c0 = (dbg & 8) ? bn : 0; c0 < bn; c0 += CPC) {
                 uint32_t r[CPC];
+                if (SPLIT) {
+                    // the ranges' partial sums, added in their fixed order (bn is a multiple of CPC in this variant); the
+                    // next range's loads are in flight while this one is added
+                    const uint4 *src = split_rows + (size_t)(c0 / 4) * 128;
+                    uint4 v[CPC / 4], w[CPC / 4];
 #pragma unroll
-                for (int u = 0; u < CPC / 16; ++u) {
-                    if (c0 + 16 * u < bn) {
-                        tmem_ld16(t_row + c0 + 16 * u, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * u]));
-                    } else {
+                    for (int q = 0; q < CPC / 4; ++q) v[q] = __ldcg(src + (size_t)q * 128);
+                    if (splits > 1) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) r[16 * u + j] = 0u;
+                        for (int q = 0; q < CPC / 4; ++q) w[q] = __ldcg(src + (size_t)32 * bn + (size_t)q * 128);
                     }
+#pragma unroll 1
+                    for (int sp = 1; sp < splits; ++sp) {
+                        uint4 cur[CPC / 4];
+#pragma unroll
+                        for (int q = 0; q < CPC / 4; ++q) cur[q] = w[q];
+                        if (sp + 1 < splits) {
+#pragma unroll
+                            for (int q = 0; q < CPC / 4; ++q) w[q] = __ldcg(src + (size_t)(sp + 1) * 32 * bn + (size_t)q * 128);
+                        }
+#pragma unroll
+                        for (int q = 0; q < CPC / 4; ++q) {
+                            if (I8) { v[q].x += cur[q].x; v[q].y += cur[q].y; v[q].z += cur[q].z; v[q].w += cur[q].w; }
+                            else {
+                                v[q].x = __float_as_uint(__uint_as_float(v[q].x) + __uint_as_float(cur[q].x));
+                                v[q].y = __float_as_uint(__uint_as_float(v[q].y) + __uint_as_float(cur[q].y));
+                                v[q].z = __float_as_uint(__uint_as_float(v[q].z) + __uint_as_float(cur[q].z));
+                                v[q].w = __float_as_uint(__uint_as_float(v[q].w) + __uint_as_float(cur[q].w));
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < CPC / 4; ++q) { r[4 * q] = v[q].x; r[4 * q + 1] = v[q].y; r[4 * q + 2] = v[q].z; r[4 * q + 3] = v[q].w; }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < CPC / 16; ++u) {
+                        if (c0 + 16 * u < bn) {
+                            tmem_ld16(t_row + c0 + 16 * u, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * u]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) r[16 * u + j] = 0u;
+                        }
+                    }
+                    tmem_ld_wait();
                 }
-                tmem_ld_wait();
                 uint4 res[RES_V];
                 if (res_direct) {
 #pragma unroll
@@ -685,14 +773,27 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
     const int cpc = a.store_row_bytes / (obf ? 2 : 4);
     if (cpc != 16 && cpc != 32 && cpc != 64) DNB_FAIL(DNB_EINVAL, "conv_tc: staged row of %d bytes", a.store_row_bytes);
     if (a.pair && !((!obf && cpc == 32) || (obf && cpc == 64))) DNB_FAIL(DNB_EINVAL, "conv_tc: pair mode needs 128-byte staged rows");
+    if (a.splits > 1 && (!((!obf && cpc == 32) || (obf && cpc == 64)) || a.bn % cpc || a.halo || !a.split_scratch || !a.split_counters))
+        DNB_FAIL(DNB_EINVAL, "conv_tc: split-K needs 128-byte staged rows, whole chunks per tile, no halo mode, and its scratch");
     // one instantiation per (activation, columns per staged chunk, output type, fused shortcut, pair mode, operand kind)
+    // split-K variants exist for 128-byte staged rows, f32 / bf16 operands; with a fused residual only as pairs (the
+    // single-CTA kernel streams residual tiles ahead of the epilogue, which a tile finished elsewhere would derail)
 #define DNB_TC_GO(ACT, CPC, OBF, ACT2, I8)                                                          \
     do {                                                                                            \
-        if (a.pair) DNB_TRY(launch_one(conv_tc_kernel<ACT, CPC, OBF, ACT2, true, I8>, a, smem, s)); \
+        if (a.splits > 1) {                                                                         \
+            if (I8) DNB_FAIL(DNB_EINVAL, "conv_tc: no split-K variant of the int8 kind");            \
+            if (a.pair) DNB_TRY(launch_one(conv_tc_kernel<ACT, CPC, OBF, ACT2, true, false, !I8>, a, smem, s)); \
+            else if (ACT2 != ACT2_NONE) DNB_FAIL(DNB_EINVAL, "conv_tc: split-K with a fused residual runs as CTA pairs only"); \
+            else DNB_TRY(launch_one(conv_tc_kernel<ACT, CPC, OBF, ACT2_NONE, false, false, !I8>, a, smem, s)); \
+        } else if (a.pair) DNB_TRY(launch_one(conv_tc_kernel<ACT, CPC, OBF, ACT2, true, I8>, a, smem, s)); \
         else DNB_TRY(launch_one(conv_tc_kernel<ACT, CPC, OBF, ACT2, false, I8>, a, smem, s));       \
     } while (0)
     // pair-mode kernels exist for 128-byte staged rows only, so the narrower variants are instantiated without it
-#define DNB_TC_GO_SINGLE(ACT, CPC, OBF, ACT2, I8) DNB_TRY(launch_one(conv_tc_kernel<ACT, CPC, OBF, ACT2, false, I8>, a, smem, s))
+#define DNB_TC_GO_SINGLE(ACT, CPC, OBF, ACT2, I8)                                                   \
+    do {                                                                                            \
+        if (a.splits > 1) DNB_FAIL(DNB_EINVAL, "conv_tc: no split-K variant for this staged row width"); \
+        DNB_TRY(launch_one(conv_tc_kernel<ACT, CPC, OBF, ACT2, false, I8>, a, smem, s));            \
+    } while (0)
 #define DNB_TC_LAUNCH_ACT(ACT, ACT2)                                            \
     do {                                                                        \
         if (!obf && cpc == 32) DNB_TC_GO(ACT, 32, false, ACT2, false);          \

@@ -852,6 +852,7 @@ extern "C" int dnb_network_collect(dnb_network *net, float **output)
         const int code = net->status_host[slot];
         net->status_host[slot] = 0;
         cudaMemsetAsync(net->status_dev + slot, 0, sizeof(int), net->stream);   // before the slot's next step, which follows on this stream
+        for (Layer &L : net->layers) conv_plan_reset_after_abort(L.plan, net->stream);
         char text[512];
         snprintf(text, sizeof(text), kTimeoutText, code);
         DNB_FAIL(DNB_ETIMEOUT, "network_predict: %s", text);
@@ -961,6 +962,7 @@ extern "C" int dnb_network_check_status(dnb_network *net)
     DNB_CUDA(cudaMemcpy(v, net->status_dev, sizeof(v), cudaMemcpyDeviceToHost));
     if (v[0] || v[1]) {
         DNB_CUDA(cudaMemset(net->status_dev, 0, sizeof(v)));
+        for (Layer &L : net->layers) conv_plan_reset_after_abort(L.plan);
         char text[512];
         snprintf(text, sizeof(text), kTimeoutText, v[0] ? v[0] : v[1]);
         DNB_FAIL(DNB_ETIMEOUT, "network_forward: %s", text);

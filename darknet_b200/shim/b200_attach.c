@@ -43,6 +43,9 @@ typedef struct attached {
     dnb_network *whole;         /* b200_attach_network: this library's own network object, or NULL */
     float **saved_delta;        /* b200_attach_network: the delta_gpu pointers taken out of the layers */
     char *pinned;               /* per layer: l.output was page-locked here (and is released by b200_detach) */
+    void **shadow;              /* per layer: channels-last copy of a replaced convolution's output that the next
+                                 * replaced convolution reads instead of transposing l.output_gpu again, or NULL */
+    int mode;
     struct attached *next;
 } attached;
 
@@ -70,13 +73,29 @@ static dnb_tensor nchw(float *gpu, int n, int c, int h, int w)
     return t;
 }
 
+static dnb_tensor nhwc(void *gpu, int mode, int n, int c, int h, int w)
+{
+    dnb_tensor t;
+    t.data = gpu; t.layout = DNB_NHWC; t.dtype = mode == DNB_MODE_BF16 ? DNB_BF16 : DNB_F32;
+    t.n = n; t.c = c; t.h = h; t.w = w; t.cpitch = (c + 7) / 8 * 8;
+    return t;
+}
+
+/* Darknet's tensors are NCHW, the tensor-core kernel reads channels-last: a replaced convolution transposes its
+ * input into a scratch of its plan first.  Where the layer before it is a replaced convolution too, that layer has
+ * written a channels-last copy of its output beside l.output_gpu (the second output of dnb_conv_forward), and this
+ * one reads the copy; l.output_gpu is still written for every other reader. */
 static void forward_convolutional_layer_b200(layer l, network net)
 {
     attached *a = find_attached(net.layers);
-    if (!a || net.index < 0 || net.index >= a->n || !a->plans[net.index]) error("darknet_b200: convolution called on a network that is not attached");
+    const int i = net.index;
+    if (!a || i < 0 || i >= a->n || !a->plans[i]) error("darknet_b200: convolution called on a network that is not attached");
     dnb_tensor x = nchw(net.input_gpu, l.batch, l.c, l.h, l.w);
+    if (i > 0 && a->shadow[i - 1] && net.input_gpu == net.layers[i - 1].output_gpu)
+        x = nhwc(a->shadow[i - 1], a->mode, l.batch, l.c, l.h, l.w);
     dnb_tensor y = nchw(l.output_gpu, l.batch, l.out_c, l.out_h, l.out_w);
-    if (dnb_conv_forward(a->plans[net.index], &x, &y, NULL, NULL)) fail("convolution");
+    dnb_tensor y2 = nhwc(a->shadow[i], a->mode, l.batch, l.out_c, l.out_h, l.out_w);
+    if (dnb_conv_forward(a->plans[i], &x, &y, a->shadow[i] ? &y2 : NULL, NULL)) fail("convolution");
 }
 
 static void forward_maxpool_layer_b200(layer l, network net)
@@ -164,9 +183,11 @@ static void release(attached *a, network *net)
         if (net && a->original[i]) net->layers[i].forward_gpu = a->original[i];
         if (net && a->saved_delta && a->saved_delta[i]) net->layers[i].delta_gpu = a->saved_delta[i];
         if (a->plans[i]) dnb_conv_plan_destroy(a->plans[i]);
+        if (a->shadow && a->shadow[i]) cudaFree(a->shadow[i]);
     }
     if (a->whole) dnb_free_network(a->whole);
     free(a->pinned);
+    free(a->shadow);
     free(a->saved_delta);
     free(a->plans);
     free(a->original);
@@ -181,6 +202,8 @@ int b200_attach(network *net, int mode)
     a->n = net->n;
     a->plans = calloc((size_t)net->n, sizeof *a->plans);
     a->original = calloc((size_t)net->n, sizeof *a->original);
+    a->shadow = calloc((size_t)net->n, sizeof *a->shadow);
+    a->mode = mode;
     int count = 0;
     for (int i = 0; i < net->n; ++i) {
         layer *l = &net->layers[i];
@@ -214,6 +237,20 @@ int b200_attach(network *net, int mode)
             a->original[i] = l->forward_gpu;
             l->forward_gpu = repl;
             ++count;
+        }
+    }
+    /* channels-last copies between consecutive replaced convolutions (tensor-core plans, whose kernels read and write
+     * that layout); B200_ATTACH_SHADOWS=0 in the environment keeps every boundary in Darknet's layout only */
+    {
+        const char *e = getenv("B200_ATTACH_SHADOWS");
+        for (int i = 0; i + 1 < net->n && !(e && atoi(e) == 0); ++i) {
+            const layer *l = &net->layers[i];
+            if (!a->plans[i] || !a->plans[i + 1]) continue;
+            const char *k0 = dnb_conv_plan_kernel(a->plans[i]), *k1 = dnb_conv_plan_kernel(a->plans[i + 1]);
+            if (strncmp(k0, "tc_", 3) || strncmp(k1, "tc_", 3)) continue;
+            const size_t bytes = (size_t)l->batch * l->out_h * l->out_w * ((l->out_c + 7) / 8 * 8) * (mode == DNB_MODE_BF16 ? 2 : 4);
+            if (cudaMalloc(&a->shadow[i], bytes) != cudaSuccess) { cudaGetLastError(); a->shadow[i] = NULL; break; }   /* out of memory: the rest stay as they were */
+            if (cudaMemset(a->shadow[i], 0, bytes) != cudaSuccess) cudaGetLastError();                                /* padding channels are zero */
         }
     }
     /* inference only from here to b200_detach: forward_network_gpu zero-fills every layer's delta before calling
@@ -339,6 +376,8 @@ int b200_attach_network(network *net, int mode)
     a->plans = calloc(count, sizeof *a->plans);
     a->original = calloc(count, sizeof *a->original);
     a->saved_delta = calloc(count, sizeof *a->saved_delta);
+    a->shadow = calloc(count, sizeof *a->shadow);
+    a->mode = mode;
     a->whole = whole;
     for (int i = 0; i < net->n; ++i) {
         layer *l = &net->layers[i];

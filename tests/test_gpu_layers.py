@@ -433,6 +433,7 @@ def test_conv_tc_cta_pairs(name, mode, tol, monkeypatch):
     each): against the checker, against the single-CTA kernel, and with Darknet's layout written beside."""
     case = conv_case(260, **PAIR_CASES[name])
     want = oracle_conv(case)
+    monkeypatch.setenv("DNB_TC_SPLITK", "0")   # the pair kernel by itself; split-K has its own tests below
     monkeypatch.setenv("DNB_TC_PAIR", "1")
     plan, got, _ = run_conv(case, mode, "nhwc", "nhwc")
     assert "pair=1" in plan.describe(), plan.describe()
@@ -459,6 +460,7 @@ def test_conv_tc_cta_pairs_1x1_when_forced(monkeypatch):
 def test_conv_tc_cta_pairs_with_fused_shortcut(mode, tol, monkeypatch):
     import ctypes as C
     monkeypatch.setenv("DNB_TC_PAIR", "1")
+    monkeypatch.setenv("DNB_TC_SPLITK", "0")
     case = conv_case(262, b=8, c=128, h=38, w=38, n=512, size=3)
     x, w = case["x"], case["w"]
     b, c, h, wd = x.shape
@@ -517,6 +519,88 @@ def test_conv_with_fused_yolo_head(shape, mode, tol):
     with pytest.raises(dn.DarknetB200Error) as e:
         dn.check(dn.lib().dnb_conv_yolo_forward(plan.handle, C.byref(xd), C.byref(yd), anchors + 1, classes, None))
     assert e.value.status == dn.EINVAL
+
+
+SPLIT_CASES = {
+    # (case, forced ranges or None for the plan's own choice, expects pair mode)
+    "single_19x19_c256_n128_forced3": (dict(b=2, c=256, h=19, w=19, n=128, size=3), "3", False),
+    "single_1x1_c512_n64_forced2": (dict(b=1, c=512, h=13, w=13, n=64, size=1), "2", False),
+    "single_s2_c128_n128_forced8": (dict(b=1, c=128, h=38, w=38, n=128, size=3, stride=2), "8", False),
+    "pair_19x19_c1024_n512_batch4_auto": (dict(b=4, c=1024, h=19, w=19, n=512, size=3), None, True),       # YOLOv3's 19x19 shape at 8 images per GPU
+    "pair_19x19_c1024_n1024_batch1_auto": (dict(b=1, c=1024, h=19, w=19, n=1024, size=3), None, True),    # one image of YOLOv3's last stage: 8 pair tiles
+    "pair_19x19_c512_n256_batch3_forced5": (dict(b=3, c=512, h=19, w=19, n=256, size=3, act="linear", bn=False), "5", True),  # odd pixel tiles: a phantom tile delivers ranges too
+}
+
+
+@pytest.mark.parametrize("name", list(SPLIT_CASES))
+@pytest.mark.parametrize("mode,tol", [(dn.MODE_TF32, TOL_TF32), (dn.MODE_BF16, TOL_BF16)])
+def test_conv_tc_split_k(name, mode, tol, monkeypatch):
+    """Split-K: every tile's K loop cut into ranges that run on different CTAs and meet through L2.  Against the
+    checker, against the unsplit kernel, and three launches in a row (the counters reset themselves)."""
+    shape, forced, pair = SPLIT_CASES[name]
+    case = conv_case(280, **shape)
+    want = oracle_conv(case)
+    if forced:
+        monkeypatch.setenv("DNB_TC_SPLITK", forced)
+    else:
+        monkeypatch.delenv("DNB_TC_SPLITK", raising=False)
+    x, w = case["x"], case["w"]
+    b, c, h, wd = x.shape
+    n, size = w.shape[0], w.shape[2]
+    plan = dn.ConvPlan(b, c, h, wd, n, size, case["stride"], case["pad"], 1, case["scales"] is not None, case["act"], False, mode)
+    plan.set_params(w, case["biases"], case["scales"], case["mean"], case["var"])
+    store = torch.bfloat16 if mode == dn.MODE_BF16 else torch.float32
+    xt, xd = dev_nhwc(x, store)
+    yt, yd = empty_nhwc(b, n, plan.out_h, plan.out_w, store)
+    outs = []
+    for _ in range(3):
+        yt.zero_()
+        plan.forward(xd, yd)
+        torch.cuda.synchronize()
+        plan.check_status()
+        outs.append(host_from_nhwc(yt, n))
+    d = plan.describe()
+    assert f"pair={int(pair)}" in d, d
+    splits = int(d.split("splits=")[1].split()[0])
+    assert splits > 1 and (not forced or splits == int(forced)), d
+    parity(outs[0], want, tol, name)
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])   # fixed order of the ranges: bit-reproducible
+    assert padding_is_zero(yt, n)
+    monkeypatch.setenv("DNB_TC_SPLITK", "0")
+    plan0, whole, _ = run_conv(case, mode, "nhwc", "nhwc")
+    assert "splits=1" in plan0.describe()
+    parity(outs[0], whole, (2e-3 if mode == dn.MODE_TF32 else 1e-2), "split against unsplit")
+
+
+@pytest.mark.parametrize("mode,tol", [(dn.MODE_TF32, TOL_TF32), (dn.MODE_BF16, TOL_BF16)])
+def test_conv_tc_split_k_with_fused_shortcut(mode, tol, monkeypatch):
+    """A residual block of YOLOv3's 19x19 stage at 2 images: CTA pairs, split-K chosen by the plan, residual added by
+    the CTA that finishes each tile."""
+    import ctypes as C
+    monkeypatch.delenv("DNB_TC_SPLITK", raising=False)
+    case = conv_case(281, b=2, c=1024, h=19, w=19, n=1024, size=3)
+    x, w = case["x"], case["w"]
+    b, c, h, wd = x.shape
+    n = w.shape[0]
+    add = rng(282).standard_normal((b, n, h, wd), dtype=np.float32)
+    store = torch.bfloat16 if mode == dn.MODE_BF16 else torch.float32
+    if mode == dn.MODE_BF16:
+        add = bf16_round(add)
+    want = orc.shortcut_forward(oracle_conv(case), add, 1.0, 1.0, "linear")
+    plan = dn.ConvPlan(b, c, h, wd, n, 3, 1, 1, 1, True, case["act"], False, mode)
+    plan.set_params(w, case["biases"], case["scales"], case["mean"], case["var"])
+    xt, xd = dev_nhwc(x, store)
+    at, ad = dev_nhwc(add, store)
+    yt, yd = empty_nhwc(b, n, h, wd, store)
+    for _ in range(2):
+        yt.zero_()
+        dn.check(dn.lib().dnb_conv_shortcut_forward(plan.handle, C.byref(xd), C.byref(ad), C.byref(yd), 1.0, 1.0, dn.ACTIVATIONS["linear"],
+                                                    C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        torch.cuda.synchronize()
+        plan.check_status()
+        d = plan.describe()
+        assert "pair=1" in d and "splits=1" not in d, d
+        parity(host_from_nhwc(yt, n), want, tol, "split-K pair with fused shortcut")
 
 
 def test_conv_tc_all_ones_counts_taps():
