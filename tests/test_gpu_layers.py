@@ -603,6 +603,38 @@ def test_conv_tc_split_k_with_fused_shortcut(mode, tol, monkeypatch):
         parity(host_from_nhwc(yt, n), want, tol, "split-K pair with fused shortcut")
 
 
+@pytest.mark.parametrize("act", list(dn.ACTIVATIONS))
+@pytest.mark.parametrize("kernel", ["tc_tf32", "tc_bf16", "direct_fp32", "shortcut"])
+def test_every_activation(act, kernel):
+    """All fourteen activations of src/activations.h:35-86 through every epilogue that applies one: the tensor-core
+    convolution (compiled in: linear, leaky; the others through the run-time switch), the CUDA-core convolution and
+    the shortcut kernel.  `stair` is a step function: values a rounding error away from a step land on the other side
+    of it, so it is compared element by element with a small share of misses allowed."""
+    mode, tol = {"tc_tf32": (dn.MODE_TF32, TOL_TF32), "tc_bf16": (dn.MODE_BF16, TOL_BF16), "direct_fp32": (dn.MODE_FP32, TOL_FP32),
+                 "shortcut": (dn.MODE_FP32, TOL_FP32)}[kernel]
+    if kernel == "shortcut":
+        g = rng(301)
+        x = g.standard_normal((2, 24, 9, 10), dtype=np.float32) * 2
+        add = g.standard_normal((2, 24, 9, 10), dtype=np.float32) * 2
+        want = orc.shortcut_forward(x, add, 1.0, 1.0, act)
+        xt, xd = dev_nhwc(x)
+        at, ad = dev_nhwc(add)
+        yt, yd = empty_nhwc(2, 24, 9, 10)
+        dn.shortcut(xd, ad, yd, 1.0, 1.0, act)
+        torch.cuda.synchronize()
+        got = host_from_nhwc(yt, 24)
+    else:
+        case = conv_case(300, b=2, c=16, h=12, w=12, n=24, size=3, act=act)
+        plan, got, _ = run_conv(case, mode, "nhwc" if kernel.startswith("tc_") else "nchw", "nhwc" if kernel.startswith("tc_") else "nchw")
+        assert plan.kernel == kernel
+        want = oracle_conv(case)
+    if act == "stair":
+        close = np.abs(got - want) <= tol * np.abs(want).max()
+        assert close.mean() > 0.99, f"{kernel} stair: {100 * (1 - close.mean()):.2f} % of the values on the other side of a step"
+    else:
+        parity(got, want, tol, f"{kernel} activation {act}")
+
+
 def test_conv_tc_all_ones_counts_taps():
     # analytic known answer: ones everywhere -> in-image taps x channels, exact in TF32 and BF16
     C, H, W, N = 16, 9, 10, 16
