@@ -418,20 +418,27 @@ def roofline_of(net, cfg: str, per_gpu: int, mean_ms, mode: str, workload: str, 
             # int8 sign tensors through the tensor cores (kind::i8): the integer sums cost a few per cent of the int8 tensor
             # rate; what bounds the layer is the fp32 activations around it.  Algorithmic bytes per layer: fp32 input read
             # once by the sign pass, int8 signs written and read once, fp32 output written, the int8 weights once.
+            # Where one xnor layer feeds the next, the first writes the second's signs from its epilogue (1 byte per output
+            # more) and the second reads only those.
             bytes_ = 0.0
+            passes = 0
             for i in np.nonzero(xn)[0]:
                 c, h, w = net.layer_shape(int(i))
                 sh = shapes[int(i)]
                 stride = int(sections[int(i)][1].get("stride", 1))
                 in_e = float(per_gpu) * sh.c * (h * stride) * (w * stride)
-                bytes_ += 4.0 * in_e + 2.0 * in_e + 4.0 * per_gpu * sh.n * h * w + sh.n * sh.c * sh.size * sh.size
+                out_e = float(per_gpu) * sh.n * h * w
+                desc = net.layer_describe(int(i))
+                given, gives = "signs_in=1" in desc, "signs_out=1" in desc
+                passes += 0 if given else 1
+                bytes_ += (1.0 * in_e if given else 4.0 * in_e + 2.0 * in_e) + (5.0 if gives else 4.0) * out_e + sh.n * sh.c * sh.size * sh.size
             gbs = bytes_ / (x_ms / 1000.0) / 1e9
             ops = 2.0 * 32.0 * words   # multiply-adds of +-1 values, two operations each
             roofline = {"kernel": "conv_tc_kernel (int8 kind) + pack_sign_i8_kernel", "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                        "frac": gbs / peaks["hbm_gbs"], "traffic": None, "launches_per_step": 2 * int(xn.sum()), "ms_per_step": x_ms,
+                        "frac": gbs / peaks["hbm_gbs"], "traffic": None, "launches_per_step": int(xn.sum()) + passes, "ms_per_step": x_ms,
                         "share_of_step": x_ms / float(mean_ms.sum()), "integer_tops": ops / (x_ms / 1000.0) / 1e12,
                         "peak_source": f"{peaks['source']}: STREAM-style copy",
-                        "what": "xnor layers as int8 sign tensors on tcgen05 (exact int32 sums); bytes = fp32 input + int8 signs written and read + fp32 output + int8 weights"}
+                        "what": "xnor layers as int8 sign tensors on tcgen05 (exact int32 sums); bytes = fp32 output + int8 weights + either the fp32 input and its int8 signs written and read (sign pass) or the int8 signs the previous xnor layer wrote (1 byte written there, 1 read here)"}
         else:
             roofline = {"kernel": "conv_xnor_kernel", "bound": "popc issue", "achieved": rate, "unit": "T word-popcounts/s", "peak": None, "frac": None,
                         "binary_tops": rate * 64.0, "traffic": None, "launches_per_step": int(xn.sum()), "ms_per_step": x_ms,

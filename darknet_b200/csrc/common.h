@@ -61,7 +61,8 @@ inline size_t tensor_elems(const dnb_tensor *t)
 }
 
 // ---- kernels_mem.cu
-int launch_maxpool(const dnb_tensor *x, const dnb_tensor *y, int size, int stride, int padding, cudaStream_t s);
+// signs: optional int8 channels-last tensor of pitch spitch that receives the output's signs (f32 channels-last tensors)
+int launch_maxpool(const dnb_tensor *x, const dnb_tensor *y, int size, int stride, int padding, cudaStream_t s, int8_t *signs = nullptr, int spitch = 0);
 int launch_upsample(const dnb_tensor *x, const dnb_tensor *y, int stride, float scale, cudaStream_t s);
 int launch_shortcut(const dnb_tensor *x, const dnb_tensor *add, const dnb_tensor *y, float alpha, float beta,
                     int activation, cudaStream_t s);

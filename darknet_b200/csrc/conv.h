@@ -51,6 +51,7 @@ struct alignas(64) TcArgs {
     CUtensorMap tmw;      // weights [taps][n_pad][c_pad], channels innermost
     CUtensorMap tmy;      // NHWC output, written by TMA stores from the staging rows
     CUtensorMap tmr;      // fused residual (same extents and box as tmy), loaded tile by tile in the epilogue
+    CUtensorMap tms;      // sign output (int8 channels-last, the next xnor layer's operand): 32-channel boxes of the same pixels as tmy
     int is_bf16;          // operand kind: 0 kind::tf32 on f32 operands, 1 kind::f16 on bf16 operands, 2 kind::i8 on int8 sign tensors (xnor)
     int row_bytes;        // bytes of channels per pipeline stage row: 128, 64 or 32 (= swizzle span)
     int bk;               // channels per stage row (row_bytes / element size)
@@ -84,6 +85,8 @@ struct alignas(64) TcArgs {
     float *y_nchw;
     int *status;          // device word: 0, or the code of the wait that expired
     // split-K (layers with fewer tiles than SMs and a long K loop): total_tiles counts (output tile, K range) pairs
+    void *sign_out;       // int8 kind: also write the output's signs here ([b][h][w][sign_cpitch] bytes), or null
+    int sign_cpitch;
     int splits;           // K ranges per output tile; 1 = off
     void *split_scratch;  // [output tile][range][128 rows][bn] raw accumulators (f32, or int32 of the int8 kind)
     int *split_counters;  // [output tile] ranges delivered so far; zero between launches
@@ -160,6 +163,11 @@ struct dnb_conv_plan {
     const void *tc_res_ptr;  // fused residual the load map was built for (NULL: none)
     int tc_res_cpitch;
     int tc_y_cpitch, tc_y_dtype;
+    // xnor layers in a row (tensor-core kind): the producer's epilogue writes the consumer's int8 operand
+    dnb_conv_plan *sign_consumer;   // this plan also fills that plan's x_i8 (set by the network object), or null
+    bool signs_given;               // this plan's x_i8 is filled by the layer before it: no sign pass of its own
+    const void *signs_of;           // ... as long as the input it is given is this tensor
+    void *tc_sign_out;              // the sign output the cached launch block was built for
     void *split_scratch;     // split-K partial sums and counters of the cached launch block (owned by the plan)
     size_t split_scratch_bytes;
     int *split_counters;
@@ -172,3 +180,7 @@ struct dnb_conv_plan {
 
 // zero the split-K counters a timed-out launch may have left part-way (on `s`; a null plan or one without counters: nothing)
 void conv_plan_reset_after_abort(dnb_conv_plan *p, cudaStream_t s = nullptr);
+
+// producers of a tensor-core xnor layer's int8 operand (see conv_plan.cu)
+int8_t *conv_plan_expect_signs(dnb_conv_plan *consumer, const void *tensor, int batch, int c, int h, int w);
+bool conv_plan_link_signs(dnb_conv_plan *producer, dnb_conv_plan *consumer, const void *tensor);

@@ -89,8 +89,8 @@ extern "C" int dnb_conv_plan_describe(const dnb_conv_plan *p, char *buf, int len
     if (!p || !buf || len < 1) DNB_FAIL(DNB_EINVAL, "conv describe: bad argument");
     const TcArgs &a = p->tc;
     if ((p->kernel == K_TC_TF32 || p->kernel == K_TC_BF16 || (p->kernel == K_XNOR && p->xnor_tc)) && p->tc_x_ptr)
-        snprintf(buf, len, "%s pair=%d halo=%d bn=%d tile=%dx%dx%d tiles=%d stages=%d ctas_per_sm=%d srb=%d splits=%d", kKernelNames[p->kernel], a.pair, a.halo,
-                 a.bn, a.wt, a.ht, a.bt, a.total_tiles, a.stages, a.ctas_per_sm, a.store_row_bytes, a.splits);
+        snprintf(buf, len, "%s pair=%d halo=%d bn=%d tile=%dx%dx%d tiles=%d stages=%d ctas_per_sm=%d srb=%d splits=%d signs_in=%d signs_out=%d", kKernelNames[p->kernel], a.pair, a.halo,
+                 a.bn, a.wt, a.ht, a.bt, a.total_tiles, a.stages, a.ctas_per_sm, a.store_row_bytes, a.splits, p->signs_given ? 1 : 0, a.sign_out ? 1 : 0);
     else
         snprintf(buf, len, "%s", dnb_conv_plan_kernel(p));
     return DNB_OK;
@@ -321,7 +321,7 @@ static void pick_pixel_tile(const ConvGeom &g, bool nchw_out, int *wt, int *ht, 
 }
 
 static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, int y_dtype, int y_cpitch,
-                         const void *residual, int res_cpitch, bool nchw_out)
+                         const void *residual, int res_cpitch, bool nchw_out, void *sign_out = nullptr, int sign_cpitch = 0)
 {
     TcArgs &a = p->tc;
     // A 1x1 convolution (stride 1, no padding) does not care which pixels are neighbours: with Darknet's layout among
@@ -432,9 +432,10 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     // at least four ring stages
     const int out_es = bf16 ? 2 : 4;   // channels-last output uses the plan's storage type
     const int pitch_bytes = y_nhwc ? y_cpitch * out_es : 32;
-    const int min_srb = 16 * out_es;  // a staged row holds at least one 16-column piece of the accumulator
+    const int min_srb = sign_out ? 128 : 16 * out_es;  // a staged row holds at least one 16-column piece of the accumulator; the sign output is built for 32 columns per chunk
     int srb = pitch_bytes >= 128 ? 128 : (pitch_bytes >= 64 ? 64 : 32);
     if (srb < min_srb) srb = min_srb;  // the box may be wider than a narrow tensor: the TMA unit clips it
+    if (sign_out && (pitch_bytes < 128 || !i8)) DNB_FAIL(DNB_EINVAL, "conv: the sign output needs an int8-kind plan with at least 32 output channels");
     if (const char *e = getenv("DNB_TC_SRB")) {   // tuning knob: widest staged row to try (128, 64 or 32)
         const int v = atoi(e);
         if ((v == 128 || v == 64 || v == 32) && v >= min_srb && v < srb && !a.pair) srb = v;
@@ -447,6 +448,9 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     // twice the warps hide the per-tile hand-offs that dominate layers with few K iterations.
     a.ctas_per_sm = 1;
     a.stage_bufs = (residual && !a.pair) ? 4 : 2;   // a pair reads the residual with plain loads: nothing lands in the staging buffers
+    if (sign_out) a.stage_bufs = 3;   // the third buffer holds the staged signs
+    a.sign_out = sign_out;
+    a.sign_cpitch = sign_cpitch;
     a.debug = (getenv("DNB_TC_DEBUG") ? atoi(getenv("DNB_TC_DEBUG")) : 0) | p->debug_bits;
     a.wait_limit = p->wait_limit > 0 ? p->wait_limit : DEFAULT_WAIT_CYCLES;
     int stages = 0;
@@ -605,6 +609,13 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
             DNB_TRY(encode_tensor_map(&a.tmr, bf16, 4, const_cast<void *>(residual), rdims, rstrides, box, srb));
         }
     }
+    if (sign_out) {
+        uint64_t dims[4] = {(uint64_t)sign_cpitch, (uint64_t)g.out_w, (uint64_t)g.out_h, (uint64_t)g.batch};
+        uint64_t strides[3] = {(uint64_t)sign_cpitch, (uint64_t)sign_cpitch * g.out_w, (uint64_t)sign_cpitch * g.out_w * g.out_h};
+        uint32_t box[4] = {32u, (uint32_t)a.wt, (uint32_t)a.ht, (uint32_t)a.bt};
+        DNB_TRY(encode_tensor_map(&a.tms, 2, 4, sign_out, dims, strides, box, 32));
+    }
+    p->tc_sign_out = sign_out;
     p->tc_x_ptr = x->data;
     p->tc_x_cpitch = x->cpitch;
     p->tc_y_ptr = y_nhwc;
@@ -614,6 +625,40 @@ static int build_tc_args(dnb_conv_plan *p, const dnb_tensor *x, void *y_nhwc, in
     p->tc_res_cpitch = res_cpitch;
     p->tc_nchw_out = nchw_out ? 1 : 0;
     return DNB_OK;
+}
+
+// A tensor-core xnor layer reads its input as int8 signs.  Where the layer before it can write them as it writes its
+// own f32 output (another tensor-core xnor layer, from its epilogue; a maxpool layer), the sign pass over the f32 tensor
+// disappears.  conv_plan_expect_signs prepares the consumer (its operand buffer is allocated and returned; it skips its
+// own pass whenever it is given `tensor`, the channels-last tensor that carries the producer's output) and
+// conv_plan_link_signs also tells a producing xnor plan.  DNB_XNOR_SIGNS=0: never.
+int8_t *conv_plan_expect_signs(dnb_conv_plan *consumer, const void *tensor, int batch, int c, int h, int w)
+{
+    const char *e = getenv("DNB_XNOR_SIGNS");
+    if (e && atoi(e) == 0) return nullptr;
+    if (!consumer || !tensor || consumer->kernel != K_XNOR || !consumer->xnor_tc) return nullptr;
+    const ConvGeom &b = consumer->g;
+    if (c != b.c || h != b.h || w != b.w || batch != b.batch || c % 32 || consumer->c_pad_i8 != c) return nullptr;
+    const size_t need = (size_t)b.batch * b.h * b.w * consumer->c_pad_i8;
+    if (need > consumer->x_i8_bytes) {
+        cudaFree(consumer->x_i8);
+        consumer->x_i8 = nullptr; consumer->x_i8_bytes = 0;
+        if (cudaMalloc((void **)&consumer->x_i8, need) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        consumer->x_i8_bytes = need;
+        consumer->tc_x_ptr = nullptr;
+    }
+    consumer->signs_given = true;
+    consumer->signs_of = tensor;
+    return consumer->x_i8;
+}
+
+bool conv_plan_link_signs(dnb_conv_plan *producer, dnb_conv_plan *consumer, const void *tensor)
+{
+    if (!producer || producer->kernel != K_XNOR || !producer->xnor_tc) return false;
+    const ConvGeom &a = producer->g;
+    if (!conv_plan_expect_signs(consumer, tensor, a.batch, a.n, a.out_h, a.out_w)) return false;
+    producer->sign_consumer = consumer;
+    return true;
 }
 
 // ------------------------------------------------------------------ forward
@@ -715,13 +760,19 @@ static int conv_forward_impl(dnb_conv_plan *p, const dnb_tensor *x, const dnb_te
             p->x_i8_bytes = need;
             p->tc_x_ptr = nullptr;
         }
-        DNB_TRY(launch_pack_sign_i8(x, p->x_i8, p->c_pad_i8, s));
+        // (the xnor layer before this one, if the network linked the two, has written the signs from its epilogue)
+        const bool given = p->signs_given && x->layout == DNB_NHWC && x->data == p->signs_of;
+        if (!given) DNB_TRY(launch_pack_sign_i8(x, p->x_i8, p->c_pad_i8, s));
         dnb_tensor xin{p->x_i8, DNB_NHWC, DNB_F32, g.batch, g.c, g.h, g.w, p->c_pad_i8};   // dtype unused: the plan's kind says int8
         if (y_nhwc && y_dtype != DNB_F32) DNB_FAIL(DNB_EINVAL, "conv: an xnor plan writes channels-last output as f32");
         float *nchw = acc_out ? reinterpret_cast<float *>(acc_out) : y_nchw;
         void *nhwc = acc_out ? nullptr : y_nhwc;
-        if (p->tc_x_ptr != xin.data || p->tc_y_ptr != nhwc || p->tc_y_cpitch != (nhwc ? y_cpitch : 0) || !p->status || p->tc_nchw_out != (nchw ? 1 : 0))
-            DNB_TRY(build_tc_args(p, &xin, nhwc, DNB_F32, nhwc ? y_cpitch : 0, nullptr, 0, nchw != nullptr));
+        // signs for the next xnor layer, when this launch writes the very tensor that layer reads
+        dnb_conv_plan *next = p->sign_consumer;
+        void *sign_out = (next && nhwc && nhwc == next->signs_of && next->x_i8) ? next->x_i8 : nullptr;
+        if (p->tc_x_ptr != xin.data || p->tc_y_ptr != nhwc || p->tc_y_cpitch != (nhwc ? y_cpitch : 0) || !p->status || p->tc_nchw_out != (nchw ? 1 : 0) ||
+            p->tc_sign_out != sign_out)
+            DNB_TRY(build_tc_args(p, &xin, nhwc, DNB_F32, nhwc ? y_cpitch : 0, nullptr, 0, nchw != nullptr, sign_out, sign_out ? next->c_pad_i8 : 0));
         TcArgs &a = p->tc;
         a.y_nhwc = nhwc; a.y_dtype = DNB_F32; a.y_cpitch = nhwc ? y_cpitch : 0; a.y_nchw = nchw;
         ep.scale = p->scale_i8;

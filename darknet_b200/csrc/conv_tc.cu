@@ -96,10 +96,15 @@ __device__ __forceinline__ float act_apply(float x, int runtime_act)
 // global memory (L2), then adds one to the tile's counter; the CTA that finds the counter at splits - 1 is the last
 // one, sums all ranges in their fixed order (so the result does not depend on who came last) and runs the normal
 // epilogue.  Nobody waits for anybody: no spin, no deadlock.  The last CTA resets the counter for the next launch.
-template <int ACT, int CPC, bool OUT_BF16, int ACT2, bool PAIR, bool I8 = false, bool SPLIT = false>
+// SIGNS (int8 kind, 128-byte staged rows): beside its f32 output the layer writes the output's signs (+1 where the value
+// is > 0, else -1, 0 beyond the layer's filters) as the int8 channels-last tensor that the xnor layer after it reads as
+// its operand: that layer's sign pass over the f32 tensor disappears.  The signs of a chunk are staged in a third
+// staging buffer (two 4 KB halves in rotation) and leave with the chunk's output rows, in the same bulk group.
+template <int ACT, int CPC, bool OUT_BF16, int ACT2, bool PAIR, bool I8 = false, bool SPLIT = false, bool SIGNS = false>
 __global__ void __launch_bounds__(TC_THREADS)
 conv_tc_kernel(const __grid_constant__ TcArgs a)
 {
+    static_assert(!SIGNS || (I8 && CPC == 32 && !OUT_BF16 && !SPLIT), "the sign output belongs to the int8 kind with 128-byte staged rows");
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // operand ring, 1024-byte aligned (the 128-byte swizzle pattern repeats every 1024 bytes).  The kernel
     // has no static shared memory, so the dynamic window starts aligned; no slack is budgeted for rounding
@@ -627,11 +632,32 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                         *reinterpret_cast<uint4 *>(row + ((q ^ q_xor) << 4)) = pk;
                     }
                 }
+                if (SIGNS) {
+                    // 32 signs of this pixel = one 32-byte row of a 32-byte-swizzled box: its two 16-byte halves swap on rows 4..7 of every 8
+                    uint32_t sw[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        uint32_t wd = 0u;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int j = 4 * q + e;
+                            const uint32_t sgn = j < nvalid ? (__uint_as_float(r[j]) > 0.f ? 0x01u : 0xFFu) : 0u;
+                            wd |= sgn << (8 * e);
+                        }
+                        sw[q] = wd;
+                    }
+                    uint8_t *srow = stage_out + (size_t)2 * 128 * srb + (size_t)(chunk_count & 1u) * 128 * 32 + (size_t)m * 32;
+                    const int sx = (m >> 2) & 1;
+                    *reinterpret_cast<uint4 *>(srow + ((0 ^ sx) << 4)) = make_uint4(sw[0], sw[1], sw[2], sw[3]);
+                    *reinterpret_cast<uint4 *>(srow + ((1 ^ sx) << 4)) = make_uint4(sw[4], sw[5], sw[6], sw[7]);
+                }
                 fence_async_smem();            // staged rows visible to the TMA unit
                 epilogue_bar();
                 if (store_thread) {
                     // the TMA unit clips the box at the tensor's extents: ragged tiles need no predicates
                     if (y_nhwc && !(dbg & 2) && (!PAIR || b0 < g.batch)) tma_store_4d(ymap, smem_u32(stage_out + (size_t)buf * 128 * srb), nl0, ow0, oh0, b0);
+                    if (SIGNS && (!PAIR || b0 < g.batch))
+                        tma_store_4d(&a.tms, smem_u32(stage_out + (size_t)2 * 128 * srb + (size_t)(chunk_count & 1u) * 128 * 32), nl0, ow0, oh0, b0);
                     tma_store_commit();
                     if (res_tiles) {
                         // the tile three chunks on goes into the buffer of the previous chunk, once that chunk's
@@ -816,6 +842,11 @@ int launch_conv_tc(const TcArgs &a, cudaStream_t s)
     } while (0)
 #define DNB_TC_LAUNCH_I8_ACT(ACT)                                               \
     do {                                                                        \
+        if (a.sign_out) {                                                       \
+            if (cpc != 32 || a.stage_bufs != 3 || a.splits > 1 || a.ep.raw_acc) DNB_FAIL(DNB_EINVAL, "conv_tc: the sign output needs 128-byte staged rows and a third staging buffer"); \
+            if (a.pair) DNB_TRY(launch_one(conv_tc_kernel<ACT, 32, false, ACT2_NONE, true, true, false, true>, a, smem, s)); \
+            else DNB_TRY(launch_one(conv_tc_kernel<ACT, 32, false, ACT2_NONE, false, true, false, true>, a, smem, s)); \
+        } else                                                                  \
         if (cpc == 32) DNB_TC_GO(ACT, 32, false, ACT2_NONE, true);              \
         else if (cpc == 16) DNB_TC_GO_SINGLE(ACT, 16, false, ACT2_NONE, true);  \
         else DNB_FAIL(DNB_EINVAL, "conv_tc: no int8 kernel for %d columns per chunk", cpc); \

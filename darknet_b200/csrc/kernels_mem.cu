@@ -49,8 +49,10 @@ template <typename T> struct Vec16 {
 template <typename T, int SIZE>
 __global__ void __launch_bounds__(256)
 maxpool_nhwc_kernel(const T *__restrict__ x, T *__restrict__ y, int B, int H, int W, int cvecs,
-                    int OH, int OW, int size_rt, int stride, int off)
+                    int OH, int OW, int size_rt, int stride, int off, int8_t *__restrict__ signs, int spitch)
 {
+    // signs (f32 tensors only): also write the signs of the output (+1 where > 0, else -1) as an int8 channels-last
+    // tensor of pitch spitch, the operand of the tensor-core xnor layer that follows; every channel is a real one there
     using V = Vec16<T>;
     const int size = SIZE > 0 ? SIZE : size_rt;
     const int rows = B * OH, row_vecs = OW * cvecs;
@@ -103,6 +105,11 @@ maxpool_nhwc_kernel(const T *__restrict__ x, T *__restrict__ y, int B, int H, in
 #pragma unroll
             for (int k = 0; k < V::N; ++k) o.v[k] = from_float<T>(best[k]);
             yrow[j] = o.raw;
+            if (V::N == 4 && signs) {
+                const uint32_t sg = (best[0] > 0.f ? 0x01u : 0xFFu) | (best[1] > 0.f ? 0x0100u : 0xFF00u) |
+                                    (best[2] > 0.f ? 0x010000u : 0xFF0000u) | (best[V::N - 1] > 0.f ? 0x01000000u : 0xFF000000u);
+                *reinterpret_cast<uint32_t *>(signs + ((size_t)row * OW + ow) * spitch + 4 * cv) = sg;
+            }
         }
     }
 }
@@ -131,7 +138,7 @@ __global__ void maxpool_nchw_kernel(const float *__restrict__ x, float *__restri
     }
 }
 
-int launch_maxpool(const dnb_tensor *x, const dnb_tensor *y, int size, int stride, int padding, cudaStream_t s)
+int launch_maxpool(const dnb_tensor *x, const dnb_tensor *y, int size, int stride, int padding, cudaStream_t s, int8_t *signs, int spitch)
 {
     DNB_TRY(check_tensor(x, "maxpool input"));
     DNB_TRY(check_tensor(y, "maxpool output"));
@@ -151,13 +158,16 @@ int launch_maxpool(const dnb_tensor *x, const dnb_tensor *y, int size, int strid
         if (x->cpitch != y->cpitch) DNB_FAIL(DNB_EINVAL, "maxpool: cpitch differs (%d vs %d)", x->cpitch, y->cpitch);
         if (x->dtype == DNB_F32) {
             int cv = x->cpitch / 4;
-            MAXPOOL_LAUNCH(float, (const float *)x->data, (float *)y->data, x->n, x->h, x->w, cv, oh, ow, size, stride, off);
+            if (signs && (x->c % 32 || x->cpitch != x->c || spitch < x->c)) DNB_FAIL(DNB_EINVAL, "maxpool: the sign output needs a multiple of 32 channels, unpadded");
+            MAXPOOL_LAUNCH(float, (const float *)x->data, (float *)y->data, x->n, x->h, x->w, cv, oh, ow, size, stride, off, signs, spitch);
         } else {
             int cv = x->cpitch / 8;
-            MAXPOOL_LAUNCH(__nv_bfloat16, (const __nv_bfloat16 *)x->data, (__nv_bfloat16 *)y->data, x->n, x->h, x->w, cv, oh, ow, size, stride, off);
+            if (signs) DNB_FAIL(DNB_EINVAL, "maxpool: the sign output is built for f32 tensors");
+            MAXPOOL_LAUNCH(__nv_bfloat16, (const __nv_bfloat16 *)x->data, (__nv_bfloat16 *)y->data, x->n, x->h, x->w, cv, oh, ow, size, stride, off, nullptr, 0);
         }
     } else {
         if (x->dtype != DNB_F32) DNB_FAIL(DNB_EINVAL, "maxpool: NCHW tensors must be f32");
+        if (signs) DNB_FAIL(DNB_EINVAL, "maxpool: the sign output is built for channels-last tensors");
         size_t total = (size_t)y->n * y->c * oh * ow;
         maxpool_nchw_kernel<<<grid_for(total, 128), 128, 0, s>>>((const float *)x->data, (float *)y->data, x->n * x->c, x->h, x->w, oh, ow, size, stride, off);
     }

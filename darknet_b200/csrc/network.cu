@@ -55,6 +55,9 @@ struct Layer {
     bool fuses_next_shortcut = false, fused_into_prev = false;
     // a convolution that also performs the [yolo] layer right after it (that layer is then fused_into_prev too)
     bool fuses_next_yolo = false;
+    // a maxpool layer that also writes the signs of its output, the next (tensor-core xnor) layer's operand
+    int8_t *sign_out = nullptr;
+    int sign_pitch = 0;
     // the output is a channel range of a later [route] layer's output: its producer writes it in place and the route
     // has nothing to copy for it (the memory belongs to the route layer)
     bool out_is_view = false;
@@ -403,6 +406,17 @@ static int build_network(const char *text, int mode, int batch_override, dnb_net
         }
         R.launches = copies;
     }
+    // xnor layers in a row: the first one's epilogue writes the second one's int8 operand (conv_plan_link_signs)
+    for (int i = 0; i + 1 < (int)net->layers.size(); ++i) {
+        Layer &A = net->layers[i], &B = net->layers[i + 1];
+        if (B.kind != L_CONV || !B.plan || !A.out.data || A.out.layout != DNB_NHWC) continue;
+        if (A.kind == L_CONV && A.plan) {
+            if (conv_plan_link_signs(A.plan, B.plan, A.out.data)) B.launches = 1;   // no sign pass of its own
+        } else if (A.kind == L_MAXPOOL && A.out.dtype == DNB_F32 && A.out.cpitch == A.out_c) {
+            A.sign_out = conv_plan_expect_signs(B.plan, A.out.data, net->batch, A.out_c, A.out_h, A.out_w);
+            if (A.sign_out) { A.sign_pitch = A.out_c; B.launches = 1; }
+        }
+    }
     const Layer &last = net->layers.back();
     net->outputs = last.out_c * last.out_h * last.out_w;
     DNB_CUDA(cudaMalloc((void **)&net->input_dev, (size_t)net->batch * net->inputs * sizeof(float)));
@@ -687,7 +701,7 @@ static int forward_layer(dnb_network *net, int i, const float *device_input, cud
         flat.c = flat.cpitch = L.cd.c;
         return dnb_conv_forward(L.plan, &flat, &L.out, nullptr, s);
     }
-    case L_MAXPOOL: return launch_maxpool(&in, &L.out, L.size, L.stride, L.padding, s);
+    case L_MAXPOOL: return launch_maxpool(&in, &L.out, L.size, L.stride, L.padding, s, L.sign_out, L.sign_pitch);
     case L_UPSAMPLE: return launch_upsample(&in, &L.out, L.stride, L.scale, s);
     case L_SHORTCUT:
         if (L.fused_into_prev) return DNB_OK;   // done by the convolution before it

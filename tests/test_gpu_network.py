@@ -243,3 +243,26 @@ def test_xnor_network_teacher_forced(tmp_path):
     net.predict(x)
     assert sum(net.layer_kernel(i).startswith("xnor_") for i in range(net.n)) == 17
     parity(net.layer_output(0), want[0], 1e-3)   # fp32 stem, stored rounded to TF32 for the next layer
+
+
+@pytest.mark.parametrize("size,batch", [(64, 3), (224, 2)])
+def test_xnor_layers_in_a_row_share_their_signs(size, batch, tmp_path, monkeypatch):
+    """Where one tensor-core xnor layer feeds the next, the first writes the second's int8 operand from its epilogue
+    and the second runs no sign pass.  The signs are those of the stored f32 values, so every layer output must be
+    bit-identical to the network that computes them with the separate pass (DNB_XNOR_SIGNS=0), and fewer kernels run."""
+    cfg = synth.darknet19_cfg(batch=batch, size=size, xnor=True)
+    params = synth.seeded_params(cfg, 31)
+    x = synth.seeded_input(cfg, 31, "uniform")
+    outs, launches = {}, {}
+    for knob in ("0", "1"):
+        monkeypatch.setenv("DNB_XNOR_SIGNS", knob)
+        net = build(cfg, params, tmp_path, dn.MODE_TF32)
+        out = net.predict(x).copy()
+        layers = [net.layer_output(i).copy() for i in range(net.n)]
+        assert sum(net.layer_kernel(i) == "xnor_tc" for i in range(net.n)) == 17
+        outs[knob] = (out, layers)
+        net.close()
+    for i, (a, b) in enumerate(zip(outs["0"][1], outs["1"][1])):
+        assert np.array_equal(a, b), f"layer {i} differs when the signs come from the previous layer's epilogue"
+    assert np.array_equal(outs["0"][0], outs["1"][0])
+    assert np.isfinite(outs["1"][0]).all()
