@@ -125,8 +125,11 @@ int dnb_conv_plan_set_params(dnb_conv_plan *plan, const float *weights, const fl
  * x: input, NCHW f32 or NHWC (f32 for TF32/FP32/xnor plans, bf16 for BF16 plans).
  * y: output, NCHW f32 or NHWC in the plan's storage type (f32, or bf16 for BF16
  * plans).  y2: optional second copy of the
- * output in the other layout (NULL for none).  stream: a cudaStream_t (NULL =
- * default stream). */
+ * output in the other layout (NULL for none).  A TF32 plan rounds the values of
+ * a channels-last f32 output to TF32 (they feed the next layer's tensor-core
+ * operand, which would truncate them otherwise); a copy in Darknet's layout
+ * written by the same call holds the same rounded values, an NCHW-only output
+ * the unrounded ones.  stream: a cudaStream_t (NULL = default stream). */
 int dnb_conv_forward(dnb_conv_plan *plan, const dnb_tensor *x, const dnb_tensor *y,
                      const dnb_tensor *y2, void *stream);
 
