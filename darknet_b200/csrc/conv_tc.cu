@@ -73,7 +73,11 @@ __device__ __forceinline__ float act_apply(float x, int runtime_act)
 {
     if (ACT == DNB_LINEAR || ACT == ACT_YOLO) return x;
     if (ACT == DNB_LEAKY) return fmaxf(x, 0.1f * x);   // x > 0 ? x : 0.1x
-    return activate_call(x, runtime_act);   // the 14-way switch, out of line
+    // the run-time variant: relu (Darknet's VGG and AlexNet cfgs) and logistic inline, the rest of the 14-way switch
+    // out of line (a call per element costs the epilogue several times its normal instruction count)
+    if (runtime_act == DNB_RELU) return x > 0.f ? x : 0.f;
+    if (runtime_act == DNB_LOGISTIC) return 1.f / (1.f + expf(-x));
+    return activate_call(x, runtime_act);
 }
 
 // ACT: activation folded at compile time (DNB_LINEAR, DNB_LEAKY) or ACT_GENERIC (runtime switch).
