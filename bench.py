@@ -49,7 +49,7 @@ UNIT = "images/s"
 # summed over the kernel's launches of one forward), as (bytes per image, bytes per forward independent of the batch:
 # the weights, read once per launch).  Scaled by the images one step processes.
 NCU_DRAM_TRAFFIC = {
-    ("yolov3", "tf32", 608): (545_228_544.0, 247_579_648.0),
+    ("yolov3", "tf32", 608): (545_665_920.0, 247_579_648.0),
     ("conv3x3", "tf32", 224): (488.0e6 / 64, 0.0),
     ("conv1x1", "tf32", 224): (491.0e6 / 64, 0.0),
 }
