@@ -51,6 +51,7 @@ struct alignas(64) TcArgs {
     CUtensorMap tmw;      // weights [taps][n_pad][c_pad], channels innermost
     CUtensorMap tmy;      // NHWC output, written by TMA stores from the staging rows
     CUtensorMap tmr;      // fused residual (same extents and box as tmy), loaded tile by tile in the epilogue
+    CUtensorMap tmy_warp; // the same output as 32-pixel boxes: the rows one epilogue warp stages (per-warp stores)
     CUtensorMap tms;      // sign output (int8 channels-last, the next xnor layer's operand): 32-channel boxes of the same pixels as tmy
     int is_bf16;          // operand kind: 0 kind::tf32 on f32 operands, 1 kind::f16 on bf16 operands, 2 kind::i8 on int8 sign tensors (xnor)
     int row_bytes;        // bytes of channels per pipeline stage row: 128, 64 or 32 (= swizzle span)
@@ -85,6 +86,7 @@ struct alignas(64) TcArgs {
     float *y_nchw;
     int *status;          // device word: 0, or the code of the wait that expired
     // split-K (layers with fewer tiles than SMs and a long K loop): total_tiles counts (output tile, K range) pairs
+    int warp_stores;      // 1: every epilogue warp stores its own 32 rows (tmy_warp); 0: one store per chunk by one thread (tmy)
     void *sign_out;       // int8 kind: also write the output's signs here ([b][h][w][sign_cpitch] bytes), or null
     int sign_cpitch;
     int splits;           // K ranges per output tile; 1 = off

@@ -397,6 +397,13 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
         const CUtensorMap *ymap = &a.tmy;
         int *status = a.status;
         const bool store_thread = threadIdx.x == 64;
+        // Per-warp stores (no residual tiles, no sign output): every warp stages its own 32 rows, which are a box of the
+        // output like the whole tile is, and sends them off itself; the four warps then meet once per tile instead of
+        // twice per chunk, so one warp's TMEM or store wait no longer stalls the other three.
+        constexpr bool can_warp_store = ACT2 == ACT2_NONE || PAIR;
+        const bool warp_stores = can_warp_store && !SIGNS && a.warp_stores != 0 && a.y_nhwc != nullptr;
+        const int m0 = quarter * 32;
+        const int wl0 = m0 % wt, hl0 = (m0 / wt) % ht, bl0 = m0 / (wt * ht);   // origin of this warp's rows inside the tile
         constexpr bool out_bf16 = OUT_BF16;
         constexpr int srb = CPC * (OUT_BF16 ? 2 : 4);            // bytes of one staged row = swizzle span
         constexpr int q_mask = srb / 16 - 1;
@@ -437,6 +444,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
             const int ow = ow0 + wl, oh = oh0 + hl, b = b0 + bl;
             const bool pix_ok = ow < g.out_w && oh < g.out_h && b < g.batch;
             if (nt != loaded_nt) {
+                if (warp_stores) epilogue_bar();   // no per-chunk barrier in this mode: the other warps may still read the previous tile's vectors
                 // this filter tile's epilogue vectors (zero beyond the layer's filters).  Every thread is past the
                 // previous tile's last barrier, which follows the last read; the barrier below publishes the writes.
                 for (int i = threadIdx.x - 64; i < bn + 64; i += 128) {
@@ -613,8 +621,13 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 }
                 const uint32_t buf = chunk_count & buf_mask;
                 if (!res_tiles) {
-                    if (store_thread && chunk_count >= 2) tma_store_wait_read1();   // the store that last read this buffer is done
-                    epilogue_bar();
+                    if (warp_stores) {
+                        if (lane == 0 && chunk_count >= 2) tma_store_wait_read1();   // this warp's store that last read its rows of the buffer is done
+                        __syncwarp();
+                    } else {
+                        if (store_thread && chunk_count >= 2) tma_store_wait_read1();   // the store that last read this buffer is done
+                        epilogue_bar();
+                    }
                 }   // with a residual the buffer is this thread's to overwrite: its tile landed after that store, and
                     // a thread reads and writes its own row only
                 uint8_t *row = stage_out + (size_t)buf * 128 * srb + (size_t)m * srb;
@@ -656,8 +669,16 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                     *reinterpret_cast<uint4 *>(srow + ((1 ^ sx) << 4)) = make_uint4(sw[4], sw[5], sw[6], sw[7]);
                 }
                 fence_async_smem();            // staged rows visible to the TMA unit
+                if (warp_stores) {
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (!(dbg & 2) && (!PAIR || b0 < g.batch))
+                            tma_store_4d(&a.tmy_warp, smem_u32(stage_out + (size_t)buf * 128 * srb + (size_t)m0 * srb), nl0, ow0 + wl0, oh0 + hl0, b0 + bl0);
+                        tma_store_commit();
+                    }
+                } else
                 epilogue_bar();
-                if (store_thread) {
+                if (!warp_stores && store_thread) {
                     // the TMA unit clips the box at the tensor's extents: ragged tiles need no predicates
                     if (y_nhwc && !(dbg & 2) && (!PAIR || b0 < g.batch)) tma_store_4d(ymap, smem_u32(stage_out + (size_t)buf * 128 * srb), nl0, ow0, oh0, b0);
                     if (SIGNS && (!PAIR || b0 < g.batch))
@@ -693,7 +714,7 @@ conv_tc_kernel(const __grid_constant__ TcArgs a)
                 if (PAIR) mbar_arrive_leader(smem_u32(&sh->acc_empty[acc])); else mbar_arrive(smem_u32(&sh->acc_empty[acc]));
             }
         }
-        if (store_thread) tma_store_wait_all();
+        if (warp_stores ? lane == 0 : store_thread) tma_store_wait_all();
     }
 
     // ---------------- teardown (also the abort path)

@@ -635,6 +635,24 @@ def test_every_activation(act, kernel):
         parity(got, want, tol, f"{kernel} activation {act}")
 
 
+@pytest.mark.parametrize("name", ["c128_38x38_n512_odd_pixel_tiles", "c64_76x76_n256_one_filter_tile"])
+@pytest.mark.parametrize("mode,tol", [(dn.MODE_TF32, TOL_TF32), (dn.MODE_BF16, TOL_BF16)])
+def test_conv_tc_per_warp_stores(name, mode, tol, monkeypatch):
+    """The experimental epilogue in which every warp stores its own 32 rows (DNB_TC_WARP_STORES=1): pairs and single
+    CTAs, against the checker and bit-equal to the default epilogue."""
+    case = conv_case(290, **PAIR_CASES[name])
+    want = oracle_conv(case)
+    outs = {}
+    for pair in ("1", "0"):
+        monkeypatch.setenv("DNB_TC_PAIR", pair)
+        for ws in ("0", "1"):
+            monkeypatch.setenv("DNB_TC_WARP_STORES", ws)
+            _, got, _ = run_conv(case, mode, "nhwc", "nhwc")
+            outs[(pair, ws)] = got
+        assert np.array_equal(outs[(pair, "0")], outs[(pair, "1")])
+        parity(outs[(pair, "1")], want, tol, f"{name} per-warp stores, pair={pair}")
+
+
 def test_conv_tc_all_ones_counts_taps():
     # analytic known answer: ones everywhere -> in-image taps x channels, exact in TF32 and BF16
     C, H, W, N = 16, 9, 10, 16
