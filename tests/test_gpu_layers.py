@@ -653,6 +653,33 @@ def test_conv_tc_per_warp_stores(name, mode, tol, monkeypatch):
         parity(outs[(pair, "1")], want, tol, f"{name} per-warp stores, pair={pair}")
 
 
+DUAL_CASES = {
+    # Darknet's layout written beside the channels-last tensor (what the per-layer attach asks of every convolution),
+    # in the kernel variants the plain cases do not reach
+    "1x1_c512_n256_38x38_b16_pair_flat": (dict(b=16, c=512, h=38, w=38, n=256, size=1), "pair=1"),     # pairs over a plane treated as one row of pixels
+    "3x3_c1024_n1024_19x19_b1_pair_split": (dict(b=1, c=1024, h=19, w=19, n=1024, size=3), "pair=1"),  # split-K finishing CTA writes both layouts
+    "1x1_c256_n255_76x76_b2_flat": (dict(b=2, c=256, h=76, w=76, n=255, size=1, bn=False, act="linear"), "pair=0"),
+    "3x3_s2_c64_n128_76_b4": (dict(b=4, c=64, h=76, w=76, n=128, size=3, stride=2), "pair=0"),
+}
+
+
+@pytest.mark.parametrize("name", list(DUAL_CASES))
+@pytest.mark.parametrize("mode,tol", [(dn.MODE_TF32, TOL_TF32), (dn.MODE_BF16, TOL_BF16)])
+def test_conv_tc_both_layouts(name, mode, tol, monkeypatch):
+    monkeypatch.delenv("DNB_TC_SPLITK", raising=False)
+    monkeypatch.delenv("DNB_TC_PAIR", raising=False)
+    shape, expect = DUAL_CASES[name]
+    case = conv_case(295, **shape)
+    want = oracle_conv(case)
+    plan, got_nchw, got_nhwc = run_conv(case, mode, "nhwc", "nchw", both=True)
+    if mode == dn.MODE_TF32:
+        assert expect in plan.describe(), plan.describe()
+    assert np.array_equal(got_nchw, got_nhwc)
+    parity(got_nchw, want, tol, name)
+    _, only_nchw, _ = run_conv(case, mode, "nchw", "nchw")          # Darknet's layout in and out, nothing else
+    parity(only_nchw, want, tol, name + " (NCHW only)")
+
+
 def test_conv_tc_all_ones_counts_taps():
     # analytic known answer: ones everywhere -> in-image taps x channels, exact in TF32 and BF16
     C, H, W, N = 16, 9, 10, 16
