@@ -50,7 +50,8 @@ def oracle(x, wt, p, size, stride=1):
 @pytest.mark.parametrize("mode,store,tol", [(dn.MODE_TF32, torch.float32, 1e-2), (dn.MODE_BF16, torch.bfloat16, 3e-2)])
 @pytest.mark.parametrize("shape", [dict(b=2, c=64, h=13, w=13, n=64, size=3), dict(b=4, c=128, h=19, w=19, n=512, size=1),
                                    dict(b=1, c=32, h=40, w=40, n=320, size=3),
-                                   dict(b=8, c=64, h=38, w=38, n=512, size=3)])   # the last one runs as CTA pairs
+                                   dict(b=8, c=64, h=38, w=38, n=512, size=3),     # runs as CTA pairs
+                                   dict(b=1, c=1024, h=19, w=19, n=1024, size=3)])  # pairs with split-K: the tile counters a timed-out launch leaves part-way are zeroed
 def test_wait_expiry_is_reported_and_the_plan_recovers(mode, store, tol, shape):
     size = shape["size"]
     x, wt, p = make_conv(70, **shape)
